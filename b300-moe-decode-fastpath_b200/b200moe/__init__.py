@@ -1,0 +1,24 @@
+"""b200moe: the explicitly routed SwiGLU MoE decode layer on hand-written sm_100a kernels.
+
+Public names follow the reference package (fastpath/__init__.py:3-9) so that
+``from fastpath import B300MoEWorkspace, b300_moe_forward`` becomes
+``from b200moe import B300MoEWorkspace, b300_moe_forward``.
+"""
+
+from ._lib import available as cuda_extension_available
+from ._lib import build_info
+from .forward import ARCHITECTURE, b300_moe_forward
+from .stages import StagedLayer
+from .validation import RoutedMoEShape, validate_routed_moe_inputs
+from .workspace import B300MoEWorkspace
+
+__all__ = [
+    "ARCHITECTURE",
+    "B300MoEWorkspace",
+    "RoutedMoEShape",
+    "StagedLayer",
+    "b300_moe_forward",
+    "build_info",
+    "cuda_extension_available",
+    "validate_routed_moe_inputs",
+]

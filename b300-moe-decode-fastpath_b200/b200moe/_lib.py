@@ -1,0 +1,194 @@
+"""ctypes binding of libb200moe.so (declarations: include/b200moe.h).
+
+This is the only place the Python side touches native code.  It takes the
+place of the reference's pybind11 module ``fastpath._C`` (csrc/bindings.cpp:24-99),
+but the boundary is a plain C ABI: device pointers as integers, sizes, and the
+CUDA stream handle.  A missing library is an error, never a fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import threading
+from pathlib import Path
+from typing import Mapping
+
+LIBRARY_NAME = "libb200moe.so"
+ABI_VERSION = 1
+
+STATUS_BAD_EXPERT_ID = 0x1
+STATUS_PIPE_TIMEOUT = 0x2
+STATUS_PEER_TIMEOUT = 0x4
+
+FLAG_PDL = 0x1
+
+EXPORTS = (
+    "b200moe_abi_version",
+    "b200moe_build_info",
+    "b200moe_error_string",
+    "b200moe_scratch_bytes",
+    "b200moe_routing",
+    "b200moe_gather",
+    "b200moe_gate_up_swiglu",
+    "b200moe_down",
+    "b200moe_combine",
+    "b200moe_forward",
+    "b200moe_status_ptr",
+    "b200moe_nvfp4_available",
+)
+
+
+class B200MoeArgs(ctypes.Structure):
+    """Mirror of ``struct B200MoeArgs`` in include/b200moe.h (field order matters)."""
+
+    _fields_ = [
+        ("hidden_states", ctypes.c_void_p),
+        ("expert_indices", ctypes.c_void_p),
+        ("expert_weights", ctypes.c_void_p),
+        ("gate_up_weight", ctypes.c_void_p),
+        ("down_weight", ctypes.c_void_p),
+        ("num_tokens", ctypes.c_int32),
+        ("top_k", ctypes.c_int32),
+        ("num_experts", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("intermediate_size", ctypes.c_int32),
+        ("rows_cap", ctypes.c_int32),
+        ("expert_counts", ctypes.c_void_p),
+        ("expert_offsets", ctypes.c_void_p),
+        ("expert_offsets_i32", ctypes.c_void_p),
+        ("permutation", ctypes.c_void_p),
+        ("reverse_mapping", ctypes.c_void_p),
+        ("permuted_token_indices", ctypes.c_void_p),
+        ("permuted_expert_indices", ctypes.c_void_p),
+        ("permuted_weights", ctypes.c_void_p),
+        ("permuted_hidden", ctypes.c_void_p),
+        ("swiglu_output", ctypes.c_void_p),
+        ("expert_output", ctypes.c_void_p),
+        ("scratch", ctypes.c_void_p),
+        ("scratch_bytes", ctypes.c_size_t),
+        ("output", ctypes.c_void_p),
+        ("flags", ctypes.c_uint32),
+    ]
+
+
+_lock = threading.Lock()
+_library: ctypes.CDLL | None = None
+
+
+def library_path() -> Path:
+    override = os.environ.get("B200MOE_SO")
+    if override:
+        return Path(override)
+    return Path(__file__).resolve().parent / LIBRARY_NAME
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    args_p = ctypes.POINTER(B200MoeArgs)
+    lib.b200moe_abi_version.restype = ctypes.c_int
+    lib.b200moe_abi_version.argtypes = []
+    lib.b200moe_build_info.restype = ctypes.c_int
+    lib.b200moe_build_info.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    lib.b200moe_error_string.restype = ctypes.c_char_p
+    lib.b200moe_error_string.argtypes = [ctypes.c_int]
+    lib.b200moe_scratch_bytes.restype = ctypes.c_int
+    lib.b200moe_scratch_bytes.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(ctypes.c_size_t)]
+    for name in (
+        "b200moe_routing",
+        "b200moe_gather",
+        "b200moe_gate_up_swiglu",
+        "b200moe_down",
+        "b200moe_combine",
+        "b200moe_forward",
+    ):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [args_p, ctypes.c_void_p]
+    lib.b200moe_status_ptr.restype = ctypes.c_int
+    lib.b200moe_status_ptr.argtypes = [
+        ctypes.c_void_p,
+        ctypes.c_size_t,
+        ctypes.POINTER(ctypes.c_void_p),
+    ]
+    lib.b200moe_nvfp4_available.restype = ctypes.c_int
+    lib.b200moe_nvfp4_available.argtypes = []
+
+
+def load() -> ctypes.CDLL:
+    """Load the native library once; raise ``RuntimeError`` when it is absent.
+
+    Same policy as the reference's ``_load_goal_1b_extension``
+    (fastpath/b300_moe.py:394-401): a compiled backend that cannot be loaded is
+    an error, not a reason to run something else.
+    """
+
+    global _library
+    with _lock:
+        if _library is not None:
+            return _library
+        path = library_path()
+        if not path.exists():
+            raise RuntimeError(
+                f"{LIBRARY_NAME} is missing at {path}; build it for sm_100a with "
+                "`python b300-moe-decode-fastpath_b200/build.py` (there is no fallback path)"
+            )
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise RuntimeError(f"could not load {path}: {error}") from error
+        missing = [name for name in EXPORTS if not hasattr(lib, name)]
+        if missing:
+            raise RuntimeError(f"{path} lacks required exports: {', '.join(missing)}")
+        _declare(lib)
+        version = lib.b200moe_abi_version()
+        if version != ABI_VERSION:
+            raise RuntimeError(f"{path} has ABI version {version}, expected {ABI_VERSION}")
+        _library = lib
+        return lib
+
+
+def available() -> bool:
+    """Whether the native library can be loaded (mirrors ``cuda_extension_available``)."""
+
+    try:
+        load()
+    except RuntimeError:
+        return False
+    return True
+
+
+def error_string(code: int) -> str:
+    text = load().b200moe_error_string(int(code))
+    return text.decode() if text else f"error {code}"
+
+
+def check(code: int, what: str) -> None:
+    """Raise for a non-zero return code of a native call."""
+
+    if code == 0:
+        return
+    message = f"{what} failed: {error_string(code)} (code {code})"
+    if code < 0:
+        raise ValueError(message)
+    raise RuntimeError(message)
+
+
+def build_info() -> Mapping[str, object]:
+    """The library's build attestation (mirrors ``fastpath._C.build_info()``)."""
+
+    lib = load()
+    buffer = ctypes.create_string_buffer(1024)
+    lib.b200moe_build_info(buffer, len(buffer))
+    return json.loads(buffer.value.decode())
+
+
+def scratch_bytes(
+    max_tokens: int, top_k: int, num_experts: int, hidden_size: int, intermediate_size: int
+) -> int:
+    size = ctypes.c_size_t(0)
+    code = load().b200moe_scratch_bytes(
+        max_tokens, top_k, num_experts, hidden_size, intermediate_size, ctypes.byref(size)
+    )
+    check(code, "b200moe_scratch_bytes")
+    return int(size.value)

@@ -1,0 +1,304 @@
+"""``b300_moe_forward``: the reference's public entry point on the sm_100a kernels.
+
+Signature, argument meaning, check order, error types and metadata fields
+follow fastpath/b300_moe.py:847-996.  What differs is what runs: one C call
+(``b200moe_forward``) enqueues five hand-written kernels on the current stream;
+there is no PyTorch execution path, no second backend and no fallback --
+``metadata["used_fallback"]`` is always ``False`` because there is nothing to
+fall back to.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Mapping
+
+import torch
+
+from . import _lib
+from .validation import (
+    MAX_EXPERTS,
+    RoutedMoEShape,
+    normalize_backend,
+    normalize_gemm_policy,
+    normalize_quant_mode,
+    validate_routed_moe_inputs,
+)
+from .workspace import B300MoEWorkspace
+
+ARCHITECTURE = "sm_100a"
+GEMM_STRATEGY = "grouped_tcgen05"
+_ROUTING_KEYS = ("expert_counts", "expert_offsets", "permutation", "reverse_mapping")
+
+_build_info_cache: Mapping[str, object] | None = None
+
+
+def _resolve_native_backend(
+    backend: str,
+    hidden_states: torch.Tensor,
+    expert_weights: torch.Tensor,
+    gate_up_weight: torch.Tensor,
+    down_weight: torch.Tensor,
+    shape: RoutedMoEShape,
+) -> Mapping[str, object]:
+    """Hardware / dtype / build gates, in the reference's order (b300_moe.py:516-617).
+
+    Runs before the workspace is touched, so a rejected call leaves
+    ``allocation_count`` unchanged.
+    """
+
+    global _build_info_cache
+    if hidden_states.device.type != "cuda":
+        raise ValueError(f"backend={backend!r} requires CUDA tensors")
+    capability = torch.cuda.get_device_capability(hidden_states.device)
+    if capability != (10, 0):
+        raise RuntimeError(
+            f"backend={backend!r} requires B200 compute capability (10, 0), got {capability}"
+        )
+    if backend == "cutlass_nvfp4":
+        # Same promise as the reference (b300_moe.py:571-596): NVFP4 is never
+        # quietly replaced by the BF16 kernels.
+        available = bool(_lib.load().b200moe_nvfp4_available())
+        raise RuntimeError(
+            "cutlass_nvfp4 is unavailable: no NVFP4 grouped GEMM is compiled into "
+            f"libb200moe.so (nvfp4_available={available}); no fallback was used"
+        )
+    if hidden_states.dtype != torch.bfloat16:
+        raise TypeError(f"{backend} requires bfloat16 inputs and weights")
+    if shape.hidden_size % 8 or shape.intermediate_size % 8:
+        raise ValueError(
+            f"{backend} requires hidden_size and intermediate_size divisible by 8 "
+            "(16-byte BF16 alignment); padding is not implemented"
+        )
+    if shape.num_experts > MAX_EXPERTS:
+        raise ValueError("compiled Goal 1B backends support at most 256 experts")
+    if any(t.requires_grad for t in (hidden_states, expert_weights, gate_up_weight, down_weight)):
+        raise ValueError("compiled Goal 1B backends do not support autograd")
+
+    if _build_info_cache is None:
+        info = _lib.build_info()
+        if info.get("compiled_architecture") != ARCHITECTURE:
+            raise RuntimeError("libb200moe.so was not compiled for sm_100a")
+        if info.get("uses_fallback") is not False:
+            raise RuntimeError("libb200moe.so build_info did not attest uses_fallback=false")
+        _build_info_cache = info
+    return _build_info_cache
+
+
+def _native_args(
+    hidden_states: torch.Tensor,
+    expert_indices: torch.Tensor,
+    expert_weights: torch.Tensor,
+    gate_up_weight: torch.Tensor,
+    down_weight: torch.Tensor,
+    shape: RoutedMoEShape,
+    workspace: B300MoEWorkspace,
+    output: torch.Tensor,
+    flags: int,
+) -> _lib.B200MoeArgs:
+    buffers = workspace.buffers
+    scratch = workspace.scratch
+    if scratch is None:
+        raise RuntimeError("workspace has no private scratch; reserve it for a native backend")
+    args = _lib.B200MoeArgs()
+    args.hidden_states = hidden_states.data_ptr()
+    args.expert_indices = expert_indices.data_ptr()
+    args.expert_weights = expert_weights.data_ptr()
+    args.gate_up_weight = gate_up_weight.data_ptr()
+    args.down_weight = down_weight.data_ptr()
+    args.num_tokens = shape.num_tokens
+    args.top_k = shape.top_k
+    args.num_experts = shape.num_experts
+    args.hidden_size = shape.hidden_size
+    args.intermediate_size = shape.intermediate_size
+    args.rows_cap = workspace.capacity_assignments
+    for name in (
+        "expert_counts",
+        "expert_offsets",
+        "expert_offsets_i32",
+        "permutation",
+        "reverse_mapping",
+        "permuted_token_indices",
+        "permuted_expert_indices",
+        "permuted_weights",
+        "permuted_hidden",
+        "swiglu_output",
+        "expert_output",
+    ):
+        setattr(args, name, buffers[name].data_ptr())
+    args.scratch = scratch.data_ptr()
+    args.scratch_bytes = scratch.numel()
+    args.output = output.data_ptr()
+    args.flags = flags
+    return args
+
+
+def _run_native(
+    hidden_states: torch.Tensor,
+    expert_indices: torch.Tensor,
+    expert_weights: torch.Tensor,
+    gate_up_weight: torch.Tensor,
+    down_weight: torch.Tensor,
+    shape: RoutedMoEShape,
+    workspace: B300MoEWorkspace,
+    flags: int,
+) -> tuple[torch.Tensor, dict[str, torch.Tensor]]:
+    """One C call enqueues routing, gather, gate+up+SwiGLU, down and combine."""
+
+    # The result is a fresh tensor, never a view of scratch (b300_moe.py:659).
+    output = torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
+    args = _native_args(
+        hidden_states,
+        expert_indices,
+        expert_weights,
+        gate_up_weight,
+        down_weight,
+        shape,
+        workspace,
+        output,
+        flags,
+    )
+    stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
+    with torch.cuda.device(hidden_states.device):
+        code = _lib.load().b200moe_forward(ctypes.byref(args), ctypes.c_void_p(stream))
+    _lib.check(code, "b200moe_forward")
+    buffers = workspace.buffers
+    rows = shape.num_assignments
+    routed = {
+        "expert_counts": buffers["expert_counts"][: shape.num_experts],
+        "expert_offsets": buffers["expert_offsets"][: shape.num_experts + 1],
+        "permutation": buffers["permutation"][:rows],
+        "reverse_mapping": buffers["reverse_mapping"][:rows],
+    }
+    return output, routed
+
+
+def b300_moe_forward(
+    hidden_states: torch.Tensor,
+    expert_indices: torch.Tensor,
+    expert_weights: torch.Tensor,
+    gate_up_weight: torch.Tensor,
+    down_weight: torch.Tensor,
+    *,
+    num_experts: int,
+    top_k: int,
+    quant_mode: str | None = None,
+    backend: str = "cutlass_bf16",
+    workspace: B300MoEWorkspace | None = None,
+    gemm_policy: str = "auto",
+    return_metadata: bool = False,
+    check_status: bool = False,
+    use_pdl: bool = True,
+) -> torch.Tensor | tuple[torch.Tensor, dict[str, object]]:
+    """Explicitly routed two-GEMM SwiGLU MoE layer for decode-sized batches.
+
+    ``hidden_states`` [T,H], ``expert_indices`` [T,K] int64, ``expert_weights``
+    [T,K], ``gate_up_weight`` [E,2I,H] (gate rows first), ``down_weight``
+    [E,H,I]; everything BF16, contiguous, on one CUDA device of compute
+    capability 10.0.  Routing weights are used exactly as given.
+
+    ``backend``: ``"cutlass_bf16"`` (the reference's name, accepted so callers
+    need not change) and ``"b200_bf16"`` select the same sm_100a kernels;
+    ``"cutlass_nvfp4"`` always raises; ``"torch"`` raises because the PyTorch
+    path is the test oracle, not part of this library.  ``gemm_policy`` is
+    validated and reported but selects nothing.  ``check_status=True`` reads the
+    device status word after the call (one synchronisation) and raises for
+    out-of-range expert ids.  ``use_pdl`` chains the five kernels with
+    programmatic dependent launch.
+    """
+
+    if not isinstance(return_metadata, bool):
+        raise TypeError("return_metadata must be a bool")
+    backend = normalize_backend(backend)
+    gemm_policy = normalize_gemm_policy(gemm_policy)
+    shape = validate_routed_moe_inputs(
+        hidden_states,
+        expert_indices,
+        expert_weights,
+        gate_up_weight,
+        down_weight,
+        num_experts=num_experts,
+        top_k=top_k,
+    )
+    quant_mode = normalize_quant_mode(backend, quant_mode, hidden_states.dtype)
+    if workspace is not None and not isinstance(workspace, B300MoEWorkspace):
+        raise TypeError("workspace must be a B300MoEWorkspace or None")
+    if workspace is not None and any(
+        t.requires_grad for t in (hidden_states, expert_weights, gate_up_weight, down_weight)
+    ):
+        raise ValueError(
+            "B300MoEWorkspace is inference-only; omit workspace when autograd is required"
+        )
+    if backend == "torch":
+        raise RuntimeError(
+            "backend='torch' is the reference oracle (oracle/moe_oracle.py in this "
+            "repository) and is not an execution path of this library; there is no "
+            "CPU or PyTorch fallback"
+        )
+
+    build_info = _resolve_native_backend(
+        backend, hidden_states, expert_weights, gate_up_weight, down_weight, shape
+    )
+    active = workspace if workspace is not None else B300MoEWorkspace(device=hidden_states.device)
+
+    with active._lock:
+        reused = active.reserve(
+            num_tokens=shape.num_tokens,
+            num_experts=shape.num_experts,
+            top_k=shape.top_k,
+            hidden_size=shape.hidden_size,
+            intermediate_size=shape.intermediate_size,
+            device=hidden_states.device,
+            dtype=hidden_states.dtype,
+            backend=backend,
+            quant_mode=quant_mode,
+        )
+        output, routed = _run_native(
+            hidden_states,
+            expert_indices,
+            expert_weights,
+            gate_up_weight,
+            down_weight,
+            shape,
+            active,
+            _lib.FLAG_PDL if use_pdl else 0,
+        )
+        metadata: dict[str, object] | None = None
+        if return_metadata:
+            # Clones are taken while the lock is held and before the completion
+            # event is recorded, so a later reuse on another stream cannot
+            # overwrite what they read (b300_moe.py:972-990).
+            metadata = {
+                "backend": backend,
+                "architecture": ARCHITECTURE,
+                "quant_mode": quant_mode,
+                "used_fallback": False,
+            }
+            for key in _ROUTING_KEYS:
+                metadata[key] = routed[key].clone()
+            metadata["workspace"] = {
+                "capacity_tokens": active.capacity_tokens,
+                "capacity_assignments": active.capacity_assignments,
+                "capacity_bytes": active.capacity_bytes,
+                "allocation_count": active.allocation_count,
+                "reuse_count": active.reuse_count,
+                "reused": reused,
+                "shape_signature": active.shape_signature,
+            }
+            metadata["build"] = dict(build_info)
+            metadata["gemm_dispatch"] = {
+                "policy": gemm_policy,
+                "gate_up_strategy": GEMM_STRATEGY,
+                "down_strategy": GEMM_STRATEGY,
+                "total_rows": shape.num_assignments,
+                "active_experts": None,
+            }
+        active._record_use()
+        if check_status:
+            active.raise_for_status()
+
+    if return_metadata:
+        assert metadata is not None
+        return output, metadata
+    return output
+

@@ -1,0 +1,114 @@
+"""Stage-by-stage access to the native layer, for tests and per-stage timing.
+
+The reference times its stages by calling the extension's staged functions one
+by one (benchmark/benchmark_goal_1b.py:389-500).  ``StagedLayer`` does the same
+over the C ABI: it binds one set of inputs and one workspace to a
+``B200MoeArgs`` struct once and can then enqueue any single stage, or the whole
+layer, on the current stream without further Python work.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .forward import _native_args, _resolve_native_backend
+from .validation import validate_routed_moe_inputs
+from .workspace import B300MoEWorkspace
+
+STAGES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
+
+
+class StagedLayer:
+    """One bound call of the layer whose stages can be enqueued separately."""
+
+    def __init__(
+        self,
+        hidden_states: torch.Tensor,
+        expert_indices: torch.Tensor,
+        expert_weights: torch.Tensor,
+        gate_up_weight: torch.Tensor,
+        down_weight: torch.Tensor,
+        *,
+        num_experts: int,
+        top_k: int,
+        workspace: B300MoEWorkspace | None = None,
+        use_pdl: bool = True,
+    ) -> None:
+        self.shape = validate_routed_moe_inputs(
+            hidden_states,
+            expert_indices,
+            expert_weights,
+            gate_up_weight,
+            down_weight,
+            num_experts=num_experts,
+            top_k=top_k,
+        )
+        _resolve_native_backend(
+            "b200_bf16", hidden_states, expert_weights, gate_up_weight, down_weight, self.shape
+        )
+        self.device = hidden_states.device
+        self.workspace = workspace or B300MoEWorkspace(device=self.device)
+        self.workspace.reserve(
+            num_tokens=self.shape.num_tokens,
+            num_experts=self.shape.num_experts,
+            top_k=self.shape.top_k,
+            hidden_size=self.shape.hidden_size,
+            intermediate_size=self.shape.intermediate_size,
+            device=self.device,
+            dtype=hidden_states.dtype,
+            backend="b200_bf16",
+            quant_mode="bf16",
+        )
+        self.output = torch.empty_like(hidden_states)
+        # keep the inputs alive for as long as their addresses sit in the struct
+        self._inputs = (hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight)
+        self._args = _native_args(
+            hidden_states,
+            expert_indices,
+            expert_weights,
+            gate_up_weight,
+            down_weight,
+            self.shape,
+            self.workspace,
+            self.output,
+            _lib.FLAG_PDL if use_pdl else 0,
+        )
+        lib = _lib.load()
+        self._calls = {
+            "routing": lib.b200moe_routing,
+            "gather": lib.b200moe_gather,
+            "gate_up_swiglu": lib.b200moe_gate_up_swiglu,
+            "down": lib.b200moe_down,
+            "combine": lib.b200moe_combine,
+            "forward": lib.b200moe_forward,
+        }
+
+    def _stream(self) -> ctypes.c_void_p:
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def run_stage(self, name: str) -> None:
+        """Enqueue one stage (or ``"forward"`` for all five) on the current stream."""
+
+        code = self._calls[name](ctypes.byref(self._args), self._stream())
+        _lib.check(code, f"b200moe_{name}")
+
+    def forward(self) -> torch.Tensor:
+        self.run_stage("forward")
+        return self.output
+
+    def routing_tensors(self) -> dict[str, torch.Tensor]:
+        rows = self.shape.num_assignments
+        buffers = self.workspace.buffers
+        return {
+            "expert_counts": buffers["expert_counts"][: self.shape.num_experts],
+            "expert_offsets": buffers["expert_offsets"][: self.shape.num_experts + 1],
+            "expert_offsets_i32": buffers["expert_offsets_i32"][: self.shape.num_experts],
+            "permutation": buffers["permutation"][:rows],
+            "reverse_mapping": buffers["reverse_mapping"][:rows],
+            "permuted_token_indices": buffers["permuted_token_indices"][:rows],
+            "permuted_expert_indices": buffers["permuted_expert_indices"][:rows],
+            "permuted_weights": buffers["permuted_weights"][:rows],
+        }

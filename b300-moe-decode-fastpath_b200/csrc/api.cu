@@ -1,0 +1,386 @@
+// extern "C" entry points of libb200moe.so (declared in include/b200moe.h):
+// argument checks, TMA tensor-map encoding, grid sizing and kernel launches.
+// Host code here never allocates device memory, never synchronises and never
+// reads device memory.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+// kernels / launchers defined in the other translation units
+cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assign, int top_k,
+                           int num_experts, int64_t* counts, int64_t* offsets,
+                           int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
+                           int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
+                           int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
+                           int target_ctas, cudaStream_t stream);
+cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
+                          int num_assign, int num_tokens, int top_k, int hidden_size, bool pdl,
+                          cudaStream_t stream);
+cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
+                           const float* partials, const int32_t* sched, void* out,
+                           void* expert_out, int num_tokens, int top_k, int hidden_size,
+                           size_t slice_elems, bool pdl, cudaStream_t stream);
+cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
+                           const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
+                           int inter, int hidden, int rows_cap, int grid, bool pdl,
+                           cudaStream_t stream);
+cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
+                        const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
+                        float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
+                        cudaStream_t stream);
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+  bool probed = false;
+  int cc_major = 0, cc_minor = 0, sm_count = 0;
+};
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_mutex;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+bool g_encode_probed = false;
+
+// Properties of the current device, probed once per device.
+int current_device_info(DeviceInfo* out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return (int)err;
+  if (dev < 0 || dev >= kMaxDevices) return B200MOE_E_ARCH;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& info = g_devices[dev];
+  if (!info.probed) {
+    err = cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (err != cudaSuccess) return (int)err;
+    err = cudaDeviceGetAttribute(&info.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
+    if (err != cudaSuccess) return (int)err;
+    err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return (int)err;
+    info.probed = true;
+  }
+  *out = info;
+  // The cubin is sm_100a: architecture-specific, it runs on CC 10.0 only.
+  if (info.cc_major != 10 || info.cc_minor != 0) return B200MOE_E_ARCH;
+  return 0;
+}
+
+int resolve_encoder() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_encode_probed) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (err == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    g_encode_probed = true;
+  }
+  return g_encode ? 0 : B200MOE_E_DRIVER;
+}
+
+// BF16 tensor map, innermost dimension first, 128-byte swizzle, zero fill
+// outside the tensor.  `dims`/`box` have `rank` entries.
+int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint32_t* box) {
+  int rc = resolve_encoder();
+  if (rc) return rc;
+  cuuint64_t gdim[5];
+  cuuint64_t gstride[4];
+  cuuint32_t bdim[5];
+  cuuint32_t estride[5];
+  uint64_t stride = sizeof(__nv_bfloat16);
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estride[i] = 1;
+    stride *= dims[i];
+    if (i + 1 < rank) gstride[i] = stride;
+  }
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
+                        const_cast<void*>(base), gdim, gstride, bdim, estride,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_shape(int tokens, int top_k, int experts, int hidden, int inter) {
+  if (tokens < 1 || hidden < 1 || inter < 1 || experts < 1) return B200MOE_E_SHAPE;
+  if (!(top_k == 1 || top_k == 2 || top_k == 4 || top_k == 8)) return B200MOE_E_SHAPE;
+  if (experts > B200MOE_MAX_EXPERTS || top_k > experts) return B200MOE_E_SHAPE;
+  if ((long long)tokens * top_k > (1ll << 24)) return B200MOE_E_SHAPE;
+  if (hidden % 8 || inter % 8) return B200MOE_E_ALIGN;
+  return 0;
+}
+
+// Upper bound on the number of segments `rows` assignments can produce.
+int segment_bound(int rows, int experts) {
+  return (rows < experts ? rows : experts) + rows / kSegRows;
+}
+
+int tiles128(int n) { return (n + 127) / 128; }
+
+struct Scratch {
+  uint32_t* status;
+  int32_t* sched;
+  void* act_lo;
+  float* partials;
+};
+
+int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts, int hidden,
+                  int inter, Scratch* out) {
+  if (!scratch) return B200MOE_E_NULL;
+  if (reinterpret_cast<uintptr_t>(scratch) % kScratchAlign) return B200MOE_E_ALIGN;
+  const ScratchLayout l = scratch_layout(rows_cap, experts, hidden, inter);
+  if (scratch_bytes < l.total) return B200MOE_E_SCRATCH;
+  char* b = static_cast<char*>(scratch);
+  out->status = reinterpret_cast<uint32_t*>(b + l.status);
+  out->sched = reinterpret_cast<int32_t*>(b + l.sched);
+  out->act_lo = b + l.act_lo;
+  out->partials = reinterpret_cast<float*>(b + l.partials);
+  return 0;
+}
+
+int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
+               cudaStream_t stream) {
+  return (int)launch_routing(a->expert_indices, a->expert_weights, a->num_tokens * a->top_k,
+                             a->top_k, a->num_experts, a->expert_counts, a->expert_offsets,
+                             a->reverse_mapping, a->permutation, a->expert_offsets_i32,
+                             a->permuted_token_indices, a->permuted_expert_indices,
+                             a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
+                             (a->intermediate_size + 63) / 64, 2 * dev.sm_count, stream);
+}
+
+int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
+               int hidden, int inter, void* act_hi, const Scratch& s, bool pdl,
+               cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  {
+    const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
+    const uint32_t box[4] = {64, 128, 2, 1};
+    int rc = encode_bf16_map(&map_w, w, 4, dims, box);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)rows_cap};
+    const uint32_t box[2] = {64, 16};
+    int rc = encode_bf16_map(&map_x, x, 2, dims, box);
+    if (rc) return rc;
+  }
+  const int grid = segment_bound(assignments, experts) * tiles128(inter);
+  return (int)launch_gate_up(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, inter, hidden,
+                             rows_cap, grid, pdl, stream);
+}
+
+int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, int experts,
+            int hidden, int inter, const Scratch& s, const DeviceInfo& dev, bool pdl,
+            cudaStream_t stream) {
+  CUtensorMap map_w, map_hi, map_lo;
+  {
+    const uint64_t dims[3] = {(uint64_t)inter, (uint64_t)hidden, (uint64_t)experts};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = encode_bf16_map(&map_w, w, 3, dims, box);
+    if (rc) return rc;
+  }
+  const uint64_t dims[2] = {(uint64_t)inter, (uint64_t)rows_cap};
+  const uint32_t box[2] = {64, 16};
+  int rc = encode_bf16_map(&map_hi, act_hi, 2, dims, box);
+  if (rc) return rc;
+  rc = encode_bf16_map(&map_lo, s.act_lo, 2, dims, box);
+  if (rc) return rc;
+  // Without split-K there are at most bound*tiles units; with it the routing
+  // kernel keeps units*splits <= 2 * SM count.
+  int grid = segment_bound(assignments, experts) * tiles128(hidden);
+  if (grid < 2 * dev.sm_count) grid = 2 * dev.sm_count;
+  return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
+                          rows_cap, grid, pdl, stream);
+}
+
+struct Ctx {
+  DeviceInfo dev;
+  Scratch s;
+  int assignments;
+  bool pdl;
+  cudaStream_t stream;
+};
+
+// Checks shared by every stage: geometry, device, scratch region.
+int prepare(const B200MoeArgs* a, void* stream, Ctx* c) {
+  if (!a) return B200MOE_E_NULL;
+  int rc = check_shape(a->num_tokens, a->top_k, a->num_experts, a->hidden_size,
+                       a->intermediate_size);
+  if (rc) return rc;
+  c->assignments = a->num_tokens * a->top_k;
+  if (a->rows_cap < c->assignments) return B200MOE_E_SHAPE;
+  rc = current_device_info(&c->dev);
+  if (rc) return rc;
+  rc = carve_scratch(a->scratch, a->scratch_bytes, a->rows_cap, a->num_experts, a->hidden_size,
+                     a->intermediate_size, &c->s);
+  if (rc) return rc;
+  c->pdl = (a->flags & B200MOE_FLAG_PDL) != 0;
+  c->stream = static_cast<cudaStream_t>(stream);
+  return 0;
+}
+
+int stage_routing(const B200MoeArgs* a, const Ctx& c) {
+  if (!a->expert_indices || !a->expert_counts || !a->expert_offsets || !a->expert_offsets_i32 ||
+      !a->permutation || !a->reverse_mapping)
+    return B200MOE_E_NULL;
+  return do_routing(a, c.s, c.dev, c.stream);
+}
+
+int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+  if (!a->hidden_states || !a->permutation || !a->permuted_hidden) return B200MOE_E_NULL;
+  if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
+  return (int)launch_gather(a->hidden_states, a->permutation, a->permuted_hidden, c.assignments,
+                            a->num_tokens, a->top_k, a->hidden_size, pdl, c.stream);
+}
+
+int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+  if (!a->permuted_hidden || !a->gate_up_weight || !a->swiglu_output) return B200MOE_E_NULL;
+  if (!aligned16(a->permuted_hidden) || !aligned16(a->gate_up_weight) ||
+      !aligned16(a->swiglu_output))
+    return B200MOE_E_ALIGN;
+  return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
+                    a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
+                    pdl, c.stream);
+}
+
+int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+  if (!a->swiglu_output || !a->down_weight) return B200MOE_E_NULL;
+  if (!aligned16(a->swiglu_output) || !aligned16(a->down_weight)) return B200MOE_E_ALIGN;
+  return do_down(a->swiglu_output, a->down_weight, a->rows_cap, c.assignments, a->num_experts,
+                 a->hidden_size, a->intermediate_size, c.s, c.dev, pdl, c.stream);
+}
+
+int stage_combine(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+  if (!a->reverse_mapping || !a->expert_weights || !a->output) return B200MOE_E_NULL;
+  if (!aligned16(a->output) || (a->expert_output && !aligned16(a->expert_output)))
+    return B200MOE_E_ALIGN;
+  return (int)launch_combine(a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched,
+                             a->output, a->expert_output, a->num_tokens, a->top_k,
+                             a->hidden_size, (size_t)a->rows_cap * a->hidden_size, pdl, c.stream);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+
+int b200moe_build_info(char* json, size_t cap) {
+  char buf[768];
+  int n = snprintf(
+      buf, sizeof(buf),
+      "{\"goal\": \"1B\", \"compiled_architecture\": \"sm_100a\", "
+      "\"wrapper_compiled_architecture\": \"sm_100a\", \"uses_fallback\": false, "
+      "\"bf16_grouped_gemm_provider\": \"b200moe tcgen05 grouped GEMM (in-tree, hand-written)\", "
+      "\"bf16_provider_implementation\": \"tcgen05.mma kind::f16, TMEM accumulators, TMA 128B-swizzle loads\", "
+      "\"cutlass_version\": null, \"cuda_runtime_version\": %d, \"nvfp4_compiled\": false, "
+      "\"abi_version\": %d, \"segment_rows\": %d, \"down_split_max\": %d}",
+      (int)CUDART_VERSION, B200MOE_ABI_VERSION, kSegRows, kDownSplitMax);
+  if (json && cap > 0) {
+    size_t c = (size_t)n < cap - 1 ? (size_t)n : cap - 1;
+    memcpy(json, buf, c);
+    json[c] = '\0';
+  }
+  return n;
+}
+
+const char* b200moe_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case B200MOE_E_NULL: return "a required pointer is NULL";
+    case B200MOE_E_SHAPE: return "unsupported shape (T>=1, K in {1,2,4,8}, K<=E<=256)";
+    case B200MOE_E_ALIGN: return "pointers must be 16-byte aligned and H, I divisible by 8";
+    case B200MOE_E_SCRATCH: return "scratch region is smaller than b200moe_scratch_bytes()";
+    case B200MOE_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
+    case B200MOE_E_ARCH: return "device is not compute capability 10.0 (sm_100a)";
+    case B200MOE_E_UNSUPPORTED: return "not implemented (NVFP4 is never substituted by BF16)";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString((cudaError_t)code);
+  return "unknown b200moe error";
+}
+
+int b200moe_scratch_bytes(int max_tokens, int top_k, int num_experts, int hidden_size,
+                          int intermediate_size, size_t* bytes) {
+  if (!bytes) return B200MOE_E_NULL;
+  int rc = check_shape(max_tokens, top_k, num_experts, hidden_size, intermediate_size);
+  if (rc) return rc;
+  *bytes = scratch_layout(max_tokens * top_k, num_experts, hidden_size, intermediate_size).total;
+  return 0;
+}
+
+int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status) {
+  if (!scratch || !status) return B200MOE_E_NULL;
+  if (scratch_bytes < kStatusBytes) return B200MOE_E_SCRATCH;
+  *status = reinterpret_cast<uint32_t*>(scratch);
+  return 0;
+}
+
+int b200moe_nvfp4_available(void) { return 0; }
+
+int b200moe_routing(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  return rc ? rc : stage_routing(a, c);
+}
+
+int b200moe_gather(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  return rc ? rc : stage_gather(a, c, false);
+}
+
+int b200moe_gate_up_swiglu(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  return rc ? rc : stage_gate_up(a, c, false);
+}
+
+int b200moe_down(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  return rc ? rc : stage_down(a, c, false);
+}
+
+int b200moe_combine(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  return rc ? rc : stage_combine(a, c, false);
+}
+
+int b200moe_forward(const B200MoeArgs* a, void* stream) {
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  if (rc) return rc;
+  // All pointer checks first, so a contract error launches nothing at all.
+  if (!a->hidden_states || !a->expert_indices || !a->expert_weights || !a->gate_up_weight ||
+      !a->down_weight || !a->expert_counts || !a->expert_offsets || !a->expert_offsets_i32 ||
+      !a->permutation || !a->reverse_mapping || !a->permuted_hidden || !a->swiglu_output ||
+      !a->output)
+    return B200MOE_E_NULL;
+  if (!aligned16(a->hidden_states) || !aligned16(a->gate_up_weight) ||
+      !aligned16(a->down_weight) || !aligned16(a->permuted_hidden) ||
+      !aligned16(a->swiglu_output) || !aligned16(a->output) ||
+      (a->expert_output && !aligned16(a->expert_output)))
+    return B200MOE_E_ALIGN;
+  if ((rc = stage_routing(a, c))) return rc;
+  if ((rc = stage_gather(a, c, c.pdl))) return rc;
+  if ((rc = stage_gate_up(a, c, c.pdl))) return rc;
+  if ((rc = stage_down(a, c, c.pdl))) return rc;
+  return stage_combine(a, c, c.pdl);
+}
+
+}  // extern "C"

@@ -1,0 +1,328 @@
+// Stages 3 and 4: the two grouped BF16 GEMMs, written for the decode regime
+// where the expert weights are streamed from HBM once and the token count per
+// expert is tiny.
+//
+// Operand roles are swapped relative to the textbook layout: the WEIGHT tile is
+// the 128-row "A" operand of tcgen05.mma and the expert's token rows are the
+// "N" dimension (16..128 columns of the accumulator).  Both operands are
+// K-major in global memory already ([.., 2I, H], [.., H, I], [rows, H],
+// [rows, I]), so TMA brings 64-element (128-byte) K slices straight into the
+// 128-byte-swizzled shared-memory layout the MMA reads; nothing is transposed.
+// Accumulator element (lane m, column j) = weight row m . token row j.
+//
+// One thread block = one work unit = (segment, 128-row weight tile[, K split]).
+// Units are decoded from the schedule the routing kernel left in device memory;
+// blocks whose unit does not exist return at once, so the host launches a grid
+// sized for the worst case without ever reading the routing result back.  Two
+// blocks fit on an SM (<= 109 KB of pipeline stages and <= 256 TMEM columns
+// each), which keeps ~200 KB of TMA loads in flight per SM.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM
+// allocation + MMA issue (one lane), warps 2..5 = epilogue (each owns the 32
+// TMEM lanes its warp id modulo 4 selects).
+//
+// gate+up (stage 3): each pipeline stage holds a 128-row gate tile and the
+// matching 128-row up tile (one 4-D TMA box over [E][2][I][H]) plus the token
+// rows; two accumulators (gate, up) share the token operand, so the epilogue
+// computes silu(g) * u in FP32 thread-locally and stores it as a BF16 high
+// part plus a BF16 low-order remainder.
+//
+// down (stage 4): each stage holds one 128-row weight tile and the high and low
+// activation rows; two MMAs per K step accumulate W . hi + W . lo into one
+// accumulator.  The epilogue stores FP32 rows into this block's split-K slice.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kGemmThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kStageBudget = 108u * 1024u;           // bytes of pipeline stages
+constexpr uint32_t kGemmSmemBytes = kStageBudget + 1024u;  // + slack to align to 1024
+constexpr int kTileM = 128;   // weight rows per unit
+constexpr int kTileK = 64;    // elements per pipeline stage along K (128 bytes)
+constexpr uint64_t kAbortDrainNs = 1000000ull;
+
+struct GemmParams {
+  const int32_t* sched;
+  uint32_t* status;
+  __nv_bfloat16* act_hi;   // gate+up output [rows_cap, I]
+  __nv_bfloat16* act_lo;   // gate+up output [rows_cap, I]
+  float* partials;         // down output [splits][rows_cap][H]
+  int m_total;             // weight rows per expert matrix: I (gate+up) or H (down)
+  int k_total;             // reduction length: H (gate+up) or I (down)
+  int m_tiles;             // ceil(m_total / 128)
+  int rows_cap;
+};
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_full[kMaxStages];
+  __shared__ __align__(8) uint64_t s_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t s_acc;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // Prologue that does not depend on earlier kernels.
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_acc), 1);
+    s_abort = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_b0);
+    if (!kGateUp) prefetch_tensormap(&map_b1);
+  }
+
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // ---- decode this block's unit from the device-built schedule -------------
+  const int n_seg = p.sched[kSchedNumSegments];
+  int unit = blockIdx.x;
+  int split = 0, n_split = 1;
+  if (!kGateUp) {
+    n_split = p.sched[kSchedDownSplits];
+    split = unit % n_split;
+    unit /= n_split;
+  }
+  const int tile = unit % p.m_tiles;
+  const int seg = unit / p.m_tiles;
+  if (seg >= n_seg) return;
+
+  const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
+  const int expert = seg_words[0];
+  const int row_start = seg_words[1];
+  const int n_rows = seg_words[2];
+  const int n_mma = (n_rows + 15) & ~15;  // accumulator columns: 16..128
+
+  const int kblocks = (p.k_total + kTileK - 1) / kTileK;
+  int kb0 = 0, num_kb = kblocks;
+  if (!kGateUp) {
+    const int per = kblocks / n_split, rem = kblocks % n_split;
+    kb0 = split * per + min(split, rem);
+    num_kb = per + (split < rem ? 1 : 0);
+  }
+
+  // ---- shared-memory pipeline geometry ---------------------------------------
+  constexpr uint32_t kABytes = kGateUp ? 2u * kTileM * 128u : kTileM * 128u;
+  const uint32_t b_bytes = (uint32_t)n_mma * 128u * (kGateUp ? 1u : 2u);
+  const uint32_t stage_bytes = kABytes + b_bytes;
+  const int num_stages = min((int)(kStageBudget / stage_bytes), kMaxStages);
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  // ---- tensor memory ------------------------------------------------------------
+  const uint32_t cols_needed = (uint32_t)n_mma * (kGateUp ? 2u : 1u);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < cols_needed) tmem_cols <<= 1;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % num_stages;
+        const uint32_t round = (uint32_t)(i / num_stages);
+        if (i >= num_stages &&
+            !mbar_wait_bounded(smem_u32(&s_empty[s]), (round - 1u) & 1u, abort_flag))
+          break;
+        const uint32_t bar = smem_u32(&s_full[s]);
+        const uint32_t a_dst = smem_base + (uint32_t)s * stage_bytes;
+        const uint32_t b_dst = a_dst + kABytes;
+        const int kc = (kb0 + i) * kTileK;
+        mbar_expect_tx(bar, stage_bytes);
+        if (kGateUp) {
+          tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
+        } else {
+          tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
+        }
+        for (int r = 0; r < n_mma; r += 16) {
+          tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b0, bar, kc, row_start + r);
+          if (!kGateUp)
+            tma_load_2d(b_dst + (uint32_t)(n_mma + r) * 128u, &map_b1, bar, kc, row_start + r);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16_m128((uint32_t)n_mma);
+      bool ok = true;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % num_stages;
+        const uint32_t round = (uint32_t)(i / num_stages);
+        if (!mbar_wait_bounded(smem_u32(&s_full[s]), round & 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_base + (uint32_t)s * stage_bytes;
+        const uint32_t b_addr = a_addr + kABytes;
+        const uint64_t a0 = umma_smem_desc_sw128(a_addr);
+        const uint64_t b0 = umma_smem_desc_sw128(b_addr);
+        if (kGateUp) {
+          const uint64_t a1 = umma_smem_desc_sw128(a_addr + kTileM * 128u);  // up tile
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+            // advancing 16 BF16 elements along K = 32 bytes = 2 descriptor units
+            umma_bf16(tmem, a0 + 2u * k, b0 + 2u * k, idesc, acc);
+            umma_bf16(tmem + (uint32_t)n_mma, a1 + 2u * k, b0 + 2u * k, idesc, acc);
+          }
+        } else {
+          const uint64_t b1 = umma_smem_desc_sw128(b_addr + (uint32_t)n_mma * 128u);  // low halves
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+            umma_bf16(tmem, a0 + 2u * k, b0 + 2u * k, idesc, acc);
+            umma_bf16(tmem, a0 + 2u * k, b1 + 2u * k, idesc, 1u);
+          }
+        }
+        umma_commit(smem_u32(&s_empty[s]));  // frees the stage once these MMAs have read it
+      }
+      if (ok && num_kb > 0) umma_commit(smem_u32(&s_acc));  // accumulators complete
+    }
+  } else {
+    // ===== epilogue: TMEM -> registers -> global =====
+    const int quarter = warp & 3;
+    const int m = tile * kTileM + quarter * 32 + lane;  // weight row of this thread
+    const bool m_ok = m < p.m_total;
+    bool have_acc = num_kb > 0;
+    if (have_acc) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
+    have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld needs the whole warp
+    // A block that gave up writes nothing; the status word reports it.
+    if (have_acc || num_kb == 0) {
+      tc_fence_after_sync();
+      const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+      for (int c0 = 0; c0 < n_mma; c0 += 16) {
+        uint32_t g[16], u[16];
+        if (num_kb > 0) {
+          tmem_ld_16(lane_base + (uint32_t)c0, g);
+          if (kGateUp) tmem_ld_16(lane_base + (uint32_t)(n_mma + c0), u);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+        }
+        if (kGateUp) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (m_ok && c0 + j < n_rows) {
+              const float gate = __uint_as_float(g[j]);
+              const float up = __uint_as_float(u[j]);
+              const float act = gate / (1.0f + __expf(-gate)) * up;
+              const __nv_bfloat16 hi = __float2bfloat16_rn(act);
+              const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
+              const size_t o = (size_t)(row_start + c0 + j) * p.m_total + m;
+              p.act_hi[o] = hi;
+              p.act_lo[o] = lo;
+            }
+          }
+        } else {
+          float* dst = p.partials + (size_t)split * p.rows_cap * p.m_total;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (m_ok && c0 + j < n_rows)
+              dst[(size_t)(row_start + c0 + j) * p.m_total + m] = __uint_as_float(g[j]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    // Some wait ran out.  Give copies and MMAs still in flight time to land
+    // before shared and tensor memory are released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < kAbortDrainNs) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem, tmem_cols);
+  }
+}
+
+template <bool kGateUp>
+static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_b0,
+                               const CUtensorMap& map_b1, const GemmParams& params, int grid,
+                               bool pdl, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    err = cudaFuncSetAttribute(grouped_gemm_kernel<kGateUp>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<kGateUp>, map_w, map_b0, map_b1, params);
+}
+
+cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
+                           const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
+                           int inter, int hidden, int rows_cap, int grid, bool pdl,
+                           cudaStream_t stream) {
+  GemmParams p;
+  p.sched = sched;
+  p.status = status;
+  p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
+  p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
+  p.partials = nullptr;
+  p.m_total = inter;
+  p.k_total = hidden;
+  p.m_tiles = (inter + kTileM - 1) / kTileM;
+  p.rows_cap = rows_cap;
+  return launch_gemm<true>(map_w, map_x, map_x, p, grid, pdl, stream);
+}
+
+cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
+                        const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
+                        float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
+                        cudaStream_t stream) {
+  GemmParams p;
+  p.sched = sched;
+  p.status = status;
+  p.act_hi = nullptr;
+  p.act_lo = nullptr;
+  p.partials = partials;
+  p.m_total = hidden;
+  p.k_total = inter;
+  p.m_tiles = (hidden + kTileM - 1) / kTileM;
+  p.rows_cap = rows_cap;
+  return launch_gemm<false>(map_w, map_hi, map_lo, p, grid, pdl, stream);
+}
+
+}  // namespace b200moe

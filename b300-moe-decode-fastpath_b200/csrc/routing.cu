@@ -1,0 +1,198 @@
+// Stage 1: routing metadata in one launch of one thread block.
+//
+// Computes what the reference builds with three fills, three kernels and a
+// copy (csrc/routing_kernels.cu:24-139, fastpath/b300_moe.py:652-653):
+//   counts[e]          = #{a : id[a] == e}
+//   offsets            = [0, cumsum(counts)]   (empty experts: equal adjacent offsets)
+//   permutation        = stable argsort of the flattened ids
+//   reverse_mapping    = its inverse
+// and, in the same launch, the segment schedule both grouped GEMMs read, so no
+// host synchronisation is needed to size their work.
+//
+// Stability: assignments are visited in chunks of 1024 in increasing order; in
+// a chunk, a warp owns 32 consecutive assignments, a lane's rank among equal
+// ids in its warp is the number of lower lanes with the same id, and warps are
+// ordered by a per-expert running cursor.  Rows of one expert therefore keep
+// increasing assignment ids, which is torch.argsort(stable=True).
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kRoutingThreads = 1024;
+constexpr int kRoutingWarps = kRoutingThreads / 32;
+
+// Exclusive scan of one int per thread over the whole block.  `total` receives
+// the block sum in every thread.  `tmp` is kRoutingWarps ints of shared memory.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* tmp, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += n;
+  }
+  if (lane == 31) tmp[warp] = inc;
+  __syncthreads();
+  int base = 0, sum = 0;
+#pragma unroll 8
+  for (int w = 0; w < kRoutingWarps; ++w) {
+    int t = tmp[w];
+    if (w < warp) base += t;
+    sum += t;
+  }
+  __syncthreads();
+  total = sum;
+  return base + inc - v;
+}
+
+__global__ void __launch_bounds__(kRoutingThreads, 1)
+routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ weights,
+               int num_assign, int top_k, int num_experts, int64_t* __restrict__ counts,
+               int64_t* __restrict__ offsets, int64_t* __restrict__ reverse_mapping,
+               int64_t* __restrict__ permutation, int32_t* __restrict__ offsets_i32,
+               int64_t* __restrict__ perm_tokens, int64_t* __restrict__ perm_experts,
+               __nv_bfloat16* __restrict__ perm_weights, int32_t* __restrict__ sched,
+               uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas) {
+  __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
+  __shared__ int s_cursor[B200MOE_MAX_EXPERTS];
+  __shared__ int s_whist[kRoutingWarps][B200MOE_MAX_EXPERTS];
+  __shared__ int s_tmp[kRoutingWarps];
+  __shared__ int s_bad;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // Everything the next kernel needs from this one is written before this grid
+  // completes, and it waits for completion; let its launch overlap this one.
+  pdl_launch_dependents();
+
+  if (tid < B200MOE_MAX_EXPERTS) s_cnt[tid] = 0;
+  if (tid == 0) {
+    s_bad = 0;
+    *status = 0u;  // the status word describes the forward this launch begins
+  }
+  __syncthreads();
+
+  // Pass 1: histogram.  Ids outside [0, E) are not counted (the reference
+  // ignores them the same way, csrc/routing_kernels.cu:33) and are reported.
+  for (int a = tid; a < num_assign; a += kRoutingThreads) {
+    const int64_t e = ids[a];
+    if (e >= 0 && e < (int64_t)num_experts) {
+      atomicAdd(&s_cnt[(int)e], 1);
+    } else {
+      s_bad = 1;
+    }
+  }
+  __syncthreads();
+
+  const bool is_expert = tid < num_experts;
+  const int my_cnt = is_expert ? s_cnt[tid] : 0;
+  int n_valid;
+  const int my_off = block_exclusive_scan(my_cnt, s_tmp, n_valid);
+  const int my_chunks = (my_cnt + kSegRows - 1) / kSegRows;
+  int n_seg;
+  const int my_seg = block_exclusive_scan(my_chunks, s_tmp, n_seg);
+  const int n_active = __syncthreads_count(my_cnt > 0);
+
+  if (is_expert) {
+    counts[tid] = my_cnt;
+    offsets[tid + 1] = my_off + my_cnt;
+    offsets_i32[tid] = my_off + my_cnt;
+    s_cursor[tid] = my_off;
+    for (int c = 0; c < my_chunks; ++c) {
+      int32_t* seg = sched + kSchedHeaderWords + kSchedSegWords * (my_seg + c);
+      const int done = c * kSegRows;
+      seg[0] = tid;
+      seg[1] = my_off + done;
+      seg[2] = min(kSegRows, my_cnt - done);
+      seg[3] = 0;
+    }
+  }
+  if (tid == 0) {
+    offsets[0] = 0;
+    // Split-K factor of the down projection: when few (segment, tile) units
+    // exist, cut K so that about `target_ctas` blocks stream weights at once.
+    int splits = 1;
+    const int units = n_seg * down_tiles;
+    if (units > 0 && units < target_ctas) splits = target_ctas / units;
+    splits = min(splits, kDownSplitMax);
+    splits = min(splits, max(1, down_kblocks / 4));
+    sched[kSchedNumSegments] = n_seg;
+    sched[kSchedNumActive] = n_active;
+    sched[kSchedNumValidRows] = n_valid;
+    sched[kSchedDownSplits] = splits;
+    sched[4] = 0;
+    sched[5] = 0;
+    sched[6] = 0;
+    sched[7] = 0;
+  }
+  __syncthreads();
+
+  // Pass 2: stable placement, 1024 assignments per round.
+  for (int base = 0; base < num_assign; base += kRoutingThreads) {
+    for (int i = tid; i < kRoutingWarps * B200MOE_MAX_EXPERTS; i += kRoutingThreads)
+      (&s_whist[0][0])[i] = 0;
+    __syncthreads();
+
+    const int a = base + tid;
+    int64_t e64 = -1;
+    if (a < num_assign) e64 = ids[a];
+    const bool valid = (a < num_assign) && e64 >= 0 && e64 < (int64_t)num_experts;
+    const int e = valid ? (int)e64 : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank == 0) s_whist[warp][e] = __popc(peers);
+    __syncthreads();
+
+    if (is_expert) {
+      int run = s_cursor[tid];
+#pragma unroll 8
+      for (int w = 0; w < kRoutingWarps; ++w) {
+        const int t = s_whist[w][tid];
+        s_whist[w][tid] = run;
+        run += t;
+      }
+      s_cursor[tid] = run;
+    }
+    __syncthreads();
+
+    if (valid) {
+      const int p = s_whist[warp][e] + rank;
+      reverse_mapping[a] = p;
+      permutation[p] = a;
+      if (perm_tokens) perm_tokens[p] = a / top_k;
+      if (perm_experts) perm_experts[p] = e;
+      if (perm_weights && weights) perm_weights[p] = weights[a];
+    } else if (a < num_assign) {
+      reverse_mapping[a] = -1;
+    }
+    __syncthreads();
+  }
+
+  // Rows past the valid ones exist only when some id was out of range: mark
+  // them invalid so the gather zero-fills them and nothing reads stale indices.
+  if (s_bad) {
+    for (int p = n_valid + tid; p < num_assign; p += kRoutingThreads) {
+      permutation[p] = -1;
+      if (perm_tokens) perm_tokens[p] = -1;
+      if (perm_experts) perm_experts[p] = -1;
+      if (perm_weights) perm_weights[p] = __float2bfloat16(0.0f);
+    }
+    if (tid == 0) atomicOr(status, B200MOE_STATUS_BAD_EXPERT_ID);
+  }
+}
+
+cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assign, int top_k,
+                           int num_experts, int64_t* counts, int64_t* offsets,
+                           int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
+                           int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
+                           int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
+                           int target_ctas, cudaStream_t stream) {
+  routing_kernel<<<1, kRoutingThreads, 0, stream>>>(
+      ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
+      offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
+      static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
+      target_ctas);
+  return cudaGetLastError();
+}
+
+}  // namespace b200moe

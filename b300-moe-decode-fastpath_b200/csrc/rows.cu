@@ -1,0 +1,130 @@
+// Stage 2 (gather) and stage 5 (combine): the two row-moving kernels either
+// side of the grouped GEMMs.  Both are pure HBM traffic and use 16-byte
+// accesses throughout.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kRowThreads = 256;
+
+// permuted_hidden[p, :] = hidden[permutation[p] / K, :]
+// Same contract as the reference gather (csrc/permutation_kernels.cu:25-50): a
+// row whose mapping is outside [0, A) is zero-filled.
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
+                   uint4* __restrict__ out, int num_assign, int num_tokens, int top_k,
+                   int vec_per_row) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const int64_t a = permutation[row];
+  const bool valid = a >= 0 && a < (int64_t)num_assign && (a / top_k) < (int64_t)num_tokens;
+  const uint4* src = hidden + (valid ? (size_t)(a / top_k) * vec_per_row : 0);
+  uint4* dst = out + (size_t)row * vec_per_row;
+  for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) x = __ldg(src + v);
+    dst[v] = x;
+  }
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 p;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+// out[t, :] = bf16( sum_k float(w[t,k]) * row(reverse_mapping[t*K+k]) ), where
+// row(p) = sum over the split-K slices of the down projection, slice 0 first.
+// FP32 accumulation in slot order; weights used as supplied; rows whose
+// mapping is invalid are skipped (csrc/combine_kernels.cu:39-47).  One thread
+// owns eight consecutive hidden columns.
+__global__ void __launch_bounds__(128)
+combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
+                    const __nv_bfloat16* __restrict__ weights, const float* __restrict__ partials,
+                    const int32_t* __restrict__ sched, uint4* __restrict__ out,
+                    uint4* __restrict__ expert_out, int num_assign, int top_k, int hidden,
+                    size_t slice_elems) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int token = blockIdx.x;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (col >= hidden) return;
+  const int splits = sched[kSchedDownSplits];
+
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+
+  for (int k = 0; k < top_k; ++k) {
+    const int a = token * top_k + k;
+    const int64_t row = reverse_mapping[a];
+    if (row < 0 || row >= (int64_t)num_assign) continue;
+    const float w = __bfloat162float(weights[a]);
+    const float* src = partials + (size_t)row * hidden + col;
+    float v[8];
+    {
+      const float4 lo = *reinterpret_cast<const float4*>(src);
+      const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+      v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    }
+    for (int s = 1; s < splits; ++s) {
+      const float* ps = src + (size_t)s * slice_elems;
+      const float4 lo = *reinterpret_cast<const float4*>(ps);
+      const float4 hi = *reinterpret_cast<const float4*>(ps + 4);
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+    if (expert_out) expert_out[((size_t)row * hidden + col) >> 3] = pack_bf16x8(v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[i], w, acc[i]);
+  }
+  out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
+}
+
+static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void** args,
+                                   bool pdl, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelExC(&cfg, func, args);
+}
+
+cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
+                          int num_assign, int num_tokens, int top_k, int hidden_size, bool pdl,
+                          cudaStream_t stream) {
+  int vec_per_row = hidden_size / 8;
+  const uint4* h = static_cast<const uint4*>(hidden);
+  uint4* o = static_cast<uint4*>(out);
+  void* args[] = {&h, &permutation, &o, &num_assign, &num_tokens, &top_k, &vec_per_row};
+  return launch_with_pdl(reinterpret_cast<const void*>(&gather_rows_kernel), dim3(num_assign),
+                         dim3(kRowThreads), args, pdl, stream);
+}
+
+cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
+                           const float* partials, const int32_t* sched, void* out,
+                           void* expert_out, int num_tokens, int top_k, int hidden_size,
+                           size_t slice_elems, bool pdl, cudaStream_t stream) {
+  int num_assign = num_tokens * top_k;
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weights);
+  uint4* o = static_cast<uint4*>(out);
+  uint4* eo = static_cast<uint4*>(expert_out);
+  void* args[] = {&reverse_mapping, &w, &partials, &sched, &o, &eo, &num_assign, &top_k,
+                  &hidden_size, &slice_elems};
+  const int vecs = hidden_size / 8;
+  dim3 grid(num_tokens, (vecs + 127) / 128);
+  return launch_with_pdl(reinterpret_cast<const void*>(&combine_rows_kernel), grid, dim3(128),
+                         args, pdl, stream);
+}
+
+}  // namespace b200moe

@@ -1,0 +1,192 @@
+/*
+ * b200moe.h -- C ABI of libb200moe.so: the explicitly routed SwiGLU MoE decode
+ * layer as hand-written sm_100a kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and an explicit CUDA
+ * stream (passed as void* so that C callers need no CUDA headers).  Nothing
+ * here allocates device memory, synchronises the stream or reads device memory
+ * back to the host unless the comment of the function says so.
+ *
+ * Return value convention:
+ *    0  work was enqueued on the stream
+ *   <0  B200MOE_E_* : argument/contract error found on the host, nothing launched
+ *   >0  a cudaError_t reported by the CUDA runtime or driver
+ *
+ * Conditions that can only be seen on the device (an expert id outside
+ * [0, E), a pipeline wait that ran out) never trap: they set bits in the
+ * caller-provided 32-bit status word and the offending row is dropped.
+ *
+ * Index conventions (same as the reference, csrc/moe_fastpath.h:9-12):
+ *   assignment a = token * top_k + slot          (token-major, slot-minor)
+ *   permutation[p]     = a   expert-major row -> assignment  ("permuted_to_assignment")
+ *   reverse_mapping[a] = p   assignment -> expert-major row  ("assignment_to_permuted")
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* host-side contract errors */
+#define B200MOE_E_NULL        (-1)  /* a required pointer is NULL */
+#define B200MOE_E_SHAPE       (-2)  /* T, K, E, H or I outside the supported range */
+#define B200MOE_E_ALIGN       (-3)  /* pointer not 16-byte aligned, or H/I not a multiple of 8 */
+#define B200MOE_E_SCRATCH     (-4)  /* scratch region smaller than b200moe_scratch_bytes() */
+#define B200MOE_E_DRIVER      (-5)  /* cuTensorMapEncodeTiled could not be resolved / failed */
+#define B200MOE_E_ARCH        (-6)  /* current device is not compute capability 10.0 */
+#define B200MOE_E_UNSUPPORTED (-7)  /* feature is declared but not implemented (NVFP4) */
+
+/* bits of the device status word */
+#define B200MOE_STATUS_BAD_EXPERT_ID  0x1u  /* some expert id was outside [0, E); its row was dropped */
+#define B200MOE_STATUS_PIPE_TIMEOUT   0x2u  /* a bounded mbarrier wait inside a GEMM gave up */
+#define B200MOE_STATUS_PEER_TIMEOUT   0x4u  /* a bounded wait on an expert-parallel peer flag gave up */
+
+#define B200MOE_MAX_EXPERTS   256   /* same limit as the reference, csrc/routing_kernels.cu:107 */
+
+/* flags of B200MoeArgs.flags */
+#define B200MOE_FLAG_PDL      0x1u  /* launch kernels 2..5 with programmatic dependent launch */
+
+/* ABI version of the loaded library (== B200MOE_ABI_VERSION it was built with). */
+int b200moe_abi_version(void);
+
+/*
+ * Writes a NUL-terminated JSON object describing the build into `json`
+ * (at most `cap` bytes) and returns the length that was needed.  Keys mirror
+ * the reference's build_info() dict (csrc/bindings.cpp:63-85):
+ * compiled_architecture ("sm_100a"), uses_fallback (false),
+ * bf16_grouped_gemm_provider, cuda_runtime_version, nvfp4_compiled (false), ...
+ */
+int b200moe_build_info(char* json, size_t cap);
+
+/* Human-readable text for a negative B200MOE_E_* code; cudaGetErrorString for positive ones. */
+const char* b200moe_error_string(int code);
+
+/*
+ * Bytes of private scratch the layer needs, beyond the reference's twelve
+ * public workspace buffers, for up to `max_tokens` tokens: the FP32 split-K
+ * partial rows of the down projection, the low-order halves of the SwiGLU
+ * activations, the device-built segment schedule and the status word.
+ * Replaces the hidden allocations ATen's grouped GEMM makes per call in the
+ * reference (csrc/grouped_gemm_sm103.cu:47-52).
+ */
+int b200moe_scratch_bytes(int max_tokens, int top_k, int num_experts,
+                          int hidden_size, int intermediate_size, size_t* bytes);
+
+/*
+ * Arguments of the layer.  Every stage entry point takes the same struct, so
+ * the scratch region is carved identically by all of them; each stage reads
+ * only the fields its comment names.
+ */
+typedef struct B200MoeArgs {
+  /* inputs */
+  const void*    hidden_states;      /* [T,H]     bf16 */
+  const int64_t* expert_indices;     /* [T,K]     int64 */
+  const void*    expert_weights;     /* [T,K]     bf16 */
+  const void*    gate_up_weight;     /* [E,2I,H]  bf16, gate rows first */
+  const void*    down_weight;        /* [E,H,I]   bf16 */
+  int32_t num_tokens, top_k, num_experts, hidden_size, intermediate_size;
+  int32_t rows_cap;                  /* rows of the permuted_* buffers (>= T*K) */
+  /* reference workspace buffers (fastpath/b300_moe.py:182-195) */
+  int64_t* expert_counts;            /* [E]   */
+  int64_t* expert_offsets;           /* [E+1] */
+  int32_t* expert_offsets_i32;       /* [E]   cumulative END offsets */
+  int64_t* permutation;              /* [rows_cap] */
+  int64_t* reverse_mapping;          /* [rows_cap] */
+  int64_t* permuted_token_indices;   /* [rows_cap] or NULL */
+  int64_t* permuted_expert_indices;  /* [rows_cap] or NULL */
+  void*    permuted_weights;         /* [rows_cap] bf16 or NULL */
+  void*    permuted_hidden;          /* [rows_cap,H] bf16 */
+  void*    swiglu_output;            /* [rows_cap,I] bf16 */
+  void*    expert_output;            /* [rows_cap,H] bf16 or NULL */
+  /* private scratch, b200moe_scratch_bytes() for rows_cap / top_k tokens, 256-byte aligned */
+  void*    scratch;
+  size_t   scratch_bytes;
+  /* result */
+  void*    output;                   /* [T,H] bf16 */
+  uint32_t flags;                    /* B200MOE_FLAG_* */
+} B200MoeArgs;
+
+/*
+ * Stage 1 -- routing metadata.  Replaces routing_metadata_out_cuda
+ * (csrc/routing_kernels.cu:79-139) plus the int32 offsets copy
+ * (fastpath/b300_moe.py:652-653): histogram, exclusive scan (empty experts
+ * keep equal adjacent offsets), stable expert-major permutation and its exact
+ * inverse, in one launch.  Also fills permuted_token_indices /
+ * permuted_expert_indices / permuted_weights when those pointers are non-NULL,
+ * and builds, on the device and with no host synchronisation, the segment
+ * schedule the two GEMMs consume.  Clears the status word.
+ * Reads: expert_indices, expert_weights.  Writes: the routing buffers, scratch.
+ */
+int b200moe_routing(const B200MoeArgs* args, void* stream);
+
+/*
+ * Stage 2 -- gather.  Replaces permute_out_cuda (csrc/permutation_kernels.cu:72-110):
+ * permuted_hidden[p, :] = hidden_states[permutation[p] / K, :] with 16-byte
+ * loads and stores; rows whose mapping is invalid are zero-filled exactly like
+ * the reference kernel (csrc/permutation_kernels.cu:41-48).
+ */
+int b200moe_gather(const B200MoeArgs* args, void* stream);
+
+/*
+ * Stage 3 -- grouped gate+up GEMM with SwiGLU in the epilogue.  Replaces
+ * grouped_gemm_bf16_out_cuda on the [E,2I,H] weight (csrc/grouped_gemm_sm103.cu:21-53)
+ * followed by swiglu_out_cuda (csrc/moe_fastpath.cu:24-71):
+ *   act[p, i] = silu(x_p . Wgate[e(p), i, :]) * (x_p . Wup[e(p), i, :])
+ * accumulated and activated in FP32 (tcgen05 MMA, TMEM accumulators), written
+ * as a BF16 high part into swiglu_output and a BF16 low-order remainder into
+ * the scratch region, so the down projection sees the FP32 value to ~2^-17.
+ * Must run after stage 1 on the same scratch region.
+ */
+int b200moe_gate_up_swiglu(const B200MoeArgs* args, void* stream);
+
+/*
+ * Stage 4 -- grouped down GEMM.  Replaces grouped_gemm_bf16_out_cuda on the
+ * [E,H,I] weight (csrc/grouped_gemm_sm103.cu:21-53).  Consumes the high/low
+ * activation pair and writes FP32 rows (split-K partial slices, summed in a
+ * fixed order by stage 5) into the scratch region.
+ */
+int b200moe_down(const B200MoeArgs* args, void* stream);
+
+/*
+ * Stage 5 -- combine.  Replaces combine_out_cuda (csrc/combine_kernels.cu:55-93):
+ *   output[t, :] = bf16( sum_k float(w[t,k]) * row(reverse_mapping[t*K+k]) )
+ * FP32 accumulation in slot order, weights used exactly as supplied
+ * (unnormalised, negative, zero); invalid rows are skipped like the
+ * reference kernel (csrc/combine_kernels.cu:44).  row() is the fixed-order sum
+ * of the split-K slices stage 4 wrote.  When expert_output is non-NULL the
+ * BF16-rounded expert rows are stored there too, which is what the reference
+ * keeps in its expert_output buffer.
+ */
+int b200moe_combine(const B200MoeArgs* args, void* stream);
+
+/*
+ * The whole layer: stages 1..5 enqueued back to back on `stream` by one call.
+ * Replaces _call_compiled_bf16 (fastpath/b300_moe.py:620-760).  No allocation,
+ * no synchronisation, no host read-back.
+ */
+int b200moe_forward(const B200MoeArgs* args, void* stream);
+
+/*
+ * Device address of the 32-bit status word inside a scratch region, so a
+ * caller can copy it back when it chooses to synchronise.  Replaces the
+ * device-side assert the reference uses for out-of-range ids
+ * (fastpath/reference.py:99-103), which would poison the CUDA context.
+ */
+int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status);
+
+/*
+ * NVFP4 capability probe.  Mirrors nvfp4_grouped_gemm_available_cuda
+ * (csrc/quantization_kernels.cu:7-13): always 0; BF16 is never substituted.
+ */
+int b200moe_nvfp4_available(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,178 @@
+"""GPU tests of the API contract: workspace reuse, streams, metadata, explicit failures.
+
+These replay, on the sm_100a kernels, the behaviours the reference's B300-only
+suite pins (tests/test_goal_1b_cuda.py:139-175, 213-247, 316-400).
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import moe_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(device, tokens=8, experts=16, top_k=2, hidden=64, inter=96, routing="uniform",
+          weight_kind="softmax", seed=1234):
+    from b200moe import workloads
+
+    return workloads.make_case(tokens, hidden, inter, experts, top_k, routing=routing,
+                               weight_kind=weight_kind, seed=seed, std=None, device=device)
+
+
+def test_workspace_reuse_is_bitwise_repeatable_on_a_side_stream(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    tensors = _case(cuda_device, tokens=9, routing="empty_half", weight_kind="raw")
+    workspace = B300MoEWorkspace(capacity_tokens=16, device=cuda_device)
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        first, meta1 = b300_moe_forward(*tensors, num_experts=16, top_k=2, workspace=workspace,
+                                        return_metadata=True)
+        ptrs = workspace.buffer_data_ptrs()
+        second, meta2 = b300_moe_forward(*tensors, num_experts=16, top_k=2, workspace=workspace,
+                                         return_metadata=True)
+    side.synchronize()
+    assert torch.equal(first, second)
+    assert workspace.buffer_data_ptrs() == ptrs
+    assert workspace.allocation_count == 1 and workspace.reuse_count == 1
+    assert meta1["workspace"]["reused"] is False and meta2["workspace"]["reused"] is True
+    assert workspace.last_stream == int(side.cuda_stream)
+    assert first.data_ptr() != second.data_ptr()
+    for buffer in workspace.buffers.values():
+        assert first.data_ptr() != buffer.data_ptr()
+    ref, _ = moe_oracle.routed_moe(*(t.cpu() for t in tensors), num_experts=16, top_k=2)
+    assert moe_oracle.relative_max_error(first.float().cpu(), ref) <= 2e-2
+
+
+def test_metadata_survives_reuse_from_another_stream(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    workspace = B300MoEWorkspace(device=cuda_device)
+    a = _case(cuda_device, seed=10)
+    b = _case(cuda_device, seed=20, routing="concentrated")
+    s1, s2 = torch.cuda.Stream(device=cuda_device), torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(s1):
+        _, meta_a = b300_moe_forward(*a, num_experts=16, top_k=2, workspace=workspace,
+                                     return_metadata=True)
+    with torch.cuda.stream(s2):
+        _, meta_b = b300_moe_forward(*b, num_experts=16, top_k=2, workspace=workspace,
+                                     return_metadata=True)
+    torch.cuda.synchronize(cuda_device)
+    want_a = moe_oracle.group_tokens(a[1].cpu(), 16)
+    want_b = moe_oracle.group_tokens(b[1].cpu(), 16)
+    assert meta_a["permutation"].cpu().tolist() == want_a.permutation.tolist()
+    assert meta_b["permutation"].cpu().tolist() == want_b.permutation.tolist()
+    assert meta_a["expert_offsets"].cpu().tolist() == want_a.expert_offsets.tolist()
+
+
+def test_two_streams_with_own_workspaces_run_concurrently(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    cases = [_case(cuda_device, tokens=17, seed=s, hidden=256, inter=512) for s in (1, 2)]
+    spaces = [B300MoEWorkspace(device=cuda_device) for _ in cases]
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in cases]
+    outs = []
+    torch.cuda.synchronize(cuda_device)
+    for _ in range(3):
+        outs = []
+        for case, space, stream in zip(cases, spaces, streams):
+            with torch.cuda.stream(stream):
+                outs.append(b300_moe_forward(*case, num_experts=16, top_k=2, workspace=space))
+    torch.cuda.synchronize(cuda_device)
+    for case, out in zip(cases, outs):
+        ref, _ = moe_oracle.routed_moe(*(t.cpu() for t in case), num_experts=16, top_k=2)
+        assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2
+
+
+def test_workspace_grows_and_rebinds(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    workspace = B300MoEWorkspace(capacity_tokens=4, device=cuda_device)
+    b300_moe_forward(*_case(cuda_device, tokens=3), num_experts=16, top_k=2, workspace=workspace)
+    assert (workspace.allocation_count, workspace.capacity_tokens) == (1, 4)
+    assert workspace.capacity_assignments == 8
+    b300_moe_forward(*_case(cuda_device, tokens=6), num_experts=16, top_k=2, workspace=workspace)
+    assert workspace.allocation_count == 2 and workspace.capacity_tokens >= 8
+    b300_moe_forward(*_case(cuda_device, tokens=2, top_k=1, hidden=72), num_experts=16, top_k=1,
+                     workspace=workspace)
+    assert workspace.allocation_count == 3
+    assert workspace.last_shape == (2, 16, 1, 72, 96)
+    assert workspace.private_bytes > 0 and workspace.capacity_bytes > workspace.private_bytes
+
+
+def test_single_expert_in_both_slots_known_counts(cuda_device) -> None:
+    from b200moe import b300_moe_forward
+
+    hidden, ids, weights, gate_up, down = _case(cuda_device, tokens=8)
+    ids = torch.full_like(ids, 5)
+    out, meta = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=16, top_k=2,
+                                 return_metadata=True)
+    assert meta["expert_counts"].cpu().tolist() == [0] * 5 + [16] + [0] * 10
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
+                                   down.cpu(), num_experts=16, top_k=2)
+    assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2
+
+
+def test_out_of_range_id_sets_status_and_never_traps(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    hidden, ids, weights, gate_up, down = _case(cuda_device, tokens=4)
+    bad = ids.clone()
+    bad[1, 0] = 16
+    workspace = B300MoEWorkspace(device=cuda_device)
+    with pytest.raises(ValueError, match="out-of-range"):
+        b300_moe_forward(hidden, bad, weights, gate_up, down, num_experts=16, top_k=2,
+                         workspace=workspace, check_status=True)
+    # the context is intact and the dropped row contributed nothing
+    out, meta = b300_moe_forward(hidden, bad, weights, gate_up, down, num_experts=16, top_k=2,
+                                 workspace=workspace, return_metadata=True)
+    assert int(meta["reverse_mapping"][2]) == -1
+    assert int(meta["expert_counts"].sum()) == 7
+    keep = weights.clone()
+    keep[1, 0] = 0
+    good = ids.clone()
+    good[1, 0] = 0
+    want = b300_moe_forward(hidden, good, keep, gate_up, down, num_experts=16, top_k=2)
+    assert moe_oracle.relative_max_error(out.float().cpu(), want.float().cpu()) <= 2e-2
+    clean = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=16, top_k=2,
+                             workspace=workspace, check_status=True)
+    assert clean.shape == hidden.shape
+
+
+def test_explicit_failures_on_device(cuda_device) -> None:
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    tensors = _case(cuda_device)
+    with pytest.raises(RuntimeError, match="NVFP4|nvfp4"):
+        b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="cutlass_nvfp4")
+    with pytest.raises(RuntimeError, match="oracle"):
+        b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="torch")
+    odd = _case(cuda_device, hidden=30 * 2 + 2, inter=46 * 2 + 2)  # 62, 94: not multiples of 8
+    workspace = B300MoEWorkspace(device=cuda_device)
+    with pytest.raises(ValueError, match="divisible by 8"):
+        b300_moe_forward(*odd, num_experts=16, top_k=2, workspace=workspace)
+    assert workspace.allocation_count == 0
+    halves = tuple(t.half() if t.is_floating_point() else t for t in tensors)
+    with pytest.raises(TypeError, match="requires bfloat16"):
+        b300_moe_forward(*halves, num_experts=16, top_k=2)
+
+
+def test_tokens_beyond_decode_sizes_stay_correct(cuda_device) -> None:
+    """T is unbounded in the contract (reference.py:74-75): 300 tokens x 8 slots = 2400
+    assignments exercises the multi-round routing kernel and many segments."""
+
+    from b200moe import b300_moe_forward
+
+    tensors = _case(cuda_device, tokens=300, top_k=8, experts=16, hidden=64, inter=128,
+                    routing="zipf")
+    out, meta = b300_moe_forward(*tensors, num_experts=16, top_k=8, return_metadata=True,
+                                 check_status=True)
+    want = moe_oracle.group_tokens(tensors[1].cpu(), 16)
+    assert meta["permutation"].cpu().tolist() == want.permutation.tolist()
+    assert meta["reverse_mapping"].cpu().tolist() == want.reverse_mapping.tolist()
+    ref, _ = moe_oracle.routed_moe(*(t.cpu() for t in tensors), num_experts=16, top_k=8)
+    assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2

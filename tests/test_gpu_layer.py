@@ -1,0 +1,141 @@
+"""GPU parity tests: the sm_100a kernels, called through the C ABI, against the oracle.
+
+Bars: routing tensors bit-exact; output within ``2e-2 x rms(reference)`` of the
+FP32 reference on identical inputs (max-abs error), the tolerance the layer is
+specified to.  Every case also prints the BF16 rounding floor of the reference,
+because the output dtype alone costs most of that budget.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES
+from oracle import moe_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOLERANCE = 2e-2  # max|y - y_ref| <= TOLERANCE * rms(y_ref)
+
+
+def _forward(case_inputs, num_experts, top_k, device, **kwargs):
+    from b200moe import b300_moe_forward
+
+    tensors = tuple(t.to(device) for t in case_inputs)
+    return b300_moe_forward(
+        *tensors, num_experts=num_experts, top_k=top_k, backend="cutlass_bf16", **kwargs
+    )
+
+
+def _check_routing(metadata, routing) -> None:
+    for key in ("permutation", "reverse_mapping", "expert_counts", "expert_offsets"):
+        got = metadata[key].cpu().numpy()
+        want = routing[key] if isinstance(routing, dict) else getattr(routing, key)
+        want = want.numpy() if isinstance(want, torch.Tensor) else want
+        assert got.dtype == np.int64
+        np.testing.assert_array_equal(got, want, err_msg=key)
+
+
+def _check_output(out: torch.Tensor, ref: torch.Tensor, label: str) -> None:
+    assert out.dtype == torch.bfloat16 and out.is_contiguous()
+    err = moe_oracle.relative_max_error(out.float().cpu(), ref)
+    floor = moe_oracle.bf16_floor(ref)
+    print(f"{label}: err/rms={err:.5f} floor={floor:.5f}")
+    assert err <= TOLERANCE, f"{label}: {err:.5f} > {TOLERANCE} (floor {floor:.5f})"
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES, ids=lambda c: c.label)
+def test_golden_cases_match_reference(case, cuda_device) -> None:
+    out, metadata = _forward(
+        case.inputs(), case.num_experts, case.top_k, cuda_device,
+        return_metadata=True, check_status=True,
+    )
+    _check_routing(metadata, case.routing)
+    _check_output(out, case.output_fp32, case.label)
+    assert metadata["used_fallback"] is False
+    assert metadata["architecture"] == "sm_100a"
+    assert metadata["backend"] == "cutlass_bf16"
+
+
+@pytest.mark.parametrize("use_pdl", [False, True])
+@pytest.mark.parametrize("case", GOLDEN_CASES[::3], ids=lambda c: c.label)
+def test_pdl_and_plain_launch_agree_bitwise(case, use_pdl, cuda_device) -> None:
+    a = _forward(case.inputs(), case.num_experts, case.top_k, cuda_device, use_pdl=use_pdl)
+    b = _forward(case.inputs(), case.num_experts, case.top_k, cuda_device, use_pdl=not use_pdl)
+    assert torch.equal(a, b)
+
+
+CONFIG_CASES = [
+    # (label, T, H, I, E, K, routing, weight_kind, std)
+    ("cpu_small_bf16", 16, 256, 512, 8, 2, "uniform", "softmax", None),
+    ("mixtral_T1", 1, 4096, 14336, 8, 2, "uniform", "softmax", 0.02),
+    ("mixtral_T8", 8, 4096, 14336, 8, 2, "uniform", "softmax", 0.02),
+    ("mixtral_T64", 64, 4096, 14336, 8, 2, "uniform", "softmax", 0.02),
+    ("irregular_T1_K1", 1, 2880, 2880, 32, 1, "uniform", "softmax", 0.02),
+    ("irregular_T3_K2_empty", 3, 2880, 2880, 32, 2, "empty_half", "softmax", 0.02),
+    ("irregular_T17_K4_conc", 17, 2880, 2880, 32, 4, "concentrated", "softmax", 0.02),
+    ("irregular_T63_K8_conc", 63, 2880, 2880, 32, 8, "concentrated", "softmax", 0.02),
+    ("irregular_T63_K8_dup", 63, 2880, 2880, 32, 8, "duplicates", "raw", 0.02),
+    ("deepseek_like_E64_T8", 8, 7168, 2048, 64, 8, "uniform", "softmax", 0.02),
+    ("deepseek_like_E64_T64_hot", 64, 7168, 2048, 64, 8, "hotspot", "softmax", 0.02),
+    ("wide_like_E16_T64_zipf", 64, 4096, 14336, 16, 8, "zipf", "raw", 0.02),
+]
+
+
+@pytest.mark.parametrize("spec", CONFIG_CASES, ids=lambda s: s[0])
+def test_benchmark_shapes_match_fp32_oracle(spec, cuda_device) -> None:
+    """Benchmark-configuration shapes (expert count cut where the CPU oracle needs it).
+
+    Weights are drawn on the GPU and copied back, so the oracle sees the same bits.
+    """
+
+    from b200moe import workloads
+
+    label, T, H, I, E, K, routing, weight_kind, std = spec
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing=routing, weight_kind=weight_kind, std=std, device=cuda_device
+    )
+    out, metadata = _forward(
+        (hidden, ids, weights, gate_up, down), E, K, cuda_device,
+        return_metadata=True, check_status=True,
+    )
+    ref, ref_routing = moe_oracle.routed_moe(
+        hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(), down.cpu(),
+        num_experts=E, top_k=K,
+    )
+    _check_routing(metadata, ref_routing)
+    _check_output(out, ref, label)
+
+
+def test_full_size_linearity_in_routing_weights(cuda_device) -> None:
+    """Size-independent property at a full configuration: the output is linear in the
+    routing weights (exactly for a power-of-two scale), and zero weights give zeros."""
+
+    from b200moe import workloads
+
+    T, H, I, E, K = 32, 4096, 14336, 8, 2
+    hidden, ids, weights, gate_up, down = workloads.make_case(T, H, I, E, K, device=cuda_device)
+    base = _forward((hidden, ids, weights, gate_up, down), E, K, cuda_device)
+    scaled = _forward((hidden, ids, weights * -2, gate_up, down), E, K, cuda_device)
+    assert torch.equal(scaled.float(), base.float() * -2)
+    zero = _forward((hidden, ids, torch.zeros_like(weights), gate_up, down), E, K, cuda_device)
+    assert float(zero.float().abs().max()) == 0.0
+
+
+def test_full_size_token_permutation_equivariance(cuda_device) -> None:
+    """Reordering the tokens reorders the output rows and changes nothing else:
+    every accumulation order inside the kernels is independent of the token position."""
+
+    from b200moe import workloads
+
+    T, H, I, E, K = 16, 7168, 2048, 32, 8
+    hidden, ids, weights, gate_up, down = workloads.make_case(T, H, I, E, K, device=cuda_device)
+    base = _forward((hidden, ids, weights, gate_up, down), E, K, cuda_device)
+    order = torch.randperm(T, generator=torch.Generator().manual_seed(5)).to(cuda_device)
+    moved = _forward(
+        (hidden[order].contiguous(), ids[order].contiguous(), weights[order].contiguous(),
+         gate_up, down), E, K, cuda_device,
+    )
+    assert torch.equal(moved, base[order])
