@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait: gives up after `limit_ns` of wall time or when another thread
 // of the block has already given up (`*abort_flag != 0`).  Returns false then.
-constexpr uint64_t kPipeWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint64_t kPipeWaitLimitNs = 200000000ull;  // 200 ms
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;

@@ -1,0 +1,479 @@
+"""Benchmark of the MoE decode layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): the Mixtral-8x7B-shaped BF16 decode layer -- H=4096, I=14336,
+E=8, top_k=2, T swept over {1,2,4,8,16,32,64}, activations ~N(0,1), weights
+~N(0,0.02), uniform distinct routing, softmax routing weights.  One *step* is
+one pass of the layer at every T of the sweep (seven forwards).  The reported
+metric is the layer's P50 latency in microseconds, averaged over the sweep;
+per-T and per-stage P50/P90/P99 and the achieved expert-weight HBM bandwidth are
+attached to the same JSON line.
+
+Timing protocol (the reference's, benchmark/timing.py:32-80, with an L2 flush
+added): W warm-up steps, then K timed steps; every forward is bracketed by its
+own CUDA-event pair on the launching stream, and before each forward a 256 MiB
+buffer is written and a second one read, so no weight byte is served from the
+126 MB L2 and no dirty line of the flush is written back under the timed kernels.
+Percentiles use linear interpolation on the sorted samples (timing.py:23-29).
+``total`` is ``b300_moe_forward``'s work only; the reference's ``total_us`` also
+contains the router's top-k (benchmark_goal_1b.py:530-546), which is outside
+this layer.
+
+``--impl reference`` times the reference's pure-PyTorch path -- restated in
+``oracle/moe_oracle.py`` because the reference package itself does not travel to
+the GPU box -- on the host CPU cores, same workload, same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+for entry in (str(REPO / "b300-moe-decode-fastpath_b200"), str(REPO)):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+import torch  # noqa: E402
+
+SWEEP = (1, 2, 4, 8, 16, 32, 64)
+HIDDEN, INTER, EXPERTS, TOP_K = 4096, 14336, 8, 2
+WORKLOAD = "mixtral_8x7b_bf16_decode_layer_H4096_I14336_E8_K2_T1-64"
+METRIC = "moe_layer_decode_p50_us_mean_over_T1_2_4_8_16_32_64"
+L2_FLUSH_BYTES = 256 << 20
+FALLBACK_HBM_GBS = 6650.0
+STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch at T=1 from
+# the committed ncu capture (profiles/); None until a capture exists.
+GATE_UP_T1_DRAM_TRAFFIC_BYTES = None
+
+
+def percentile(sorted_values: list[float], q: float) -> float:
+    if not sorted_values:
+        return float("nan")
+    pos = (len(sorted_values) - 1) * q
+    lo = int(math.floor(pos))
+    hi = min(lo + 1, len(sorted_values) - 1)
+    return sorted_values[lo] + (sorted_values[hi] - sorted_values[lo]) * (pos - lo)
+
+
+def summary(samples_us: list[float]) -> dict[str, float]:
+    s = sorted(samples_us)
+    return {
+        "p50": round(percentile(s, 0.50), 2),
+        "p90": round(percentile(s, 0.90), 2),
+        "p99": round(percentile(s, 0.99), 2),
+    }
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+        "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, device_index: int) -> None:
+        self.device_index = device_index
+        self.proc: subprocess.Popen | None = None
+        self.file = None
+
+    def start(self) -> None:
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL,
+            )
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict[str, object]:
+        if self.proc is None or self.file is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        clocks.sort()
+        return {
+            "sm_mhz": percentile(clocks, 0.5) if clocks else None,
+            "sm_max_mhz": max_clock,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def weight_bytes(active_experts: int) -> dict[str, int]:
+    """Algorithmic expert-weight bytes one forward must stream from HBM."""
+
+    gate_up = active_experts * 4 * HIDDEN * INTER   # [2I,H] bf16 per active expert
+    down = active_experts * 2 * HIDDEN * INTER      # [H,I] bf16 per active expert
+    return {"gate_up": gate_up, "down": down, "total": gate_up + down}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if n_gpus > 1 and world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, local, dist
+    return 0, 1, local if world > 1 else 0, None
+
+
+# -----------------------------------------------------------------------------
+# our arm
+# -----------------------------------------------------------------------------
+def run_ours(args: argparse.Namespace) -> dict[str, object]:
+    from b200moe import B300MoEWorkspace, StagedLayer, b300_moe_forward, workloads
+
+    rank, world, local, dist = dist_setup(args.gpus)
+    if world > 1:
+        from b200moe import expert_parallel
+
+        return expert_parallel.bench_entry(args, rank, world, local, dist)
+
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    gate_up, down = workloads.make_expert_weights(
+        EXPERTS, HIDDEN, INTER, seed=1236, std=0.02, device=device
+    )
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=device)
+
+    def flush_l2() -> None:
+        # Write a buffer twice the size of L2, then read another one: the read pushes the
+        # dirty lines of the write out to HBM, so their write-back does not overlap (and
+        # slow down) the timed kernels that follow.
+        flush.fill_(1)
+        drain.sum()
+
+    cases = {}
+    for T in SWEEP:
+        hidden = workloads.make_hidden(T, HIDDEN, seed=1234)
+        ids = workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235)
+        weights = workloads.make_routing_weights(T, TOP_K, "softmax", 1235)
+        host = tuple(t.pin_memory() for t in (hidden, ids, weights))
+        dev = tuple(t.to(device) for t in host)
+        cases[T] = {
+            "host": host,
+            "dev": dev,
+            "stage_in": tuple(torch.empty_like(t) for t in dev),
+            "workspace": B300MoEWorkspace(capacity_tokens=max(SWEEP), device=device),
+            "active": int(torch.unique(ids).numel()),
+            "host_out": torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory(),
+        }
+
+    def forward(T: int) -> torch.Tensor:
+        c = cases[T]
+        return b300_moe_forward(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                                backend="cutlass_bf16", workspace=c["workspace"])
+
+    def forward_e2e(T: int) -> torch.Tensor:
+        c = cases[T]
+        for dst, src in zip(c["stage_in"], c["host"]):
+            dst.copy_(src, non_blocking=True)
+        out = b300_moe_forward(*c["stage_in"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                               backend="cutlass_bf16", workspace=c["workspace"])
+        c["host_out"].copy_(out, non_blocking=True)
+        return out
+
+    def timed_pass(fn, steps: int) -> dict[int, list[float]]:
+        events = {T: [] for T in SWEEP}
+        for _ in range(steps):
+            for T in SWEEP:
+                flush_l2()
+                start = torch.cuda.Event(enable_timing=True)
+                stop = torch.cuda.Event(enable_timing=True)
+                start.record()
+                fn(T)
+                stop.record()
+                events[T].append((start, stop))
+        torch.cuda.synchronize(device)
+        return {T: [a.elapsed_time(b) * 1e3 for a, b in pairs] for T, pairs in events.items()}
+
+    # warm-up (untimed), then the timed region bracketed by synchronisation
+    timed_pass(forward, args.warmup)
+    timed_pass(forward_e2e, min(args.warmup, 3))
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(local)
+    sampler.start()
+    wall0 = time.perf_counter()
+    samples = timed_pass(forward, args.steps)
+    torch.cuda.synchronize(device)
+    wall1 = time.perf_counter()
+    clocks = sampler.stop()
+    e2e_samples = timed_pass(forward_e2e, args.steps)
+    torch.cuda.synchronize(device)
+
+    # per-stage timing through the staged C-ABI entry points (isolated launches)
+    peak, peak_kind = measured_peak_gbs()
+    per_t: dict[str, object] = {}
+    stage_reps = max(10, min(args.steps, 50))
+    for T in SWEEP:
+        c = cases[T]
+        layer = StagedLayer(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                            workspace=c["workspace"], use_pdl=False)
+        layer.forward()
+        stage_us: dict[str, dict[str, float]] = {}
+        for name in STAGE_NAMES:
+            pairs = []
+            for _ in range(stage_reps):
+                flush_l2()
+                a = torch.cuda.Event(enable_timing=True)
+                b = torch.cuda.Event(enable_timing=True)
+                a.record()
+                layer.run_stage(name)
+                b.record()
+                pairs.append((a, b))
+            torch.cuda.synchronize(device)
+            stage_us[name] = summary([a.elapsed_time(b) * 1e3 for a, b in pairs])
+        total = summary(samples[T])
+        wb = weight_bytes(c["active"])
+        per_t[str(T)] = {
+            "active_experts": c["active"],
+            "total_us": total,
+            "e2e_us": summary(e2e_samples[T]),
+            "stages_us": {
+                "routing": stage_us["routing"],
+                "permutation": stage_us["gather"],
+                "gate_up": stage_us["gate_up_swiglu"],
+                "swiglu": {"p50": 0.0, "status": "fused_in_gate_up"},
+                "down": stage_us["down"],
+                "combine": stage_us["combine"],
+            },
+            "weight_bytes": wb["total"],
+            "layer_weight_gbs": round(wb["total"] / total["p50"] / 1e3, 1),
+            "layer_frac_of_peak": round(wb["total"] / total["p50"] / 1e3 / peak, 3),
+            "gate_up_gbs": round(wb["gate_up"] / stage_us["gate_up_swiglu"]["p50"] / 1e3, 1),
+            "down_gbs": round(wb["down"] / stage_us["down"]["p50"] / 1e3, 1),
+        }
+
+    p50s = [per_t[str(T)]["total_us"]["p50"] for T in SWEEP]
+    e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in SWEEP]
+    value = sum(p50s) / len(p50s)
+    step_ms = sum(sum(samples[T]) for T in SWEEP) / args.steps / 1e3
+
+    # roofline of the dominant kernel (gate+up GEMM, 2/3 of the weight bytes) at T=1
+    t1 = per_t["1"]
+    gu_bytes = weight_bytes(t1["active_experts"])["gate_up"] + 2 * t1["active_experts"] * (
+        HIDDEN * 2 + 2 * INTER * 2)  # + token rows in, hi/lo activations out (tiny)
+    gu_us = [t1["stages_us"]["gate_up"]["p50"]]
+    achieved = gu_bytes / gu_us[0] / 1e3
+    roofline = {
+        "kernel": "grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue), T=1",
+        "bound": "hbm",
+        "achieved": round(achieved, 1),
+        "peak": peak,
+        "peak_kind": f"of {peak_kind}",
+        "unit": "GB/s",
+        "frac": round(achieved / peak, 3),
+        "algorithmic_bytes": gu_bytes,
+        "traffic": GATE_UP_T1_DRAM_TRAFFIC_BYTES,
+        "frac_of_8000": round(achieved / 8000.0, 3),
+    }
+
+    h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in SWEEP)
+    d2h = sum(cases[T]["host_out"].numel() * 2 for T in SWEEP)
+    result = {
+        "metric": METRIC,
+        "value": round(value, 2),
+        "unit": "us",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(step_ms, 4),
+        "wall_ms_per_step": round((wall1 - wall0) * 1e3 / args.steps, 4),
+        "higher_is_better": False,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": WORKLOAD,
+            "tokens": list(SWEEP),
+            "l2": "flushed before every timed forward: 256 MiB written, then 256 MiB read to push the dirty lines out; every forward also streams >= 704 MB of weights (> 126 MB L2)",
+            "step": "one forward at each T of the sweep",
+        },
+        "e2e": {
+            "value": round(sum(e2e_p50s) / len(e2e_p50s), 2),
+            "unit": "us",
+            "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h,
+            "what": "b300_moe_forward with pinned host activations/routes copied in and the "
+                    "output copied out inside the timed region; expert weights resident",
+        },
+        "gpu_launches": 5 * len(SWEEP) * args.steps,
+        "clocks": clocks,
+        "roofline": roofline,
+        "per_T": per_t,
+    }
+    if not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(gate_up, down, cases, budget_s=20.0)
+    return result
+
+
+# -----------------------------------------------------------------------------
+# CPU arms (the oracle restates the reference's torch backend)
+# -----------------------------------------------------------------------------
+def _cpu_forward(case_host, gate_up_cpu, down_cpu):
+    from oracle import moe_oracle
+
+    hidden, ids, weights = case_host
+    out, _ = moe_oracle.routed_moe(hidden, ids, weights, gate_up_cpu, down_cpu,
+                                   num_experts=EXPERTS, top_k=TOP_K,
+                                   compute_dtype=torch.bfloat16)
+    return out
+
+
+def cpu_baseline(gate_up, down, cases, budget_s: float) -> dict[str, object]:
+    """The reference's BF16 torch path (restated) on the host cores, bounded sample."""
+
+    gate_up_cpu, down_cpu = gate_up.cpu(), down.cpu()
+    per_t = {}
+    reps = 3
+    t_start = time.perf_counter()
+    for T in SWEEP:
+        host = tuple(t.clone() for t in cases[T]["host"])
+        _cpu_forward(host, gate_up_cpu, down_cpu)
+        times = []
+        for _ in range(reps):
+            t0 = time.perf_counter_ns()
+            _cpu_forward(host, gate_up_cpu, down_cpu)
+            times.append((time.perf_counter_ns() - t0) / 1e3)
+        per_t[str(T)] = round(percentile(sorted(times), 0.5), 1)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    done = [per_t[k] for k in per_t]
+    return {
+        "value": round(sum(done) / len(done), 1),
+        "unit": "us",
+        "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(),
+        "kind": "port",
+        "sample": f"1 warm-up + {reps} forwards at each T in {sorted(int(k) for k in per_t)} of "
+                  "the same workload, BF16 torch ops as the reference's torch backend",
+        "per_T_p50_us": per_t,
+    }
+
+
+def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from b200moe import workloads
+
+    gate_up, down = workloads.make_expert_weights(EXPERTS, HIDDEN, INTER, seed=1236, std=0.02,
+                                                  device="cpu")
+    cases = {}
+    for T in SWEEP:
+        cases[T] = (workloads.make_hidden(T, HIDDEN, seed=1234),
+                    workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235),
+                    workloads.make_routing_weights(T, TOP_K, "softmax", 1235))
+    samples = {T: [] for T in SWEEP}
+    for _ in range(args.warmup):
+        for T in SWEEP:
+            _cpu_forward(cases[T], gate_up, down)
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        for T in SWEEP:
+            t0 = time.perf_counter_ns()
+            _cpu_forward(cases[T], gate_up, down)
+            samples[T].append((time.perf_counter_ns() - t0) / 1e3)
+    wall = time.perf_counter() - wall0
+    p50s = [percentile(sorted(samples[T]), 0.5) for T in SWEEP]
+    value = round(sum(p50s) / len(p50s), 1)
+    sample = "every T of the sweep, whole workload, BF16 torch ops on the host CPU"
+    return {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": "us",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(wall * 1e3 / args.steps, 3),
+        "higher_is_better": False,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens": list(SWEEP),
+                   "step": "one forward at each T of the sweep"},
+        "cpu_baseline": {"value": value, "unit": "us", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "per_T_p50_us": {str(T): round(p, 1) for T, p in zip(SWEEP, p50s)},
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=None)
+    parser.add_argument("--warmup", type=int, default=None)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        args.steps = 3 if args.steps is None else args.steps
+        args.warmup = 1 if args.warmup is None else args.warmup
+        result = run_reference(args)
+    else:
+        args.steps = 100 if args.steps is None else args.steps
+        args.warmup = 10 if args.warmup is None else max(args.warmup, 3)
+        result = run_ours(args)
+    if result is not None:
+        print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -175,4 +175,9 @@ def test_tokens_beyond_decode_sizes_stay_correct(cuda_device) -> None:
     assert meta["permutation"].cpu().tolist() == want.permutation.tolist()
     assert meta["reverse_mapping"].cpu().tolist() == want.reverse_mapping.tolist()
     ref, _ = moe_oracle.routed_moe(*(t.cpu() for t in tensors), num_experts=16, top_k=8)
-    assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2
+    # The 2e-2 bar is stated for T <= 64.  Over 300 x 64 outputs the largest |y| / rms grows,
+    # and rounding the exact result to BF16 alone can exceed it; the kernels must then sit
+    # on that floor.
+    err = moe_oracle.relative_max_error(out.float().cpu(), ref)
+    floor = moe_oracle.bf16_floor(ref)
+    assert err <= max(2e-2, 1.03 * floor), (err, floor)
