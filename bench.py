@@ -180,6 +180,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
 
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    sweep = tuple(args.only_tokens) if args.only_tokens else SWEEP
     gate_up, down = workloads.make_expert_weights(
         EXPERTS, HIDDEN, INTER, seed=1236, std=0.02, device=device
     )
@@ -194,7 +195,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         drain.sum()
 
     cases = {}
-    for T in SWEEP:
+    for T in sweep:
         hidden = workloads.make_hidden(T, HIDDEN, seed=1234)
         ids = workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235)
         weights = workloads.make_routing_weights(T, TOP_K, "softmax", 1235)
@@ -204,7 +205,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "host": host,
             "dev": dev,
             "stage_in": tuple(torch.empty_like(t) for t in dev),
-            "workspace": B300MoEWorkspace(capacity_tokens=max(SWEEP), device=device),
+            "workspace": B300MoEWorkspace(capacity_tokens=max(sweep), device=device),
             "active": int(torch.unique(ids).numel()),
             "host_out": torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory(),
         }
@@ -224,9 +225,9 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         return out
 
     def timed_pass(fn, steps: int) -> dict[int, list[float]]:
-        events = {T: [] for T in SWEEP}
+        events = {T: [] for T in sweep}
         for _ in range(steps):
-            for T in SWEEP:
+            for T in sweep:
                 flush_l2()
                 start = torch.cuda.Event(enable_timing=True)
                 stop = torch.cuda.Event(enable_timing=True)
@@ -255,7 +256,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     peak, peak_kind = measured_peak_gbs()
     per_t: dict[str, object] = {}
     stage_reps = max(10, min(args.steps, 50))
-    for T in SWEEP:
+    for T in sweep:
         c = cases[T]
         layer = StagedLayer(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
                             workspace=c["workspace"], use_pdl=False)
@@ -294,19 +295,19 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "down_gbs": round(wb["down"] / stage_us["down"]["p50"] / 1e3, 1),
         }
 
-    p50s = [per_t[str(T)]["total_us"]["p50"] for T in SWEEP]
-    e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in SWEEP]
+    p50s = [per_t[str(T)]["total_us"]["p50"] for T in sweep]
+    e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in sweep]
     value = sum(p50s) / len(p50s)
-    step_ms = sum(sum(samples[T]) for T in SWEEP) / args.steps / 1e3
+    step_ms = sum(sum(samples[T]) for T in sweep) / args.steps / 1e3
 
     # roofline of the dominant kernel (gate+up GEMM, 2/3 of the weight bytes) at T=1
-    t1 = per_t["1"]
+    t1 = per_t[str(sweep[0])]
     gu_bytes = weight_bytes(t1["active_experts"])["gate_up"] + 2 * t1["active_experts"] * (
         HIDDEN * 2 + 2 * INTER * 2)  # + token rows in, hi/lo activations out (tiny)
     gu_us = [t1["stages_us"]["gate_up"]["p50"]]
     achieved = gu_bytes / gu_us[0] / 1e3
     roofline = {
-        "kernel": "grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue), T=1",
+        "kernel": f"grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue), T={sweep[0]}",
         "bound": "hbm",
         "achieved": round(achieved, 1),
         "peak": peak,
@@ -318,8 +319,8 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "frac_of_8000": round(achieved / 8000.0, 3),
     }
 
-    h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in SWEEP)
-    d2h = sum(cases[T]["host_out"].numel() * 2 for T in SWEEP)
+    h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in sweep)
+    d2h = sum(cases[T]["host_out"].numel() * 2 for T in sweep)
     result = {
         "metric": METRIC,
         "value": round(value, 2),
@@ -336,7 +337,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "data": "synthetic",
         "config": {
             "workload": WORKLOAD,
-            "tokens": list(SWEEP),
+            "tokens": list(sweep),
             "l2": "flushed before every timed forward: 256 MiB written, then 256 MiB read to push the dirty lines out; every forward also streams >= 704 MB of weights (> 126 MB L2)",
             "step": "one forward at each T of the sweep",
         },
@@ -348,7 +349,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "what": "b300_moe_forward with pinned host activations/routes copied in and the "
                     "output copied out inside the timed region; expert weights resident",
         },
-        "gpu_launches": 5 * len(SWEEP) * args.steps,
+        "gpu_launches": 5 * len(sweep) * args.steps,
         "clocks": clocks,
         "roofline": roofline,
         "per_T": per_t,
@@ -378,7 +379,7 @@ def cpu_baseline(gate_up, down, cases, budget_s: float) -> dict[str, object]:
     per_t = {}
     reps = 3
     t_start = time.perf_counter()
-    for T in SWEEP:
+    for T in cases:
         host = tuple(t.clone() for t in cases[T]["host"])
         _cpu_forward(host, gate_up_cpu, down_cpu)
         times = []
@@ -461,6 +462,8 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
+                        help="restrict the sweep (profiling runs); the default is the full sweep")
     args = parser.parse_args()
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
