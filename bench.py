@@ -53,7 +53,7 @@ FALLBACK_HBM_GBS = 6650.0
 STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch at T=1 from
 # the committed ncu capture (profiles/); None until a capture exists.
-GATE_UP_T1_DRAM_TRAFFIC_BYTES = None
+GATE_UP_T1_DRAM_TRAFFIC_BYTES = 476_054_016  # 469.82 MB read + 6.24 MB written
 
 
 def percentile(sorted_values: list[float], q: float) -> float:
@@ -185,7 +185,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         EXPERTS, HIDDEN, INTER, seed=1236, std=0.02, device=device
     )
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
-    drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=device)
+    drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=device)
 
     def flush_l2() -> None:
         # Write a buffer twice the size of L2, then read another one: the read pushes the
