@@ -24,12 +24,15 @@ STATUS_PEER_TIMEOUT = 0x4
 
 FLAG_PDL = 0x1
 
+STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
+
 EXPORTS = (
     "b200moe_abi_version",
     "b200moe_build_info",
     "b200moe_error_string",
     "b200moe_scratch_bytes",
     "b200moe_routing",
+    "b200moe_routing_static",
     "b200moe_gather",
     "b200moe_gate_up_swiglu",
     "b200moe_down",
@@ -96,6 +99,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200moe_scratch_bytes.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(ctypes.c_size_t)]
     for name in (
         "b200moe_routing",
+        "b200moe_routing_static",
         "b200moe_gather",
         "b200moe_gate_up_swiglu",
         "b200moe_down",

@@ -19,6 +19,12 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, cudaStream_t stream);
+cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int num_assign,
+                                  int top_k, int num_experts, int64_t* counts, int64_t* offsets,
+                                  int64_t* reverse_mapping, int64_t* permutation,
+                                  int32_t* offsets_i32, int64_t* perm_tokens,
+                                  int64_t* perm_experts, void* perm_weights, int down_tiles,
+                                  int down_kblocks, int target_ctas, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
                           int num_assign, int num_tokens, int top_k, int hidden_size, bool pdl,
                           cudaStream_t stream);
@@ -307,6 +313,8 @@ const char* b200moe_error_string(int code) {
     case B200MOE_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
     case B200MOE_E_ARCH: return "device is not compute capability 10.0 (sm_100a)";
     case B200MOE_E_UNSUPPORTED: return "not implemented (NVFP4 is never substituted by BF16)";
+    case B200MOE_E_LIMIT:
+      return "T * top_k exceeds the 4096 assignments the static routing scratch is sized for";
     default: break;
   }
   if (code > 0) return cudaGetErrorString((cudaError_t)code);
@@ -335,6 +343,27 @@ int b200moe_routing(const B200MoeArgs* a, void* stream) {
   Ctx c;
   int rc = prepare(a, stream, &c);
   return rc ? rc : stage_routing(a, c);
+}
+
+int b200moe_routing_static(const B200MoeArgs* a, void* stream) {
+  if (!a) return B200MOE_E_NULL;
+  if (!a->expert_indices || !a->expert_counts || !a->expert_offsets || !a->expert_offsets_i32 ||
+      !a->permutation || !a->reverse_mapping)
+    return B200MOE_E_NULL;
+  int rc = check_shape(a->num_tokens, a->top_k, a->num_experts, a->hidden_size,
+                       a->intermediate_size);
+  if (rc) return rc;
+  const long long assignments = (long long)a->num_tokens * a->top_k;
+  if (assignments > B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS) return B200MOE_E_LIMIT;
+  DeviceInfo dev;
+  rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_routing_static(
+      a->expert_indices, a->expert_weights, (int)assignments, a->top_k, a->num_experts,
+      a->expert_counts, a->expert_offsets, a->reverse_mapping, a->permutation,
+      a->expert_offsets_i32, a->permuted_token_indices, a->permuted_expert_indices,
+      a->permuted_weights, tiles128(a->hidden_size), (a->intermediate_size + 63) / 64,
+      2 * dev.sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_gather(const B200MoeArgs* a, void* stream) {

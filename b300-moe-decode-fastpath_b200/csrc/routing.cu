@@ -14,6 +14,8 @@
 // ids in its warp is the number of lower lanes with the same id, and warps are
 // ordered by a per-expert running cursor.  Rows of one expert therefore keep
 // increasing assignment ids, which is torch.argsort(stable=True).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -193,6 +195,73 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
       target_ctas);
   return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Routing for callers that must not allocate.
+//
+// The routing kernel needs a few KB of device scratch (status word + segment
+// schedule).  Hosts that gave all device memory to their own arena, or that sit
+// behind a plugin interface with a "no allocation after initialisation" rule,
+// cannot supply one with cudaMalloc.  For them the
+// scratch lives in this translation unit, inside the loaded module: every GPU
+// that loads the library holds kStaticRoutingScratchBytes until the process ends.
+//
+// `g_static_routing_scratch` is a device symbol.  In host code its name is only a
+// stand-in, so the device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+// ---------------------------------------------------------------------------
+constexpr int kStaticRoutingMaxAssignments = B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS;
+constexpr size_t kStaticRoutingScratchBytes = 8192;
+static_assert(kStatusBytes + sizeof(int32_t) * (kSchedHeaderWords +
+                                                (size_t)kSchedSegWords *
+                                                    (B200MOE_MAX_EXPERTS +
+                                                     kStaticRoutingMaxAssignments / kSegRows + 1)) <=
+                  kStaticRoutingScratchBytes,
+              "static routing scratch too small for its stated maximum");
+
+static __device__ __align__(256) unsigned char g_static_routing_scratch[kStaticRoutingScratchBytes];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_addr[kStaticMaxDevices] = {};
+}  // namespace
+
+// Returns the device address of the static scratch on the current device.
+static cudaError_t static_routing_scratch(void** out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kStaticMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* addr = nullptr;
+    err = cudaGetSymbolAddress(&addr, g_static_routing_scratch);
+    if (err != cudaSuccess) return err;
+    g_static_scratch_addr[dev] = addr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return cudaSuccess;
+}
+
+cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int num_assign,
+                                  int top_k, int num_experts, int64_t* counts, int64_t* offsets,
+                                  int64_t* reverse_mapping, int64_t* permutation,
+                                  int32_t* offsets_i32, int64_t* perm_tokens,
+                                  int64_t* perm_experts, void* perm_weights, int down_tiles,
+                                  int down_kblocks, int target_ctas, cudaStream_t stream) {
+  void* base = nullptr;
+  cudaError_t err = static_routing_scratch(&base);
+  if (err != cudaSuccess) return err;
+  unsigned char* b = static_cast<unsigned char*>(base);
+  // The kernel clears the status word and rewrites every schedule entry it
+  // later reports as used, so nothing of the previous call survives.
+  return launch_routing(ids, weights, num_assign, top_k, num_experts, counts, offsets,
+                        reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
+                        perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
+                        reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas,
+                        stream);
 }
 
 }  // namespace b200moe

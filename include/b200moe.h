@@ -41,6 +41,7 @@ extern "C" {
 #define B200MOE_E_DRIVER      (-5)  /* cuTensorMapEncodeTiled could not be resolved / failed */
 #define B200MOE_E_ARCH        (-6)  /* current device is not compute capability 10.0 */
 #define B200MOE_E_UNSUPPORTED (-7)  /* feature is declared but not implemented (NVFP4) */
+#define B200MOE_E_LIMIT       (-8)  /* T*K exceeds B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS */
 
 /* bits of the device status word */
 #define B200MOE_STATUS_BAD_EXPERT_ID  0x1u  /* some expert id was outside [0, E); its row was dropped */
@@ -48,6 +49,9 @@ extern "C" {
 #define B200MOE_STATUS_PEER_TIMEOUT   0x4u  /* a bounded wait on an expert-parallel peer flag gave up */
 
 #define B200MOE_MAX_EXPERTS   256   /* same limit as the reference, csrc/routing_kernels.cu:107 */
+
+/* most assignments (T * top_k) b200moe_routing_static() accepts */
+#define B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS 4096
 
 /* flags of B200MoeArgs.flags */
 #define B200MOE_FLAG_PDL      0x1u  /* launch kernels 2..5 with programmatic dependent launch */
@@ -124,6 +128,39 @@ typedef struct B200MoeArgs {
  * Reads: expert_indices, expert_weights.  Writes: the routing buffers, scratch.
  */
 int b200moe_routing(const B200MoeArgs* args, void* stream);
+
+/*
+ * Stage 1 for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.
+ *
+ * Some hosts of this library are not allowed to call cudaMalloc when they need
+ * routing metadata: an inference server that gave all device memory to its own
+ * arena at start-up, or a plugin whose interface forbids allocation after
+ * initialisation.  This
+ * entry point computes the same counts / offsets / permutation /
+ * reverse_mapping (and, when the pointers are non-NULL, the permuted_* arrays)
+ * as b200moe_routing, but keeps the few KB of scratch the kernel needs in a
+ * fixed 8 KiB array inside the library.  Every GPU that loads the library holds
+ * those 8 KiB until the process exits.  args->scratch and args->scratch_bytes
+ * are ignored; inputs and outputs are still the caller's buffers.
+ *
+ * Limits and rules:
+ *  - T * top_k must not exceed B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS (4096);
+ *    larger calls return B200MOE_E_LIMIT and launch nothing.
+ *  - It calls no cudaMalloc, cudaFree or other allocating routine.
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress, with that device current).  Make that first call
+ *    before any stream capture begins.
+ *  - All calls on one device share the one array: calls that may overlap on the
+ *    GPU (different streams, different threads) race and must be ordered by the
+ *    caller.  Each call clears the state it needs, so back-to-back calls on one
+ *    stream are independent of one another.
+ *  - The segment schedule stays inside the library, so the GEMM stages cannot
+ *    follow this entry point; it serves callers that need the routing tensors.
+ *    An expert id outside [0, E) shows up as reverse_mapping == -1 for that
+ *    assignment and as a shorter count total.
+ */
+int b200moe_routing_static(const B200MoeArgs* args, void* stream);
 
 /*
  * Stage 2 -- gather.  Replaces permute_out_cuda (csrc/permutation_kernels.cu:72-110):

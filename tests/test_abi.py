@@ -48,7 +48,7 @@ def test_library_exports_every_declared_symbol(lib) -> None:
 
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in include/b200moe.h but not exported"
-        assert name in _lib.EXPORTS or name == "b200moe_forward_static", name
+        assert name in _lib.EXPORTS, name
 
 
 def test_build_info_attests_sm100a_and_no_fallback(lib) -> None:
