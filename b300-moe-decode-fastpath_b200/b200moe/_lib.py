@@ -16,13 +16,15 @@ from pathlib import Path
 from typing import Mapping
 
 LIBRARY_NAME = "libb200moe.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 STATUS_BAD_EXPERT_ID = 0x1
 STATUS_PIPE_TIMEOUT = 0x2
 STATUS_PEER_TIMEOUT = 0x4
 
 FLAG_PDL = 0x1
+FLAG_LOCAL_EXPERTS = 0x2
+FLAG_F32_OUTPUT = 0x4
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
@@ -73,6 +75,7 @@ class B200MoeArgs(ctypes.Structure):
         ("scratch_bytes", ctypes.c_size_t),
         ("output", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
+        ("expert_id_base", ctypes.c_int32),
     ]
 
 

@@ -1,0 +1,291 @@
+"""Expert-parallel execution of the layer on 1/2/4/8 GPUs of one NVSwitch box.
+
+The reference has no multi-GPU code at all (README.md:206-207); this module is
+new.  Experts shard naturally: rank ``r`` of ``N`` owns the contiguous experts
+``[r*E/N, (r+1)*E/N)`` and keeps only their weights resident.
+
+One forward:
+
+1. *Dispatch.*  ``tokens="replicated"``: every rank already holds the same
+   ``[T,H]`` activations and routes (decode after tensor-parallel attention);
+   nothing moves.  ``tokens="sharded"``: every rank holds ``T/N`` tokens; the
+   activations, ids and routing weights are all-gathered (at most ~1 MB at
+   decode sizes, one NVSwitch hop).
+2. *Local experts.*  One ``b200moe_forward`` call with
+   ``B200MOE_FLAG_LOCAL_EXPERTS``: the routing kernel subtracts the rank's first
+   expert id and silently drops assignments of other ranks, so the rank's
+   stable order is the global stable order restricted to its experts; the GEMMs
+   stream only the local active experts' weights; the combine kernel stores
+   unrounded FP32 sums of the local assignments (``B200MOE_FLAG_F32_OUTPUT``).
+3. *Combine.*  The FP32 partial outputs are summed across ranks (all-reduce
+   over NVLink/NVSwitch, <= 1.8 MB) and rounded to BF16 once.  ``sharded``
+   callers keep their own rows.
+
+Global routing metadata (bit-exact against a single-GPU run) is assembled from
+the ranks' local tensors by :meth:`ExpertParallelMoE.global_routing`.
+
+The per-rank compute is injected (``local_forward``) so the host logic above
+runs under ``gloo`` on CPUs in the tests; the default is the native kernels and
+nothing else -- there is no CPU execution path in the product.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .forward import _native_args
+from .validation import RoutedMoEShape
+from .workspace import B300MoEWorkspace
+
+LocalForward = Callable[..., torch.Tensor]
+
+
+def expert_range(rank: int, world: int, num_experts: int) -> tuple[int, int]:
+    """First expert id and expert count owned by ``rank``."""
+
+    if num_experts % world != 0:
+        raise ValueError(f"num_experts={num_experts} must be divisible by the world size {world}")
+    per_rank = num_experts // world
+    return rank * per_rank, per_rank
+
+
+class ExpertParallelMoE:
+    """The MoE decode layer with its experts spread over the ranks of a process group."""
+
+    def __init__(
+        self,
+        gate_up_local: torch.Tensor,
+        down_local: torch.Tensor,
+        *,
+        num_experts: int,
+        top_k: int,
+        group: dist.ProcessGroup | None = None,
+        local_forward: LocalForward | None = None,
+        capacity_tokens: int = 64,
+        use_pdl: bool = True,
+    ) -> None:
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.base, self.local_experts = expert_range(self.rank, self.world, num_experts)
+        if gate_up_local.shape[0] != self.local_experts or down_local.shape[0] != self.local_experts:
+            raise ValueError(
+                f"rank {self.rank} owns {self.local_experts} experts but was given "
+                f"{gate_up_local.shape[0]} / {down_local.shape[0]} weight slices"
+            )
+        self.gate_up = gate_up_local
+        self.down = down_local
+        self.hidden_size = gate_up_local.shape[2]
+        self.use_pdl = use_pdl
+        self._local_forward = local_forward or self._native_local_forward
+        self._native = local_forward is None
+        self.workspace = (
+            B300MoEWorkspace(capacity_tokens=capacity_tokens, device=gate_up_local.device)
+            if self._native
+            else None
+        )
+        self._checked = False
+        self._last_call = None
+        self.last_tokens = 0
+
+    # ------------------------------------------------------------------ local compute
+    def _native_local_forward(
+        self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
+    ) -> torch.Tensor:
+        """FP32 ``[T,H]`` sum over this rank's assignments, by the sm_100a kernels."""
+
+        if not self._checked:
+            self._check_native_inputs(hidden, ids, weights)
+            self._checked = True
+        assert self.workspace is not None
+        partial, call = local_partial_forward(
+            hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
+            expert_id_base=self.base, num_experts_global=self.num_experts,
+            workspace=self.workspace, use_pdl=self.use_pdl,
+        )
+        self._last_call = call
+        return partial
+
+    def run_local_stage(self, name: str) -> None:
+        """Re-enqueue one stage of this rank's last local forward (per-stage timing)."""
+
+        args, _keepalive = self._last_call
+        fn = getattr(_lib.load(), f"b200moe_{name}")
+        device = self.gate_up.device
+        stream = torch.cuda.current_stream(device).cuda_stream
+        with torch.cuda.device(device):
+            _lib.check(fn(ctypes.byref(args), ctypes.c_void_p(stream)), f"b200moe_{name}")
+
+    def _check_native_inputs(
+        self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
+    ) -> None:
+        """The single-GPU entry point's gates (b300_moe.py:526-550), for one rank's tensors."""
+
+        if hidden.device.type != "cuda":
+            raise ValueError("expert-parallel native compute requires CUDA tensors")
+        if torch.cuda.get_device_capability(hidden.device) != (10, 0):
+            raise RuntimeError("expert-parallel native compute requires compute capability (10, 0)")
+        if ids.dtype != torch.int64:
+            raise TypeError("expert_indices must have dtype torch.int64")
+        for t in (hidden, weights, self.gate_up, self.down):
+            if t.dtype != torch.bfloat16:
+                raise TypeError("b200_bf16 requires bfloat16 inputs and weights")
+        for t in (hidden, ids, weights, self.gate_up, self.down):
+            if not t.is_contiguous():
+                raise ValueError("all inputs must be contiguous")
+            if t.device != hidden.device:
+                raise ValueError("all inputs must be on the same device")
+        inter = self.gate_up.shape[1] // 2
+        if self.hidden_size % 8 or inter % 8:
+            raise ValueError("hidden_size and intermediate_size must be divisible by 8")
+        if tuple(self.down.shape) != (self.local_experts, self.hidden_size, inter):
+            raise ValueError("down_weight must have shape [E_local, H, I]")
+        _lib.load()
+
+    # ------------------------------------------------------------------ forward
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        expert_indices: torch.Tensor,
+        expert_weights: torch.Tensor,
+        *,
+        tokens: str = "replicated",
+    ) -> torch.Tensor:
+        """Run the layer; returns BF16 ``[T,H]`` for the tokens this rank was given."""
+
+        if tokens not in ("replicated", "sharded"):
+            raise ValueError("tokens must be 'replicated' or 'sharded'")
+        if expert_indices.shape[1] != self.top_k:
+            raise ValueError("top_k must match expert_indices.shape[1]")
+        local_tokens = hidden_states.shape[0]
+        if tokens == "sharded" and self.world > 1:
+            hidden_all = self._all_gather(hidden_states)
+            ids_all = self._all_gather(expert_indices)
+            weights_all = self._all_gather(expert_weights)
+        else:
+            hidden_all, ids_all, weights_all = hidden_states, expert_indices, expert_weights
+        self.last_tokens = hidden_all.shape[0]
+
+        partial = self._local_forward(hidden_all, ids_all, weights_all)
+        if self.world > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        if tokens == "sharded" and self.world > 1:
+            partial = partial[self.rank * local_tokens:(self.rank + 1) * local_tokens]
+        return partial.to(hidden_states.dtype)
+
+    def _all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((self.world * tensor.shape[0],) + tuple(tensor.shape[1:]),
+                          dtype=tensor.dtype, device=tensor.device)
+        dist.all_gather_into_tensor(out, tensor.contiguous(), group=self.group)
+        return out
+
+    # ------------------------------------------------------------------ metadata
+    def local_routing(self) -> dict[str, torch.Tensor]:
+        """This rank's routing tensors of the last forward (native compute only)."""
+
+        assert self.workspace is not None
+        rows = self.last_tokens * self.top_k
+        b = self.workspace.buffers
+        return {
+            "expert_counts": b["expert_counts"][: self.local_experts],
+            "expert_offsets": b["expert_offsets"][: self.local_experts + 1],
+            "permutation": b["permutation"][:rows],
+            "reverse_mapping": b["reverse_mapping"][:rows],
+        }
+
+    def global_routing(self, local: dict[str, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
+        """Assemble the single-GPU routing tensors from the ranks' local ones.
+
+        Experts are contiguous per rank, so the global expert-major order is rank 0's rows,
+        then rank 1's, ...: counts concatenate, offsets are their running sum, a rank's
+        permutation entries keep their (global) assignment ids, and an assignment's global
+        row is its local row plus the rows of all lower ranks.
+        """
+
+        local = local or self.local_routing()
+        return assemble_global_routing(local, self.world, self.group)
+
+
+def local_partial_forward(
+    hidden: torch.Tensor,
+    ids: torch.Tensor,
+    weights: torch.Tensor,
+    gate_up_local: torch.Tensor,
+    down_local: torch.Tensor,
+    *,
+    top_k: int,
+    expert_id_base: int,
+    num_experts_global: int,
+    workspace: B300MoEWorkspace,
+    use_pdl: bool = True,
+):
+    """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
+    id lies in ``[expert_id_base, expert_id_base + E_local)``.
+
+    ``ids`` are GLOBAL expert ids; other ranks' assignments are dropped by the routing
+    kernel (``reverse_mapping == -1``).  Returns the partial output and the bound native
+    call (argument struct plus the tensors it points to) for per-stage re-runs.
+    """
+
+    tokens, hidden_size = hidden.shape
+    local_experts = gate_up_local.shape[0]
+    inter = gate_up_local.shape[1] // 2
+    shape = RoutedMoEShape(tokens, local_experts, top_k, hidden_size, inter)
+    with workspace._lock:
+        # public buffers are sized for the global expert count (>= top_k, >= the local share)
+        workspace.reserve(
+            num_tokens=tokens, num_experts=num_experts_global, top_k=top_k,
+            hidden_size=hidden_size, intermediate_size=inter, device=hidden.device,
+            dtype=hidden.dtype, backend="b200_bf16", quant_mode="bf16",
+        )
+        partial = torch.empty(tokens, hidden_size, dtype=torch.float32, device=hidden.device)
+        flags = _lib.FLAG_LOCAL_EXPERTS | _lib.FLAG_F32_OUTPUT
+        if use_pdl:
+            flags |= _lib.FLAG_PDL
+        args = _native_args(hidden, ids, weights, gate_up_local, down_local, shape, workspace,
+                            partial, flags, expert_id_base=expert_id_base)
+        stream = torch.cuda.current_stream(hidden.device).cuda_stream
+        with torch.cuda.device(hidden.device):
+            code = _lib.load().b200moe_forward(ctypes.byref(args), ctypes.c_void_p(stream))
+        _lib.check(code, "b200moe_forward (expert-parallel rank)")
+        workspace._record_use()
+    return partial, (args, (hidden, ids, weights, gate_up_local, down_local, partial))
+
+
+def assemble_global_routing(
+    local: dict[str, torch.Tensor], world: int, group: dist.ProcessGroup | None = None
+) -> dict[str, torch.Tensor]:
+    counts_local = local["expert_counts"].contiguous()
+    perm_local = local["permutation"].contiguous()
+    rev_local = local["reverse_mapping"].contiguous()
+    rows = perm_local.numel()
+    if world == 1:
+        return {k: v.clone() for k, v in local.items()}
+    counts = [torch.empty_like(counts_local) for _ in range(world)]
+    perms = [torch.empty_like(perm_local) for _ in range(world)]
+    revs = [torch.empty_like(rev_local) for _ in range(world)]
+    dist.all_gather(counts, counts_local, group=group)
+    dist.all_gather(perms, perm_local, group=group)
+    dist.all_gather(revs, rev_local, group=group)
+    all_counts = torch.cat(counts)
+    offsets = torch.cat([all_counts.new_zeros(1), all_counts.cumsum(0)])
+    rank_rows = torch.stack([c.sum() for c in counts])
+    rank_base = torch.cat([rank_rows.new_zeros(1), rank_rows.cumsum(0)])
+    permutation = torch.cat([perms[r][: int(rank_rows[r])] for r in range(world)])
+    reverse = torch.full((rows,), -1, dtype=rev_local.dtype, device=rev_local.device)
+    for r in range(world):
+        mine = revs[r] >= 0
+        reverse = torch.where(mine, revs[r] + rank_base[r], reverse)
+    return {
+        "expert_counts": all_counts,
+        "expert_offsets": offsets,
+        "permutation": permutation,
+        "reverse_mapping": reverse,
+    }

@@ -95,6 +95,7 @@ def _native_args(
     workspace: B300MoEWorkspace,
     output: torch.Tensor,
     flags: int,
+    expert_id_base: int = 0,
 ) -> _lib.B200MoeArgs:
     buffers = workspace.buffers
     scratch = workspace.scratch
@@ -130,6 +131,7 @@ def _native_args(
     args.scratch_bytes = scratch.numel()
     args.output = output.data_ptr()
     args.flags = flags
+    args.expert_id_base = expert_id_base
     return args
 
 

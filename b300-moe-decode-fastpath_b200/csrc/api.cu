@@ -18,7 +18,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
-                           int target_ctas, cudaStream_t stream);
+                           int target_ctas, int id_base, bool foreign_ids_allowed,
+                           cudaStream_t stream);
 cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int num_assign,
                                   int top_k, int num_experts, int64_t* counts, int64_t* offsets,
                                   int64_t* reverse_mapping, int64_t* permutation,
@@ -31,7 +32,7 @@ cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* 
 cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
                            const float* partials, const int32_t* sched, void* out,
                            void* expert_out, int num_tokens, int top_k, int hidden_size,
-                           size_t slice_elems, bool pdl, cudaStream_t stream);
+                           size_t slice_elems, bool f32_out, bool pdl, cudaStream_t stream);
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
                            int inter, int hidden, int rows_cap, int grid, bool pdl,
@@ -117,10 +118,13 @@ int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int check_shape(int tokens, int top_k, int experts, int hidden, int inter) {
+// `local_experts`: `experts` is one rank's share of a larger layer, so top_k may exceed it.
+int check_shape(int tokens, int top_k, int experts, int hidden, int inter,
+                bool local_experts = false) {
   if (tokens < 1 || hidden < 1 || inter < 1 || experts < 1) return B200MOE_E_SHAPE;
   if (!(top_k == 1 || top_k == 2 || top_k == 4 || top_k == 8)) return B200MOE_E_SHAPE;
-  if (experts > B200MOE_MAX_EXPERTS || top_k > experts) return B200MOE_E_SHAPE;
+  if (experts > B200MOE_MAX_EXPERTS || (top_k > experts && !local_experts))
+    return B200MOE_E_SHAPE;
   if ((long long)tokens * top_k > (1ll << 24)) return B200MOE_E_SHAPE;
   if (hidden % 8 || inter % 8) return B200MOE_E_ALIGN;
   return 0;
@@ -156,12 +160,14 @@ int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts
 
 int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                cudaStream_t stream) {
+  const bool local = (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0;
   return (int)launch_routing(a->expert_indices, a->expert_weights, a->num_tokens * a->top_k,
                              a->top_k, a->num_experts, a->expert_counts, a->expert_offsets,
                              a->reverse_mapping, a->permutation, a->expert_offsets_i32,
                              a->permuted_token_indices, a->permuted_expert_indices,
                              a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
-                             (a->intermediate_size + 63) / 64, 2 * dev.sm_count, stream);
+                             (a->intermediate_size + 63) / 64, 2 * dev.sm_count,
+                             local ? a->expert_id_base : 0, local, stream);
 }
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
@@ -221,8 +227,9 @@ struct Ctx {
 int prepare(const B200MoeArgs* a, void* stream, Ctx* c) {
   if (!a) return B200MOE_E_NULL;
   int rc = check_shape(a->num_tokens, a->top_k, a->num_experts, a->hidden_size,
-                       a->intermediate_size);
+                       a->intermediate_size, (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0);
   if (rc) return rc;
+  if ((a->flags & B200MOE_FLAG_LOCAL_EXPERTS) && a->expert_id_base < 0) return B200MOE_E_SHAPE;
   c->assignments = a->num_tokens * a->top_k;
   if (a->rows_cap < c->assignments) return B200MOE_E_SHAPE;
   rc = current_device_info(&c->dev);
@@ -272,7 +279,8 @@ int stage_combine(const B200MoeArgs* a, const Ctx& c, bool pdl) {
     return B200MOE_E_ALIGN;
   return (int)launch_combine(a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched,
                              a->output, a->expert_output, a->num_tokens, a->top_k,
-                             a->hidden_size, (size_t)a->rows_cap * a->hidden_size, pdl, c.stream);
+                             a->hidden_size, (size_t)a->rows_cap * a->hidden_size,
+                             (a->flags & B200MOE_FLAG_F32_OUTPUT) != 0, pdl, c.stream);
 }
 
 }  // namespace

@@ -54,7 +54,8 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
                int64_t* __restrict__ permutation, int32_t* __restrict__ offsets_i32,
                int64_t* __restrict__ perm_tokens, int64_t* __restrict__ perm_experts,
                __nv_bfloat16* __restrict__ perm_weights, int32_t* __restrict__ sched,
-               uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas) {
+               uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas,
+               int id_base, int foreign_ids_allowed) {
   __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
   __shared__ int s_cursor[B200MOE_MAX_EXPERTS];
   __shared__ int s_whist[kRoutingWarps][B200MOE_MAX_EXPERTS];
@@ -77,7 +78,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   // Pass 1: histogram.  Ids outside [0, E) are not counted (the reference
   // ignores them the same way, csrc/routing_kernels.cu:33) and are reported.
   for (int a = tid; a < num_assign; a += kRoutingThreads) {
-    const int64_t e = ids[a];
+    const int64_t e = ids[a] - id_base;
     if (e >= 0 && e < (int64_t)num_experts) {
       atomicAdd(&s_cnt[(int)e], 1);
     } else {
@@ -137,7 +138,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
 
     const int a = base + tid;
     int64_t e64 = -1;
-    if (a < num_assign) e64 = ids[a];
+    if (a < num_assign) e64 = ids[a] - id_base;
     const bool valid = (a < num_assign) && e64 >= 0 && e64 < (int64_t)num_experts;
     const int e = valid ? (int)e64 : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
@@ -179,7 +180,8 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
       if (perm_experts) perm_experts[p] = -1;
       if (perm_weights) perm_weights[p] = __float2bfloat16(0.0f);
     }
-    if (tid == 0) atomicOr(status, B200MOE_STATUS_BAD_EXPERT_ID);
+    // On an expert-parallel rank, ids outside the local range are other ranks' experts.
+    if (tid == 0 && !foreign_ids_allowed) atomicOr(status, B200MOE_STATUS_BAD_EXPERT_ID);
   }
 }
 
@@ -188,12 +190,13 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
-                           int target_ctas, cudaStream_t stream) {
+                           int target_ctas, int id_base, bool foreign_ids_allowed,
+                           cudaStream_t stream) {
   routing_kernel<<<1, kRoutingThreads, 0, stream>>>(
       ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
       offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
-      target_ctas);
+      target_ctas, id_base, foreign_ids_allowed ? 1 : 0);
   return cudaGetLastError();
 }
 
@@ -260,8 +263,8 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
   return launch_routing(ids, weights, num_assign, top_k, num_experts, counts, offsets,
                         reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
                         perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
-                        reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas,
-                        stream);
+                        reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas, 0,
+                        false, stream);
 }
 
 }  // namespace b200moe

@@ -46,7 +46,7 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
                     const __nv_bfloat16* __restrict__ weights, const float* __restrict__ partials,
                     const int32_t* __restrict__ sched, uint4* __restrict__ out,
                     uint4* __restrict__ expert_out, int num_assign, int top_k, int hidden,
-                    size_t slice_elems) {
+                    size_t slice_elems, int f32_out) {
   pdl_wait();
   pdl_launch_dependents();
   const int token = blockIdx.x;
@@ -82,7 +82,15 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[i], w, acc[i]);
   }
-  out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
+  if (f32_out) {
+    // unrounded sums, for callers that add partial outputs of several ranks
+    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) +
+                                          (size_t)token * hidden + col);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  } else {
+    out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
+  }
 }
 
 static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void** args,
@@ -114,13 +122,14 @@ cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* 
 cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
                            const float* partials, const int32_t* sched, void* out,
                            void* expert_out, int num_tokens, int top_k, int hidden_size,
-                           size_t slice_elems, bool pdl, cudaStream_t stream) {
+                           size_t slice_elems, bool f32_out, bool pdl, cudaStream_t stream) {
   int num_assign = num_tokens * top_k;
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weights);
   uint4* o = static_cast<uint4*>(out);
   uint4* eo = static_cast<uint4*>(expert_out);
+  int f32 = f32_out ? 1 : 0;
   void* args[] = {&reverse_mapping, &w, &partials, &sched, &o, &eo, &num_assign, &top_k,
-                  &hidden_size, &slice_elems};
+                  &hidden_size, &slice_elems, &f32};
   const int vecs = hidden_size / 8;
   dim3 grid(num_tokens, (vecs + 127) / 128);
   return launch_with_pdl(reinterpret_cast<const void*>(&combine_rows_kernel), grid, dim3(128),

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 /* host-side contract errors */
 #define B200MOE_E_NULL        (-1)  /* a required pointer is NULL */
@@ -55,6 +55,13 @@ extern "C" {
 
 /* flags of B200MoeArgs.flags */
 #define B200MOE_FLAG_PDL      0x1u  /* launch kernels 2..5 with programmatic dependent launch */
+/* Expert-parallel rank: this call owns experts [expert_id_base, expert_id_base + num_experts)
+ * of a larger layer.  Ids outside that range belong to other ranks: their rows are dropped
+ * silently (reverse_mapping == -1, no status bit) and contribute nothing to the output. */
+#define B200MOE_FLAG_LOCAL_EXPERTS 0x2u
+/* `output` is FP32 [T,H]: the combine stores the unrounded sums, so that partial outputs
+ * of several ranks can be added before the single BF16 rounding. */
+#define B200MOE_FLAG_F32_OUTPUT    0x4u
 
 /* ABI version of the loaded library (== B200MOE_ABI_VERSION it was built with). */
 int b200moe_abi_version(void);
@@ -112,8 +119,9 @@ typedef struct B200MoeArgs {
   void*    scratch;
   size_t   scratch_bytes;
   /* result */
-  void*    output;                   /* [T,H] bf16 */
+  void*    output;                   /* [T,H] bf16 (fp32 with B200MOE_FLAG_F32_OUTPUT) */
   uint32_t flags;                    /* B200MOE_FLAG_* */
+  int32_t  expert_id_base;           /* first global expert id of this rank (B200MOE_FLAG_LOCAL_EXPERTS) */
 } B200MoeArgs;
 
 /*

@@ -181,3 +181,43 @@ def test_tokens_beyond_decode_sizes_stay_correct(cuda_device) -> None:
     err = moe_oracle.relative_max_error(out.float().cpu(), ref)
     floor = moe_oracle.bf16_floor(ref)
     assert err <= max(2e-2, 1.03 * floor), (err, floor)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_ranks_emulated_on_one_gpu(world, cuda_device) -> None:
+    """Each rank's share of an expert-parallel forward, run one after another on one GPU:
+    the sum of the FP32 partial outputs must equal the layer, and every rank's routing
+    must be the global stable order restricted to its experts."""
+
+    from b200moe import B300MoEWorkspace, workloads
+    from b200moe.expert_parallel import expert_range, local_partial_forward
+
+    T, H, I, E, K = 16, 256, 384, 8, 2
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing="zipf", weight_kind="raw", std=None, device=cuda_device
+    )
+    total = torch.zeros(T, H, dtype=torch.float32, device=cuda_device)
+    want = moe_oracle.group_tokens(ids.cpu(), E)
+    for rank in range(world):
+        base, count = expert_range(rank, world, E)
+        workspace = B300MoEWorkspace(device=cuda_device)
+        partial, _ = local_partial_forward(
+            hidden, ids, weights, gate_up[base:base + count].contiguous(),
+            down[base:base + count].contiguous(), top_k=K, expert_id_base=base,
+            num_experts_global=E, workspace=workspace,
+        )
+        total += partial
+        assert workspace.status() == 0  # other ranks' ids are not reported as bad ids
+        rows = int(want.expert_offsets[base + count] - want.expert_offsets[base])
+        lo = int(want.expert_offsets[base])
+        perm = workspace.buffers["permutation"][: T * K].cpu()
+        assert perm[:rows].tolist() == want.permutation[lo:lo + rows].tolist()
+        assert (perm[rows:] == -1).all()
+        rev = workspace.buffers["reverse_mapping"][: T * K].cpu()
+        mine = torch.from_numpy((want.reverse_mapping >= lo) & (want.reverse_mapping < lo + rows))
+        assert torch.equal(rev[mine], torch.from_numpy(want.reverse_mapping)[mine] - lo)
+        assert (rev[~mine] == -1).all()
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
+                                   down.cpu(), num_experts=E, top_k=K)
+    err = moe_oracle.relative_max_error(total.to(torch.bfloat16).float().cpu(), ref)
+    assert err <= 2e-2, err
