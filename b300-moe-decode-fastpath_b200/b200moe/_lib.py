@@ -40,6 +40,7 @@ EXPORTS = (
     "b200moe_down",
     "b200moe_combine",
     "b200moe_forward",
+    "b200moe_ep_reduce",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
 )
@@ -79,6 +80,26 @@ class B200MoeArgs(ctypes.Structure):
     ]
 
 
+class B200MoeEpReduceArgs(ctypes.Structure):
+    """Mirror of ``struct B200MoeEpReduceArgs`` in include/b200moe.h."""
+
+    _fields_ = [
+        ("partial_ptrs", ctypes.POINTER(ctypes.c_void_p)),
+        ("flag_ptrs", ctypes.POINTER(ctypes.c_void_p)),
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("num_tokens", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32),
+        ("wait_limit_us", ctypes.c_uint32),
+        ("output", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
+        ("flags", ctypes.c_uint32),
+    ]
+
+
+EP_MAX_WORLD = 8
+
 _lock = threading.Lock()
 _library: ctypes.CDLL | None = None
 
@@ -112,6 +133,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [args_p, ctypes.c_void_p]
+    lib.b200moe_ep_reduce.restype = ctypes.c_int
+    lib.b200moe_ep_reduce.argtypes = [ctypes.POINTER(B200MoeEpReduceArgs), ctypes.c_void_p]
     lib.b200moe_status_ptr.restype = ctypes.c_int
     lib.b200moe_status_ptr.argtypes = [
         ctypes.c_void_p,

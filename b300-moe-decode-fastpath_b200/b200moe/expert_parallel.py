@@ -17,9 +17,12 @@ One forward:
    stable order is the global stable order restricted to its experts; the GEMMs
    stream only the local active experts' weights; the combine kernel stores
    unrounded FP32 sums of the local assignments (``B200MOE_FLAG_F32_OUTPUT``).
-3. *Combine.*  The FP32 partial outputs are summed across ranks (all-reduce
-   over NVLink/NVSwitch, <= 1.8 MB) and rounded to BF16 once.  ``sharded``
-   callers keep their own rows.
+3. *Combine.*  The FP32 partial outputs are summed across ranks and rounded to
+   BF16 once.  ``transport="p2p"`` does this in one kernel of this library over
+   NVLink peer memory (``b200moe_ep_reduce``: publish a flag, bounded wait for the
+   peers' flags, plain peer loads of every rank's partial rows, fixed rank-order
+   sum); ``transport="nccl"`` is the unfused baseline (all-reduce, then a cast).
+   ``sharded`` callers keep their own rows.
 
 Global routing metadata (bit-exact against a single-GPU run) is assembled from
 the ranks' local tensors by :meth:`ExpertParallelMoE.global_routing`.
@@ -68,6 +71,7 @@ class ExpertParallelMoE:
         local_forward: LocalForward | None = None,
         capacity_tokens: int = 64,
         use_pdl: bool = True,
+        transport: str = "nccl",
     ) -> None:
         self.group = group
         self.rank = dist.get_rank(group)
@@ -94,6 +98,66 @@ class ExpertParallelMoE:
         self._checked = False
         self._last_call = None
         self.last_tokens = 0
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' or 'p2p'")
+        if transport == "p2p" and not self._native:
+            raise ValueError("transport='p2p' needs the native kernels (CUDA peer memory)")
+        self.transport = transport
+        self.capacity_tokens = capacity_tokens
+        self._epoch = 0
+        if transport == "p2p":
+            self._setup_peer_memory()
+
+    # ------------------------------------------------------------------ peer memory
+    def _setup_peer_memory(self) -> None:
+        """Symmetric (peer-mapped) buffers for the native combine: two FP32 partial-output
+        buffers used alternately, and one flag word per rank.  Allocated once; every rank
+        maps every other rank's copy into its own address space."""
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        device = self.gate_up.device
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._partials = symm_mem.empty(
+            (2, self.capacity_tokens, self.hidden_size), dtype=torch.float32, device=device)
+        self._flags = symm_mem.empty((_lib.EP_MAX_WORLD,), dtype=torch.int32, device=device)
+        self._flags.zero_()
+        self._partials.zero_()
+        partial_handle = symm_mem.rendezvous(self._partials, group)
+        flag_handle = symm_mem.rendezvous(self._flags, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
+        stride = self.capacity_tokens * self.hidden_size * 4
+        self._partial_ptrs = [
+            (ctypes.c_void_p * self.world)(*[int(ptr) + parity * stride
+                                             for ptr in partial_handle.buffer_ptrs])
+            for parity in (0, 1)
+        ]
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in flag_handle.buffer_ptrs])
+        self._handles = (partial_handle, flag_handle)
+
+    def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype) -> torch.Tensor:
+        """One launch: publish, wait for the peers (bounded), add the ranks' partial outputs
+        in rank order over NVLink, round to BF16."""
+
+        assert self.workspace is not None and self.workspace.scratch is not None
+        device = self.gate_up.device
+        output = torch.empty(tokens, self.hidden_size, dtype=dtype, device=device)
+        args = _lib.B200MoeEpReduceArgs()
+        args.partial_ptrs = ctypes.cast(self._partial_ptrs[parity], ctypes.POINTER(ctypes.c_void_p))
+        args.flag_ptrs = ctypes.cast(self._flag_ptrs, ctypes.POINTER(ctypes.c_void_p))
+        args.world, args.rank = self.world, self.rank
+        args.num_tokens, args.hidden_size = tokens, self.hidden_size
+        args.epoch = self._epoch & 0xFFFFFFFF
+        args.wait_limit_us = 0
+        args.output = output.data_ptr()
+        args.status = self.workspace.scratch.data_ptr()
+        args.flags = _lib.FLAG_PDL if self.use_pdl else 0
+        stream = torch.cuda.current_stream(device).cuda_stream
+        with torch.cuda.device(device):
+            code = _lib.load().b200moe_ep_reduce(ctypes.byref(args), ctypes.c_void_p(stream))
+        _lib.check(code, "b200moe_ep_reduce")
+        return output
 
     # ------------------------------------------------------------------ local compute
     def _native_local_forward(
@@ -105,10 +169,17 @@ class ExpertParallelMoE:
             self._check_native_inputs(hidden, ids, weights)
             self._checked = True
         assert self.workspace is not None
+        out = None
+        if self.transport == "p2p":
+            if hidden.shape[0] > self.capacity_tokens:
+                raise ValueError(
+                    f"{hidden.shape[0]} tokens exceed the peer buffers' capacity "
+                    f"({self.capacity_tokens}); construct the layer with a larger capacity_tokens")
+            out = self._partials[self._epoch & 1][: hidden.shape[0]]
         partial, call = local_partial_forward(
             hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
             expert_id_base=self.base, num_experts_global=self.num_experts,
-            workspace=self.workspace, use_pdl=self.use_pdl,
+            workspace=self.workspace, use_pdl=self.use_pdl, out=out,
         )
         self._last_call = call
         return partial
@@ -173,12 +244,17 @@ class ExpertParallelMoE:
             hidden_all, ids_all, weights_all = hidden_states, expert_indices, expert_weights
         self.last_tokens = hidden_all.shape[0]
 
+        self._epoch += 1
         partial = self._local_forward(hidden_all, ids_all, weights_all)
-        if self.world > 1:
-            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        if self.transport == "p2p":
+            output = self._peer_reduce(hidden_all.shape[0], self._epoch & 1, hidden_states.dtype)
+        else:
+            if self.world > 1:
+                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            output = partial.to(hidden_states.dtype)
         if tokens == "sharded" and self.world > 1:
-            partial = partial[self.rank * local_tokens:(self.rank + 1) * local_tokens]
-        return partial.to(hidden_states.dtype)
+            output = output[self.rank * local_tokens:(self.rank + 1) * local_tokens]
+        return output
 
     def _all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
         out = torch.empty((self.world * tensor.shape[0],) + tuple(tensor.shape[1:]),
@@ -225,6 +301,7 @@ def local_partial_forward(
     num_experts_global: int,
     workspace: B300MoEWorkspace,
     use_pdl: bool = True,
+    out: torch.Tensor | None = None,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -245,7 +322,13 @@ def local_partial_forward(
             hidden_size=hidden_size, intermediate_size=inter, device=hidden.device,
             dtype=hidden.dtype, backend="b200_bf16", quant_mode="bf16",
         )
-        partial = torch.empty(tokens, hidden_size, dtype=torch.float32, device=hidden.device)
+        if out is None:
+            partial = torch.empty(tokens, hidden_size, dtype=torch.float32, device=hidden.device)
+        else:
+            if out.dtype != torch.float32 or tuple(out.shape) != (tokens, hidden_size) or \
+                    not out.is_contiguous():
+                raise ValueError("out must be a contiguous float32 [T, H] tensor")
+            partial = out
         flags = _lib.FLAG_LOCAL_EXPERTS | _lib.FLAG_F32_OUTPUT
         if use_pdl:
             flags |= _lib.FLAG_PDL

@@ -42,6 +42,11 @@ cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
                         cudaStream_t stream);
 
+cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_ptrs, int world,
+                             int rank, int num_tokens, int hidden, uint32_t epoch,
+                             unsigned long long wait_limit_ns, void* output, uint32_t* status,
+                             bool pdl, cudaStream_t stream);
+
 namespace {
 
 constexpr int kMaxDevices = 64;
@@ -396,6 +401,27 @@ int b200moe_combine(const B200MoeArgs* a, void* stream) {
   Ctx c;
   int rc = prepare(a, stream, &c);
   return rc ? rc : stage_combine(a, c, false);
+}
+
+int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
+  if (!a || !a->partial_ptrs || !a->flag_ptrs || !a->output) return B200MOE_E_NULL;
+  if (a->world < 1 || a->world > B200MOE_EP_MAX_WORLD || a->rank < 0 || a->rank >= a->world ||
+      a->num_tokens < 1 || a->hidden_size < 8)
+    return B200MOE_E_SHAPE;
+  if (a->hidden_size % 8 || !aligned16(a->output)) return B200MOE_E_ALIGN;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->partial_ptrs[r] || !a->flag_ptrs[r]) return B200MOE_E_NULL;
+    if (!aligned16(a->partial_ptrs[r])) return B200MOE_E_ALIGN;
+  }
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  const unsigned long long limit_ns =
+      (a->wait_limit_us ? (unsigned long long)a->wait_limit_us : 1000000ull) * 1000ull;
+  return (int)launch_ep_reduce(a->partial_ptrs, a->flag_ptrs, a->world, a->rank, a->num_tokens,
+                               a->hidden_size, a->epoch, limit_ns, a->output, a->status,
+                               (a->flags & B200MOE_FLAG_PDL) != 0,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_forward(const B200MoeArgs* a, void* stream) {

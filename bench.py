@@ -373,8 +373,20 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     base, count = expert_range(rank, world, EXPERTS)
     gate_up, down = workloads.make_expert_weights(count, HIDDEN, INTER, seed=1236 + rank,
                                                   std=0.02, device=device)
-    layer = ExpertParallelMoE(gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                              capacity_tokens=max(SWEEP))
+    baseline = ExpertParallelMoE(gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                                 capacity_tokens=max(SWEEP), transport="nccl")
+    transport, transport_note = args.ep_transport, None
+    layer = baseline
+    if transport == "p2p":
+        try:
+            layer = ExpertParallelMoE(gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                                      capacity_tokens=max(SWEEP), transport="p2p")
+        except Exception as error:  # peer mapping unavailable on this box: say so, use NCCL
+            transport, transport_note = "nccl", f"p2p setup failed: {type(error).__name__}: {error}"
+        agree = torch.tensor([1 if transport == "p2p" else 0], device=device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0 and transport == "p2p":
+            transport, transport_note, layer = "nccl", "p2p setup failed on another rank", baseline
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=device)
     cases = {}
@@ -436,6 +448,14 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     e2e_samples = timed_pass(forward_e2e, args.steps)
     samples = max_over_ranks(samples)
     e2e_samples = max_over_ranks(e2e_samples)
+    # the unfused baseline (NCCL all-reduce + cast) on the same inputs, for comparison
+    nccl_samples = None
+    if layer is not baseline:
+        def forward_nccl(T):
+            return baseline.forward(*cases[T]["dev"], tokens="replicated")
+
+        timed_pass(forward_nccl, 3)
+        nccl_samples = max_over_ranks(timed_pass(forward_nccl, max(5, args.steps // 2)))
 
     # per-rank stage timing of the dominant kernel at the largest T (all local experts active)
     T_big = SWEEP[-1]
@@ -473,6 +493,8 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
             "busiest_rank_weight_bytes": weight_bytes(busiest)["total"],
             "busiest_rank_weight_gbs": round(weight_bytes(busiest)["total"] / total["p50"] / 1e3, 1),
         }
+        if nccl_samples is not None:
+            per_t[str(T)]["nccl_allreduce_baseline_us"] = summary(nccl_samples[T])
     p50s = [per_t[str(T)]["total_us"]["p50"] for T in SWEEP]
     e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in SWEEP]
     gu_bytes = weight_bytes(max(r[-1] for r in active_by_rank))["gate_up"]
@@ -497,7 +519,11 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
             "workload": WORKLOAD,
             "tokens": list(SWEEP),
             "parallelism": f"expert-parallel ep{world}: {EXPERTS // world} experts per rank, "
-                           "tokens replicated, FP32 partial outputs all-reduced (NCCL)",
+                           "tokens replicated, FP32 partial outputs combined by "
+                           + ("one peer-memory kernel over NVLink (b200moe_ep_reduce)"
+                              if transport == "p2p" else "NCCL all-reduce + cast"),
+            "transport": transport,
+            "transport_note": transport_note,
             "l2": "flushed before every timed forward (256 MiB written, then 256 MiB read)",
             "step": "one forward at each T of the sweep; every sample is the max over ranks",
         },
@@ -505,7 +531,7 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "what": "ExpertParallelMoE.forward with pinned host activations/routes copied in "
                         "and the output copied out inside the timed region, per rank"},
-        "gpu_launches": 5 * len(SWEEP) * args.steps * world,
+        "gpu_launches": (6 if transport == "p2p" else 5) * len(SWEEP) * args.steps * world,
         "clocks": clocks,
         "roofline": {
             "kernel": f"grouped_gemm_kernel<gate_up> on the busiest rank, T={T_big}",
@@ -620,6 +646,8 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--ep-transport", choices=("p2p", "nccl"), default="p2p",
+                        help="N > 1: combine over NVLink peer memory (default) or NCCL")
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
     args = parser.parse_args()

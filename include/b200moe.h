@@ -218,6 +218,41 @@ int b200moe_combine(const B200MoeArgs* args, void* stream);
 int b200moe_forward(const B200MoeArgs* args, void* stream);
 
 /*
+ * Expert-parallel combine over NVLink peer memory.  No counterpart in the
+ * reference, which has no multi-GPU code (README.md:206-207).
+ *
+ * After its local b200moe_forward (B200MOE_FLAG_LOCAL_EXPERTS |
+ * B200MOE_FLAG_F32_OUTPUT, output = this rank's partial buffer), every rank calls
+ * this once per layer call with the same `epoch` (1, 2, 3, ...).  The kernel
+ * publishes the epoch into flags[rank] of every rank, waits until its own flag
+ * array shows the epoch for all ranks (at most wait_limit_us, then
+ * B200MOE_STATUS_PEER_TIMEOUT is set in *status and the output is left
+ * untouched), then adds the `world` FP32 partial outputs in rank order with plain
+ * peer loads and stores BF16 [T,H].
+ *
+ *   partial_ptrs[world]  device pointers, valid on THIS device, to every rank's
+ *                        FP32 [num_tokens, hidden_size] partial buffer
+ *   flag_ptrs[world]     device pointers, valid on THIS device, to every rank's
+ *                        uint32[world] flag array (zero before the first epoch)
+ * Both arrays are read on the host.  Callers alternate two partial buffers by
+ * epoch parity so a fast rank never overwrites a buffer a slow rank still reads.
+ */
+typedef struct B200MoeEpReduceArgs {
+  const void* const* partial_ptrs;
+  void* const*       flag_ptrs;
+  int32_t  world, rank, num_tokens, hidden_size;
+  uint32_t epoch;
+  uint32_t wait_limit_us;            /* 0 selects the default of 1 s */
+  void*    output;                   /* [T,H] bf16 */
+  uint32_t* status;                  /* device status word, or NULL */
+  uint32_t flags;                    /* B200MOE_FLAG_PDL */
+} B200MoeEpReduceArgs;
+
+#define B200MOE_EP_MAX_WORLD 8
+
+int b200moe_ep_reduce(const B200MoeEpReduceArgs* args, void* stream);
+
+/*
  * Device address of the 32-bit status word inside a scratch region, so a
  * caller can copy it back when it chooses to synchronise.  Replaces the
  * device-side assert the reference uses for out-of-range ids

@@ -221,3 +221,67 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(world, cuda_device) -> None:
                                    down.cpu(), num_experts=E, top_k=K)
     err = moe_oracle.relative_max_error(total.to(torch.bfloat16).float().cpu(), ref)
     assert err <= 2e-2, err
+
+
+def _ep_reduce_call(device, partials, flag_arrays, rank, epoch, limit_us, status, output):
+    import ctypes
+
+    from b200moe import _lib
+
+    world = len(partials)
+    args = _lib.B200MoeEpReduceArgs()
+    p_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in partials])
+    f_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in flag_arrays])
+    args.partial_ptrs = ctypes.cast(p_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.flag_ptrs = ctypes.cast(f_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.world, args.rank = world, rank
+    args.num_tokens, args.hidden_size = output.shape
+    args.epoch, args.wait_limit_us = epoch, limit_us
+    args.output, args.status, args.flags = output.data_ptr(), status.data_ptr(), 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    code = _lib.load().b200moe_ep_reduce(ctypes.byref(args), stream)
+    _lib.check(code, "b200moe_ep_reduce")
+    torch.cuda.synchronize(device)
+
+
+def test_peer_reduce_kernel_with_all_ranks_buffers_on_one_gpu(cuda_device) -> None:
+    """The expert-parallel combine kernel with the ranks' buffers all on this GPU and the
+    peers' flags written by the host: rank-order FP32 sum, one BF16 rounding."""
+
+    g = torch.Generator(device="cpu").manual_seed(3)
+    world, T, H = 4, 17, 2880
+    partials = [torch.randn(T, H, generator=g).to(cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    flags[1][:] = torch.tensor([5, 0, 5, 5, 0, 0, 0, 0], dtype=torch.int32)  # peers 0, 2, 3 arrived
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    output = torch.zeros(T, H, dtype=torch.bfloat16, device=cuda_device)
+    _ep_reduce_call(cuda_device, partials, flags, rank=1, epoch=5, limit_us=0, status=status,
+                    output=output)
+    expected = partials[0].clone()
+    for other in partials[1:]:
+        expected += other
+    assert torch.equal(output, expected.to(torch.bfloat16))
+    assert int(status.item()) == 0
+    # the kernel published this rank's epoch into slot `rank` of every rank's flag array
+    assert [int(f[1]) for f in flags] == [5, 5, 5, 5]
+
+
+def test_peer_reduce_wait_is_bounded_and_reports_a_missing_peer(cuda_device) -> None:
+    """A peer that never publishes: the wait gives up after its limit, sets the status
+    bit and leaves the output alone; the context stays usable."""
+
+    world, T, H = 2, 3, 64
+    partials = [torch.ones(T, H, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    output = torch.full((T, H), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    _ep_reduce_call(cuda_device, partials, flags, rank=0, epoch=1, limit_us=2000, status=status,
+                    output=output)
+    assert int(status.item()) & 0x4
+    assert float(output.float().min()) == 7.0 and float(output.float().max()) == 7.0
+    flags[0][1] = 1  # the peer arrives: the same call now completes
+    status.zero_()
+    _ep_reduce_call(cuda_device, partials, flags, rank=0, epoch=1, limit_us=2000, status=status,
+                    output=output)
+    assert int(status.item()) == 0
+    assert float(output.float().min()) == 2.0
