@@ -154,6 +154,8 @@ def load() -> ctypes.CDLL:
     """
 
     global _library
+    if _library is not None:
+        return _library
     with _lock:
         if _library is not None:
             return _library

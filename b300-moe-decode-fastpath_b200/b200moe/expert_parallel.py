@@ -41,7 +41,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .forward import _native_args
+from .forward import _enqueue, _native_args
 from .validation import RoutedMoEShape
 from .workspace import B300MoEWorkspace
 
@@ -153,10 +153,9 @@ class ExpertParallelMoE:
         args.output = output.data_ptr()
         args.status = self.workspace.scratch.data_ptr()
         args.flags = _lib.FLAG_PDL if self.use_pdl else 0
-        stream = torch.cuda.current_stream(device).cuda_stream
-        with torch.cuda.device(device):
-            code = _lib.load().b200moe_ep_reduce(ctypes.byref(args), ctypes.c_void_p(stream))
-        _lib.check(code, "b200moe_ep_reduce")
+        code = _enqueue(_lib.load().b200moe_ep_reduce, args, device)
+        if code:
+            _lib.check(code, "b200moe_ep_reduce")
         return output
 
     # ------------------------------------------------------------------ local compute
@@ -189,10 +188,7 @@ class ExpertParallelMoE:
 
         args, _keepalive = self._last_call
         fn = getattr(_lib.load(), f"b200moe_{name}")
-        device = self.gate_up.device
-        stream = torch.cuda.current_stream(device).cuda_stream
-        with torch.cuda.device(device):
-            _lib.check(fn(ctypes.byref(args), ctypes.c_void_p(stream)), f"b200moe_{name}")
+        _lib.check(_enqueue(fn, args, self.gate_up.device), f"b200moe_{name}")
 
     def _check_native_inputs(
         self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
@@ -334,10 +330,9 @@ def local_partial_forward(
             flags |= _lib.FLAG_PDL
         args = _native_args(hidden, ids, weights, gate_up_local, down_local, shape, workspace,
                             partial, flags, expert_id_base=expert_id_base)
-        stream = torch.cuda.current_stream(hidden.device).cuda_stream
-        with torch.cuda.device(hidden.device):
-            code = _lib.load().b200moe_forward(ctypes.byref(args), ctypes.c_void_p(stream))
-        _lib.check(code, "b200moe_forward (expert-parallel rank)")
+        code = _enqueue(_lib.load().b200moe_forward, args, hidden.device)
+        if code:
+            _lib.check(code, "b200moe_forward (expert-parallel rank)")
         workspace._record_use()
     return partial, (args, (hidden, ids, weights, gate_up_local, down_local, partial))
 

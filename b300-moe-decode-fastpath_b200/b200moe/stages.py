@@ -65,7 +65,9 @@ class StagedLayer:
         self.output = torch.empty_like(hidden_states)
         # keep the inputs alive for as long as their addresses sit in the struct
         self._inputs = (hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight)
-        self._args = _native_args(
+        # a private struct: the workspace keeps its own bound struct for forward calls
+        self._args = _lib.B200MoeArgs()
+        bound = _native_args(
             hidden_states,
             expert_indices,
             expert_weights,
@@ -76,6 +78,7 @@ class StagedLayer:
             self.output,
             _lib.FLAG_PDL if use_pdl else 0,
         )
+        ctypes.memmove(ctypes.byref(self._args), ctypes.byref(bound), ctypes.sizeof(bound))
         lib = _lib.load()
         self._calls = {
             "routing": lib.b200moe_routing,

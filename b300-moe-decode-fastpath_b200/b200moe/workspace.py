@@ -70,6 +70,8 @@ class B300MoEWorkspace:
         self._last_reused = False
         self._last_stream: int | None = None
         self._event: torch.cuda.Event | None = None
+        self._recorded_streams: set[int] = set()
+        self._args_cache: tuple[object, object] | None = None  # bound native argument struct
         self._lock = threading.RLock()
 
     # -- read-only state --------------------------------------------------------
@@ -200,6 +202,8 @@ class B300MoEWorkspace:
         self._buffers = buffers
         self._scratch = None
         self._scratch_base = None
+        self._recorded_streams = set()
+        self._args_cache = None
         if native and device.type == "cuda":
             need = _lib.scratch_bytes(tokens, top_k, num_experts, hidden, inter)
             base = torch.empty(need + _SCRATCH_ALIGN, device=device, dtype=torch.uint8)
@@ -270,7 +274,9 @@ class B300MoEWorkspace:
             on_cuda = target.type == "cuda"
             if on_cuda:
                 stream = torch.cuda.current_stream(target)
-                if self._event is not None:
+                # Work already queued on this same stream is ordered by the stream itself;
+                # the event is only needed when the previous use was on another stream.
+                if self._event is not None and self._last_stream != int(stream.cuda_stream):
                     stream.wait_event(self._event)
                 capturing = torch.cuda.is_current_stream_capturing()
                 if self._event is None:
@@ -314,6 +320,12 @@ class B300MoEWorkspace:
             return self._last_reused
 
     def _record_streams(self, stream: "torch.cuda.Stream") -> None:
+        # One record per (allocation, stream) is enough: the caching allocator keeps the
+        # stream in the block's set until the block is freed.
+        key = int(stream.cuda_stream)
+        if key in self._recorded_streams:
+            return
+        self._recorded_streams.add(key)
         for tensor in self._buffers.values():
             tensor.record_stream(stream)
         if self._scratch_base is not None:

@@ -9,8 +9,8 @@
 // and, in the same launch, the segment schedule both grouped GEMMs read, so no
 // host synchronisation is needed to size their work.
 //
-// Stability: assignments are visited in chunks of 1024 in increasing order; in
-// a chunk, a warp owns 32 consecutive assignments, a lane's rank among equal
+// Stability: assignments are visited in increasing order, one block-width (at
+// most 1024) per round; in a round, a warp owns 32 consecutive assignments, a lane's rank among equal
 // ids in its warp is the number of lower lanes with the same id, and warps are
 // ordered by a per-expert running cursor.  Rows of one expert therefore keep
 // increasing assignment ids, which is torch.argsort(stable=True).
@@ -20,13 +20,14 @@
 
 namespace b200moe {
 
-constexpr int kRoutingThreads = 1024;
+constexpr int kRoutingThreads = 1024;   // most threads per block; small calls launch fewer
 constexpr int kRoutingWarps = kRoutingThreads / 32;
 
 // Exclusive scan of one int per thread over the whole block.  `total` receives
 // the block sum in every thread.  `tmp` is kRoutingWarps ints of shared memory.
 __device__ __forceinline__ int block_exclusive_scan(int v, int* tmp, int& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int num_warps = blockDim.x >> 5;
   int inc = v;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
@@ -36,8 +37,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* tmp, int& total)
   if (lane == 31) tmp[warp] = inc;
   __syncthreads();
   int base = 0, sum = 0;
-#pragma unroll 8
-  for (int w = 0; w < kRoutingWarps; ++w) {
+  for (int w = 0; w < num_warps; ++w) {
     int t = tmp[w];
     if (w < warp) base += t;
     sum += t;
@@ -63,6 +63,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   __shared__ int s_bad;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int threads = blockDim.x, num_warps = blockDim.x >> 5;
 
   // Everything the next kernel needs from this one is written before this grid
   // completes, and it waits for completion; let its launch overlap this one.
@@ -77,7 +78,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
 
   // Pass 1: histogram.  Ids outside [0, E) are not counted (the reference
   // ignores them the same way, csrc/routing_kernels.cu:33) and are reported.
-  for (int a = tid; a < num_assign; a += kRoutingThreads) {
+  for (int a = tid; a < num_assign; a += threads) {
     const int64_t e = ids[a] - id_base;
     if (e >= 0 && e < (int64_t)num_experts) {
       atomicAdd(&s_cnt[(int)e], 1);
@@ -130,10 +131,10 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   }
   __syncthreads();
 
-  // Pass 2: stable placement, 1024 assignments per round.
-  for (int base = 0; base < num_assign; base += kRoutingThreads) {
-    for (int i = tid; i < kRoutingWarps * B200MOE_MAX_EXPERTS; i += kRoutingThreads)
-      (&s_whist[0][0])[i] = 0;
+  // Pass 2: stable placement, one block-width of assignments per round.
+  for (int base = 0; base < num_assign; base += threads) {
+    for (int i = tid; i < num_warps * num_experts; i += threads)
+      s_whist[i / num_experts][i % num_experts] = 0;
     __syncthreads();
 
     const int a = base + tid;
@@ -148,8 +149,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
 
     if (is_expert) {
       int run = s_cursor[tid];
-#pragma unroll 8
-      for (int w = 0; w < kRoutingWarps; ++w) {
+      for (int w = 0; w < num_warps; ++w) {
         const int t = s_whist[w][tid];
         s_whist[w][tid] = run;
         run += t;
@@ -174,7 +174,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   // Rows past the valid ones exist only when some id was out of range: mark
   // them invalid so the gather zero-fills them and nothing reads stale indices.
   if (s_bad) {
-    for (int p = n_valid + tid; p < num_assign; p += kRoutingThreads) {
+    for (int p = n_valid + tid; p < num_assign; p += threads) {
       permutation[p] = -1;
       if (perm_tokens) perm_tokens[p] = -1;
       if (perm_experts) perm_experts[p] = -1;
@@ -192,7 +192,12 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, int id_base, bool foreign_ids_allowed,
                            cudaStream_t stream) {
-  routing_kernel<<<1, kRoutingThreads, 0, stream>>>(
+  // One thread per expert and per assignment of a round, in whole warps; fewer warps make
+  // the block-wide barriers of a decode-sized call cheaper.
+  int threads = num_assign > num_experts ? num_assign : num_experts;
+  threads = (threads + 31) / 32 * 32;
+  if (threads > kRoutingThreads) threads = kRoutingThreads;
+  routing_kernel<<<1, threads, 0, stream>>>(
       ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
       offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,

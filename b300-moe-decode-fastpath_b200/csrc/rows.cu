@@ -58,25 +58,41 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
-  for (int k = 0; k < top_k; ++k) {
-    const int a = token * top_k + k;
-    const int64_t row = reverse_mapping[a];
-    if (row < 0 || row >= (int64_t)num_assign) continue;
-    const float w = __bfloat162float(weights[a]);
-    const float* src = partials + (size_t)row * hidden + col;
-    float v[8];
-    {
-      const float4 lo = *reinterpret_cast<const float4*>(src);
-      const float4 hi = *reinterpret_cast<const float4*>(src + 4);
-      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
-      v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+  // Slot metadata first (independent loads), then per slot all split-K slices at once:
+  // the loads of one slot are issued back to back and only the additions are ordered.
+  int64_t rows[8];
+  float wts[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    rows[k] = -1;
+    wts[k] = 0.0f;
+    if (k < top_k) {
+      rows[k] = reverse_mapping[token * top_k + k];
+      wts[k] = __bfloat162float(weights[token * top_k + k]);
     }
-    for (int s = 1; s < splits; ++s) {
-      const float* ps = src + (size_t)s * slice_elems;
-      const float4 lo = *reinterpret_cast<const float4*>(ps);
-      const float4 hi = *reinterpret_cast<const float4*>(ps + 4);
-      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
-      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (k >= top_k) break;
+    const int64_t row = rows[k];
+    if (row < 0 || row >= (int64_t)num_assign) continue;
+    const float w = wts[k];
+    const float* src = partials + (size_t)row * hidden + col;
+    float4 lo[kDownSplitMax], hi[kDownSplitMax];
+#pragma unroll
+    for (int s = 0; s < kDownSplitMax; ++s) {
+      if (s < splits) {
+        lo[s] = *reinterpret_cast<const float4*>(src + (size_t)s * slice_elems);
+        hi[s] = *reinterpret_cast<const float4*>(src + (size_t)s * slice_elems + 4);
+      }
+    }
+    float v[8] = {lo[0].x, lo[0].y, lo[0].z, lo[0].w, hi[0].x, hi[0].y, hi[0].z, hi[0].w};
+#pragma unroll
+    for (int s = 1; s < kDownSplitMax; ++s) {
+      if (s < splits) {
+        v[0] += lo[s].x; v[1] += lo[s].y; v[2] += lo[s].z; v[3] += lo[s].w;
+        v[4] += hi[s].x; v[5] += hi[s].y; v[6] += hi[s].z; v[7] += hi[s].w;
+      }
     }
     if (expert_out) expert_out[((size_t)row * hidden + col) >> 3] = pack_bf16x8(v);
 #pragma unroll

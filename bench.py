@@ -250,6 +250,16 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     e2e_samples = timed_pass(forward_e2e, args.steps)
     torch.cuda.synchronize(device)
 
+    # host cost of one call: enqueue 20 forwards back to back without synchronising
+    host_us = {}
+    for T in sweep:
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        for _ in range(20):
+            forward(T)
+        host_us[T] = (time.perf_counter() - t0) / 20 * 1e6
+    torch.cuda.synchronize(device)
+
     # per-stage timing through the staged C-ABI entry points (isolated launches)
     peak, peak_kind = measured_peak_gbs()
     per_t: dict[str, object] = {}
@@ -278,6 +288,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "active_experts": c["active"],
             "total_us": total,
             "e2e_us": summary(e2e_samples[T]),
+            "host_enqueue_us": round(host_us[T], 1),
             "stages_us": {
                 "routing": stage_us["routing"],
                 "permutation": stage_us["gather"],
@@ -457,6 +468,15 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         timed_pass(forward_nccl, 3)
         nccl_samples = max_over_ranks(timed_pass(forward_nccl, max(5, args.steps // 2)))
 
+    host_us = {}
+    for T in SWEEP:
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        for _ in range(20):
+            forward(T)
+        host_us[T] = (time.perf_counter() - t0) / 20 * 1e6
+    torch.cuda.synchronize(device)
+
     # per-rank stage timing of the dominant kernel at the largest T (all local experts active)
     T_big = SWEEP[-1]
     forward(T_big)
@@ -489,6 +509,7 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         per_t[str(T)] = {
             "total_us": total,
             "e2e_us": summary(e2e_samples[T]),
+            "host_enqueue_us_rank0": round(host_us[T], 1),
             "active_experts_per_rank": [r[i] for r in active_by_rank],
             "busiest_rank_weight_bytes": weight_bytes(busiest)["total"],
             "busiest_rank_weight_gbs": round(weight_bytes(busiest)["total"] / total["p50"] / 1e3, 1),
