@@ -82,10 +82,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     if (!kGateUp) prefetch_tensormap(&map_b1);
   }
 
-  pdl_wait();
-  pdl_launch_dependents();
-
   // ---- decode this block's unit from the device-built schedule -------------
+  // The schedule is final before this grid can start: with programmatic dependent
+  // launch a grid only starts after every block of its predecessor has passed its own
+  // dependency wait, i.e. after the routing kernel completed.  So the unit and the
+  // weight tiles (caller inputs) may be touched before this grid's own wait; only the
+  // token rows written by the previous kernel may not.
   const int n_seg = p.sched[kSchedNumSegments];
   int unit = blockIdx.x;
   int split = 0, n_split = 1;
@@ -119,6 +121,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   const int num_stages = min((int)(kStageBudget / stage_bytes), kMaxStages);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
+  // ---- weight prefetch: fill the first stages' weight tiles while the previous
+  // kernel is still finishing; the token rows of those stages follow after the wait.
+  const int prefetched = min(num_stages, num_kb);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < prefetched; ++i) {
+      const uint32_t bar = smem_u32(&s_full[i]);
+      const uint32_t a_dst = smem_base + (uint32_t)i * stage_bytes;
+      const int kc = (kb0 + i) * kTileK;
+      mbar_expect_tx(bar, stage_bytes);
+      if (kGateUp) {
+        tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
+      } else {
+        tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
+      }
+    }
+  }
+
+  pdl_wait();
+  pdl_launch_dependents();
+
   // ---- tensor memory ------------------------------------------------------------
   const uint32_t cols_needed = (uint32_t)n_mma * (kGateUp ? 2u : 1u);
   uint32_t tmem_cols = 32;
@@ -146,11 +168,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         const uint32_t a_dst = smem_base + (uint32_t)s * stage_bytes;
         const uint32_t b_dst = a_dst + kABytes;
         const int kc = (kb0 + i) * kTileK;
-        mbar_expect_tx(bar, stage_bytes);
-        if (kGateUp) {
-          tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
-        } else {
-          tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
+        if (i >= prefetched) {
+          mbar_expect_tx(bar, stage_bytes);
+          if (kGateUp) {
+            tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
+          } else {
+            tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
+          }
         }
         for (int r = 0; r < n_mma; r += 16) {
           tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b0, bar, kc, row_start + r);
