@@ -28,6 +28,10 @@ FLAG_F32_OUTPUT = 0x4
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
+TUNE_STAGE_KB = 1
+TUNE_L2_PROMOTION = 2
+TUNE_EVICT_FIRST = 3
+
 EXPORTS = (
     "b200moe_abi_version",
     "b200moe_build_info",
@@ -43,6 +47,7 @@ EXPORTS = (
     "b200moe_ep_reduce",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
+    "b200moe_tune",
 )
 
 
@@ -143,6 +148,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     ]
     lib.b200moe_nvfp4_available.restype = ctypes.c_int
     lib.b200moe_nvfp4_available.argtypes = []
+    lib.b200moe_tune.restype = ctypes.c_int
+    lib.b200moe_tune.argtypes = [ctypes.c_int, ctypes.c_int]
 
 
 def load() -> ctypes.CDLL:

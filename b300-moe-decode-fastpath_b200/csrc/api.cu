@@ -47,7 +47,12 @@ cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_
                              unsigned long long wait_limit_ns, void* output, uint32_t* status,
                              bool pdl, cudaStream_t stream);
 
+extern int g_gemm_stage_kb;
+extern int g_gemm_evict_first;
+
 namespace {
+
+int g_l2_promotion = 2;  // 0 none, 1 128 B, 2 256 B
 
 constexpr int kMaxDevices = 64;
 
@@ -114,10 +119,14 @@ int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t
     stride *= dims[i];
     if (i + 1 < rank) gstride[i] = stride;
   }
+  const CUtensorMapL2promotion promotion =
+      g_l2_promotion == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                          : (g_l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
                         const_cast<void*>(base), gdim, gstride, bdim, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
 }
 
@@ -351,6 +360,24 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status) {
 }
 
 int b200moe_nvfp4_available(void) { return 0; }
+
+int b200moe_tune(int knob, int value) {
+  switch (knob) {
+    case B200MOE_TUNE_STAGE_KB:
+      if (value < 48 || value > 220) return B200MOE_E_SHAPE;
+      g_gemm_stage_kb = value;
+      return 0;
+    case B200MOE_TUNE_L2_PROMOTION:
+      if (value < 0 || value > 2) return B200MOE_E_SHAPE;
+      g_l2_promotion = value;
+      return 0;
+    case B200MOE_TUNE_EVICT_FIRST:
+      g_gemm_evict_first = value ? 1 : 0;
+      return 0;
+    default:
+      return B200MOE_E_SHAPE;
+  }
+}
 
 int b200moe_routing(const B200MoeArgs* a, void* stream) {
   Ctx c;

@@ -36,8 +36,8 @@ namespace b200moe {
 
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kStageBudget = 108u * 1024u;           // bytes of pipeline stages
-constexpr uint32_t kGemmSmemBytes = kStageBudget + 1024u;  // + slack to align to 1024
+constexpr uint32_t kStageBudget = 108u * 1024u;           // default bytes of pipeline stages
+constexpr uint32_t kMaxStageBudget = 220u * 1024u;        // one block per SM
 constexpr int kTileM = 128;   // weight rows per unit
 constexpr int kTileK = 64;    // elements per pipeline stage along K (128 bytes)
 constexpr uint64_t kAbortDrainNs = 1000000ull;
@@ -52,6 +52,8 @@ struct GemmParams {
   int k_total;             // reduction length: H (gate+up) or I (down)
   int m_tiles;             // ceil(m_total / 128)
   int rows_cap;
+  uint32_t stage_budget;   // bytes of shared memory the stage ring may use
+  int evict_first;         // stream the weight tiles with an L2 evict-first hint
 };
 
 template <bool kGateUp>
@@ -118,8 +120,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   constexpr uint32_t kABytes = kGateUp ? 2u * kTileM * 128u : kTileM * 128u;
   const uint32_t b_bytes = (uint32_t)n_mma * 128u * (kGateUp ? 1u : 2u);
   const uint32_t stage_bytes = kABytes + b_bytes;
-  const int num_stages = min((int)(kStageBudget / stage_bytes), kMaxStages);
+  const int num_stages = min((int)(p.stage_budget / stage_bytes), kMaxStages);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const uint64_t weight_policy = p.evict_first ? l2_policy_evict_first() : 0ull;
+  auto load_weights = [&](uint32_t dst, uint32_t bar, int kc) {
+    if (kGateUp) {
+      if (p.evict_first) tma_load_4d_hint(dst, &map_w, bar, kc, tile * kTileM, 0, expert, weight_policy);
+      else tma_load_4d(dst, &map_w, bar, kc, tile * kTileM, 0, expert);
+    } else {
+      if (p.evict_first) tma_load_3d_hint(dst, &map_w, bar, kc, tile * kTileM, expert, weight_policy);
+      else tma_load_3d(dst, &map_w, bar, kc, tile * kTileM, expert);
+    }
+  };
 
   // ---- weight prefetch: fill the first stages' weight tiles while the previous
   // kernel is still finishing; the token rows of those stages follow after the wait.
@@ -130,11 +143,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       const uint32_t a_dst = smem_base + (uint32_t)i * stage_bytes;
       const int kc = (kb0 + i) * kTileK;
       mbar_expect_tx(bar, stage_bytes);
-      if (kGateUp) {
-        tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
-      } else {
-        tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
-      }
+      load_weights(a_dst, bar, kc);
     }
   }
 
@@ -170,11 +179,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         const int kc = (kb0 + i) * kTileK;
         if (i >= prefetched) {
           mbar_expect_tx(bar, stage_bytes);
-          if (kGateUp) {
-            tma_load_4d(a_dst, &map_w, bar, kc, tile * kTileM, 0, expert);
-          } else {
-            tma_load_3d(a_dst, &map_w, bar, kc, tile * kTileM, expert);
-          }
+          load_weights(a_dst, bar, kc);
         }
         for (int r = 0; r < n_mma; r += 16) {
           tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b0, bar, kc, row_start + r);
@@ -288,6 +293,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 }
 
+// Tuning knobs (b200moe_tune): process-wide, meant for benchmarking sweeps.
+int g_gemm_stage_kb = 108;
+int g_gemm_evict_first = 0;
+static uint32_t gemm_stage_budget() {
+  uint32_t b = (uint32_t)g_gemm_stage_kb * 1024u;
+  if (b < 48u * 1024u) b = 48u * 1024u;
+  if (b > kMaxStageBudget) b = kMaxStageBudget;
+  return b;
+}
+
 template <bool kGateUp>
 static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_b0,
                                const CUtensorMap& map_b1, const GemmParams& params, int grid,
@@ -298,14 +313,15 @@ static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     err = cudaFuncSetAttribute(grouped_gemm_kernel<kGateUp>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)(kMaxStageBudget + 1024u));
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cfg.dynamicSmemBytes = params.stage_budget + 1024u;  // + slack to align to 1024
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -320,6 +336,8 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            int inter, int hidden, int rows_cap, int grid, bool pdl,
                            cudaStream_t stream) {
   GemmParams p;
+  p.stage_budget = gemm_stage_budget();
+  p.evict_first = g_gemm_evict_first;
   p.sched = sched;
   p.status = status;
   p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
@@ -337,6 +355,8 @@ cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
                         cudaStream_t stream) {
   GemmParams p;
+  p.stage_budget = gemm_stage_budget();
+  p.evict_first = g_gemm_evict_first;
   p.sched = sched;
   p.status = status;
   p.act_hi = nullptr;

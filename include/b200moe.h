@@ -266,6 +266,23 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status);
  */
 int b200moe_nvfp4_available(void);
 
+/*
+ * Process-wide tuning knobs of the grouped GEMMs, for benchmarking sweeps.  No
+ * counterpart in the reference (its GEMMs are library calls with no knobs).
+ * Not thread-safe against concurrent forwards; results never depend on them.
+ *   B200MOE_TUNE_STAGE_KB      shared memory of the TMA stage ring per block,
+ *                              48..220 KB (default 108: two blocks per SM;
+ *                              above 113 one block per SM with a deeper ring)
+ *   B200MOE_TUNE_L2_PROMOTION  TMA L2 promotion of all tensor maps: 0 none,
+ *                              1 = 128 B, 2 = 256 B (default)
+ *   B200MOE_TUNE_EVICT_FIRST   1: weight tiles are loaded with an L2
+ *                              evict-first hint (default 0)
+ */
+#define B200MOE_TUNE_STAGE_KB     1
+#define B200MOE_TUNE_L2_PROMOTION 2
+#define B200MOE_TUNE_EVICT_FIRST  3
+int b200moe_tune(int knob, int value);
+
 #ifdef __cplusplus
 }
 #endif
