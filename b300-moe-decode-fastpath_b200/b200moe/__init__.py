@@ -8,6 +8,7 @@ Public names follow the reference package (fastpath/__init__.py:3-9) so that
 from ._lib import available as cuda_extension_available
 from ._lib import build_info
 from .forward import ARCHITECTURE, b300_moe_forward
+from .router import topk_routing
 from .stages import StagedLayer
 from .validation import RoutedMoEShape, validate_routed_moe_inputs
 from .workspace import B300MoEWorkspace
@@ -20,5 +21,6 @@ __all__ = [
     "b300_moe_forward",
     "build_info",
     "cuda_extension_available",
+    "topk_routing",
     "validate_routed_moe_inputs",
 ]

@@ -48,6 +48,7 @@ EXPORTS = (
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
     "b200moe_tune",
+    "b200moe_router_topk",
 )
 
 
@@ -148,6 +149,11 @@ def _declare(lib: ctypes.CDLL) -> None:
     ]
     lib.b200moe_nvfp4_available.restype = ctypes.c_int
     lib.b200moe_nvfp4_available.argtypes = []
+    lib.b200moe_router_topk.restype = ctypes.c_int
+    lib.b200moe_router_topk.argtypes = [
+        ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+    ]
     lib.b200moe_tune.restype = ctypes.c_int
     lib.b200moe_tune.argtypes = [ctypes.c_int, ctypes.c_int]
 

@@ -274,11 +274,17 @@ class B300MoEWorkspace:
             on_cuda = target.type == "cuda"
             if on_cuda:
                 stream = torch.cuda.current_stream(target)
-                # Work already queued on this same stream is ordered by the stream itself;
-                # the event is only needed when the previous use was on another stream.
-                if self._event is not None and self._last_stream != int(stream.cuda_stream):
-                    stream.wait_event(self._event)
                 capturing = torch.cuda.is_current_stream_capturing()
+                # Work already queued on this same stream is ordered by the stream itself;
+                # the event is only needed when the previous use was on another stream.  A
+                # capturing stream must not wait on work outside its graph (CUDA rejects the
+                # dependency); the caller synchronises before starting a capture.
+                if (
+                    self._event is not None
+                    and not capturing
+                    and self._last_stream != int(stream.cuda_stream)
+                ):
+                    stream.wait_event(self._event)
                 if self._event is None:
                     if capturing:
                         raise RuntimeError(
@@ -339,6 +345,9 @@ class B300MoEWorkspace:
         if self._event is None:
             raise RuntimeError("workspace completion event is missing; call reserve before use")
         stream = torch.cuda.current_stream(self._device)
-        self._event.record(stream)
+        # An event recorded while the stream is being captured belongs to the graph and
+        # cannot order later eager work; inside a capture the graph's own edges order reuse.
+        if not torch.cuda.is_current_stream_capturing():
+            self._event.record(stream)
         self._last_stream = int(stream.cuda_stream)
         self._record_streams(stream)

@@ -47,6 +47,10 @@ cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_
                              unsigned long long wait_limit_ns, void* output, uint32_t* status,
                              bool pdl, cudaStream_t stream);
 
+cudaError_t launch_router_topk(const void* logits, bool logits_f32, int num_tokens,
+                               int num_experts, int top_k, int64_t* ids, void* weights_bf16,
+                               float* weights_f32, cudaStream_t stream);
+
 extern int g_gemm_stage_kb;
 extern int g_gemm_evict_first;
 
@@ -360,6 +364,21 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status) {
 }
 
 int b200moe_nvfp4_available(void) { return 0; }
+
+int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, int num_experts,
+                        int top_k, int64_t* expert_indices, void* weights_bf16,
+                        float* weights_f32, void* stream) {
+  if (!logits || !expert_indices) return B200MOE_E_NULL;
+  if (num_tokens < 1 || num_experts < 1 || num_experts > B200MOE_MAX_EXPERTS || top_k < 1 ||
+      top_k > 8 || top_k > num_experts)
+    return B200MOE_E_SHAPE;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_router_topk(logits, logits_are_f32 != 0, num_tokens, num_experts, top_k,
+                                 expert_indices, weights_bf16, weights_f32,
+                                 static_cast<cudaStream_t>(stream));
+}
 
 int b200moe_tune(int knob, int value) {
   switch (knob) {

@@ -46,8 +46,37 @@ import torch  # noqa: E402
 
 SWEEP = (1, 2, 4, 8, 16, 32, 64)
 HIDDEN, INTER, EXPERTS, TOP_K = 4096, 14336, 8, 2
+ROUTING, WEIGHT_KIND = "uniform", "softmax"
 WORKLOAD = "mixtral_8x7b_bf16_decode_layer_H4096_I14336_E8_K2_T1-64"
 METRIC = "moe_layer_decode_p50_us_mean_over_T1_2_4_8_16_32_64"
+
+# The default (and the only configuration the driver's line is quoted on) is the
+# Mixtral-shaped sweep.  The others are the remaining benchmark configurations, run by
+# hand with --config for the numbers recorded in DESIGN.md / profiles/.
+CONFIGS = {
+    "mixtral": dict(hidden=4096, inter=14336, experts=8, top_k=2, sweep=(1, 2, 4, 8, 16, 32, 64),
+                    routing="uniform", weight_kind="softmax"),
+    "wide": dict(hidden=4096, inter=14336, experts=64, top_k=8, sweep=(64,),
+                 routing="zipf", weight_kind="raw"),
+    "deepseek": dict(hidden=7168, inter=2048, experts=256, top_k=8, sweep=(1, 8, 32, 64),
+                     routing="uniform", weight_kind="softmax"),
+    "deepseek_hotspot": dict(hidden=7168, inter=2048, experts=256, top_k=8, sweep=(1, 8, 32, 64),
+                             routing="hotspot", weight_kind="softmax"),
+    "irregular": dict(hidden=2880, inter=2880, experts=32, top_k=8, sweep=(1, 3, 17, 63),
+                      routing="concentrated", weight_kind="softmax"),
+}
+
+
+def apply_config(name: str) -> None:
+    global SWEEP, HIDDEN, INTER, EXPERTS, TOP_K, ROUTING, WEIGHT_KIND, WORKLOAD, METRIC
+    c = CONFIGS[name]
+    HIDDEN, INTER, EXPERTS, TOP_K = c["hidden"], c["inter"], c["experts"], c["top_k"]
+    SWEEP, ROUTING, WEIGHT_KIND = c["sweep"], c["routing"], c["weight_kind"]
+    if name != "mixtral":
+        tokens = "_".join(str(t) for t in SWEEP)
+        WORKLOAD = (f"{name}_bf16_decode_layer_H{HIDDEN}_I{INTER}_E{EXPERTS}_K{TOP_K}_"
+                    f"{ROUTING}_T{tokens}")
+        METRIC = f"moe_layer_decode_p50_us_mean_over_T{tokens}"
 L2_FLUSH_BYTES = 256 << 20
 FALLBACK_HBM_GBS = 6650.0
 STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
@@ -195,8 +224,8 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     cases = {}
     for T in sweep:
         hidden = workloads.make_hidden(T, HIDDEN, seed=1234)
-        ids = workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235)
-        weights = workloads.make_routing_weights(T, TOP_K, "softmax", 1235)
+        ids = workloads.make_routing(T, EXPERTS, TOP_K, ROUTING, 1235)
+        weights = workloads.make_routing_weights(T, TOP_K, WEIGHT_KIND, 1235)
         host = tuple(t.pin_memory() for t in (hidden, ids, weights))
         dev = tuple(t.to(device) for t in host)
         cases[T] = {
@@ -404,8 +433,8 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     for T in SWEEP:
         host = tuple(t.pin_memory() for t in (
             workloads.make_hidden(T, HIDDEN, seed=1234),
-            workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235),
-            workloads.make_routing_weights(T, TOP_K, "softmax", 1235)))
+            workloads.make_routing(T, EXPERTS, TOP_K, ROUTING, 1235),
+            workloads.make_routing_weights(T, TOP_K, WEIGHT_KIND, 1235)))
         dev = tuple(t.to(device) for t in host)
         ids = host[1]
         local_active = int(torch.unique(ids[(ids >= base) & (ids < base + count)]).numel())
@@ -619,8 +648,8 @@ def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
     cases = {}
     for T in SWEEP:
         cases[T] = (workloads.make_hidden(T, HIDDEN, seed=1234),
-                    workloads.make_routing(T, EXPERTS, TOP_K, "uniform", 1235),
-                    workloads.make_routing_weights(T, TOP_K, "softmax", 1235))
+                    workloads.make_routing(T, EXPERTS, TOP_K, ROUTING, 1235),
+                    workloads.make_routing_weights(T, TOP_K, WEIGHT_KIND, 1235))
     samples = {T: [] for T in SWEEP}
     for _ in range(args.warmup):
         for T in SWEEP:
@@ -667,11 +696,16 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--config", choices=tuple(CONFIGS), default="mixtral",
+                        help="benchmark configuration (default: the Mixtral-shaped sweep)")
     parser.add_argument("--ep-transport", choices=("p2p", "nccl"), default="p2p",
                         help="N > 1: combine over NVLink peer memory (default) or NCCL")
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
     args = parser.parse_args()
+    apply_config(args.config)
+    if args.config in ("wide", "deepseek", "deepseek_hotspot"):
+        args.no_cpu_baseline = True  # ~21 GiB of weights: the CPU port is not timed on these
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup

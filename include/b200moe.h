@@ -267,6 +267,22 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status);
 int b200moe_nvfp4_available(void);
 
 /*
+ * Router front end (the step in front of the layer).  Replaces the two PyTorch
+ * calls of topk_routing (baseline/routing.py:48-55), which the reference's
+ * benchmark counts in routing_us and total_us (benchmark/benchmark_goal_1b.py:464,
+ * 530-533): per token the top_k largest router logits in descending order
+ * (lower expert id first among equal logits), then a softmax over those k
+ * logits computed in FP32.
+ *   logits            [T,E] bf16, or fp32 when logits_are_f32 != 0;  E <= 256
+ *   expert_indices    [T,K] int64 out
+ *   weights_bf16      [T,K] bf16 out or NULL
+ *   weights_f32       [T,K] fp32 out or NULL
+ */
+int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, int num_experts,
+                        int top_k, int64_t* expert_indices, void* weights_bf16,
+                        float* weights_f32, void* stream);
+
+/*
  * Process-wide tuning knobs of the grouped GEMMs, for benchmarking sweeps.  No
  * counterpart in the reference (its GEMMs are library calls with no knobs).
  * Not thread-safe against concurrent forwards; results never depend on them.

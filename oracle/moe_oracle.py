@@ -12,6 +12,7 @@ what the reference's ``backend="torch"`` computes:
 * gather                baseline/torch_moe.py:96-99 (``permute_hidden_states``)
 * per-expert SwiGLU FFN fastpath/reference.py:268-281, baseline/torch_moe.py:102-120
 * weighted combine      baseline/torch_moe.py:123-133 (``combine_expert_outputs``)
+* router top-k/softmax  baseline/routing.py:48-55   (``topk_routing``)
 * an independent token/slot loop  tests/test_goal_1b_correctness.py:46-63
 
 Parity is pinned: ``tests/golden/*.npz`` hold inputs and outputs produced by
@@ -113,6 +114,21 @@ def group_tokens_by_counting(expert_indices, num_experts: int) -> Routing:
         expert_counts=counts,
         expert_offsets=offsets,
     )
+
+
+def topk_routing(router_logits: torch.Tensor, top_k: int):
+    """Top-k experts per token and a softmax over the selected logits (routing.py:48-55).
+
+    The softmax runs in FP32 and is cast back to the logits' dtype.  Ties between equal
+    logits resolve to the lower expert id here (a stable descending sort); ``torch.topk``
+    leaves that order unspecified, so parity is stated on tie-free selections.
+    """
+
+    order = torch.argsort(router_logits.float(), dim=-1, descending=True, stable=True)
+    ids = order[:, :top_k].contiguous()
+    selected = torch.gather(router_logits.float(), 1, ids)
+    weights = torch.softmax(selected, dim=-1).to(router_logits.dtype)
+    return ids, weights
 
 
 def _silu(x: torch.Tensor) -> torch.Tensor:

@@ -57,13 +57,37 @@ def load_golden_cases() -> list[GoldenCase]:
     cases: list[GoldenCase] = []
     for path in sorted(GOLDEN_DIR.glob("golden_*.npz")):
         data = np.load(path)
+        if "dims" not in data.files:
+            continue  # not a layer fixture (the router fixture has its own loader)
         group = path.stem.removeprefix("golden_")
         for index in range(int(data["num_cases"][0])):
             cases.append(GoldenCase(group, data, index))
     return cases
 
 
+def load_router_cases() -> list[dict]:
+    """Router fixtures: logits plus the reference's top-k ids and softmax weights."""
+
+    data = np.load(GOLDEN_DIR / "golden_router.npz")
+    cases = []
+    for index in range(int(data["num_cases"][0])):
+        for tag in ("f32", "bf16"):
+            p = f"case{index}_{tag}_"
+            if tag == "f32":
+                logits = torch.from_numpy(data[p + "logits"].copy())
+                weights = torch.from_numpy(data[p + "weights"].copy())
+            else:
+                logits = _from_bits(data[p + "logits"])
+                weights = _from_bits(data[p + "weights"])
+            ids = torch.from_numpy(data[p + "ids"].copy())
+            cases.append({"label": f"router{index}_{tag}_T{ids.shape[0]}_E{logits.shape[1]}"
+                                   f"_K{ids.shape[1]}",
+                          "logits": logits, "ids": ids, "weights": weights})
+    return cases
+
+
 GOLDEN_CASES = load_golden_cases()
+ROUTER_CASES = load_router_cases()
 
 
 @pytest.fixture(scope="session")

@@ -120,6 +120,21 @@ def main() -> int:
             payload[p + "label"] = np.array(f"T={T},K={K},{workload}")
         np.savez_compressed(HERE / f"golden_{name}.npz", **payload)
         print("wrote", name, {k: v.shape for k, v in payload.items() if k.startswith("case0")})
+    # router front end: the reference's generators and its topk_routing, FP32 and BF16 logits
+    router: dict[str, np.ndarray] = {}
+    specs = [(1, 8, 1, "uniform"), (7, 16, 2, "hotspot"), (64, 64, 8, "zipf"),
+             (33, 256, 8, "uniform"), (64, 128, 4, "hotspot")]
+    for index, (T, E, K, workload) in enumerate(specs):
+        logits = generate_router_logits(T, E, K, workload, 500 + index, dtype=torch.float32)
+        for tag, cast in (("f32", logits), ("bf16", logits.to(torch.bfloat16))):
+            ids, weights = topk_routing(cast, K)
+            p = f"case{index}_{tag}_"
+            router[p + "logits"] = logits.numpy() if tag == "f32" else bf16_bits(cast)
+            router[p + "ids"] = ids.numpy()
+            router[p + "weights"] = weights.numpy() if tag == "f32" else bf16_bits(weights)
+    router["num_cases"] = np.array([len(specs)], np.int64)
+    np.savez_compressed(HERE / "golden_router.npz", **router)
+    print("wrote router", len(specs))
     return 0
 
 

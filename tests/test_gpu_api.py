@@ -285,3 +285,74 @@ def test_peer_reduce_wait_is_bounded_and_reports_a_missing_peer(cuda_device) -> 
                     output=output)
     assert int(status.item()) == 0
     assert float(output.float().min()) == 2.0
+
+
+@pytest.mark.parametrize("use_pdl", [False, True])
+def test_forward_replays_from_a_cuda_graph(use_pdl, cuda_device) -> None:
+    """The whole layer is five launches and no allocation in the library, so a decode step
+    can be captured once and replayed with new activations and routes.  (The reference
+    could not do this: its grouped GEMM allocates inside ATen, docs/goal_1b_report.md:189-194.)"""
+
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    hidden, ids, weights, gate_up, down = _case(cuda_device, tokens=8, hidden=256, inter=384)
+    workspace = B300MoEWorkspace(capacity_tokens=8, device=cuda_device)
+    kwargs = dict(num_experts=16, top_k=2, workspace=workspace, use_pdl=use_pdl)
+    b300_moe_forward(hidden, ids, weights, gate_up, down, **kwargs)  # reserve before capture
+    torch.cuda.synchronize(cuda_device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = b300_moe_forward(hidden, ids, weights, gate_up, down, **kwargs)
+    other = _case(cuda_device, tokens=8, hidden=256, inter=384, seed=99, routing="zipf")
+    hidden.copy_(other[0])
+    ids.copy_(other[1])
+    weights.copy_(other[2])
+    graph.replay()
+    torch.cuda.synchronize(cuda_device)
+    replayed = captured.clone()
+    eager = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=16, top_k=2,
+                             use_pdl=use_pdl)
+    assert torch.equal(replayed, eager)
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
+                                   down.cpu(), num_experts=16, top_k=2)
+    assert moe_oracle.relative_max_error(replayed.float().cpu(), ref) <= 2e-2
+
+
+from conftest import ROUTER_CASES  # noqa: E402
+
+
+@pytest.mark.parametrize("case", ROUTER_CASES, ids=lambda c: c["label"])
+def test_router_topk_matches_reference_golden(case, cuda_device) -> None:
+    """The router kernel against what the reference's topk_routing returned for the same
+    logits: ids exact on tie-free selections, softmax weights to one ulp of their dtype."""
+
+    from b200moe import topk_routing
+
+    top_k = case["ids"].shape[1]
+    ids, weights = topk_routing(case["logits"].to(cuda_device), top_k)
+    assert ids.dtype == torch.int64 and weights.dtype == case["weights"].dtype
+    selected = torch.gather(case["logits"].float(), 1, case["ids"])
+    tie_free = (selected[:, :-1] != selected[:, 1:]).all(dim=1) if top_k > 1 else \
+        torch.ones(selected.shape[0], dtype=torch.bool)
+    assert torch.equal(ids.cpu()[tie_free], case["ids"][tie_free])
+    # the logits the kernel picked are the reference's, ties or not
+    torch.testing.assert_close(
+        torch.gather(case["logits"].float(), 1, ids.cpu()), selected, atol=0, rtol=0)
+    ulp = 2.0 ** -7 if weights.dtype == torch.bfloat16 else 2.0 ** -22
+    torch.testing.assert_close(weights.float().cpu(), case["weights"].float(), atol=ulp,
+                               rtol=ulp)
+
+
+def test_router_then_layer_end_to_end(cuda_device) -> None:
+    from b200moe import b300_moe_forward, topk_routing, workloads
+
+    T, H, I, E, K = 16, 256, 384, 32, 4
+    hidden, _, _, gate_up, down = workloads.make_case(T, H, I, E, K, std=None, device=cuda_device)
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(4)).to(
+        device=cuda_device, dtype=torch.bfloat16)
+    ids, weights = topk_routing(logits, K)
+    out = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K)
+    ref_ids, ref_w = moe_oracle.topk_routing(logits.cpu(), K)
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ref_ids, ref_w, gate_up.cpu(), down.cpu(),
+                                   num_experts=E, top_k=K)
+    assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2

@@ -93,3 +93,19 @@ def test_low_precision_variant_is_close_and_floor_is_reported() -> None:
     assert moe_oracle.relative_max_error(low.float(), ref) < 0.1
     floor = moe_oracle.bf16_floor(ref)
     assert 0.0 < floor < 2e-2
+
+
+from conftest import ROUTER_CASES  # noqa: E402
+
+
+@pytest.mark.parametrize("case", ROUTER_CASES, ids=lambda c: c["label"])
+def test_oracle_router_matches_reference_topk_routing(case) -> None:
+    ids, weights = moe_oracle.topk_routing(case["logits"], case["ids"].shape[1])
+    # compare where the selection is tie-free (torch.topk leaves ties unspecified)
+    selected = torch.gather(case["logits"].float(), 1, case["ids"])
+    tie_free = (selected[:, :-1] != selected[:, 1:]).all(dim=1) if selected.shape[1] > 1 else \
+        torch.ones(selected.shape[0], dtype=torch.bool)
+    assert bool(tie_free.any())
+    assert torch.equal(ids[tie_free], case["ids"][tie_free])
+    torch.testing.assert_close(weights.float(), case["weights"].float(), atol=1e-6, rtol=1e-6)
+    assert weights.dtype == case["weights"].dtype
