@@ -31,6 +31,7 @@ STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 TUNE_STAGE_KB = 1
 TUNE_L2_PROMOTION = 2
 TUNE_EVICT_FIRST = 3
+TUNE_EARLY_START = 4
 
 EXPORTS = (
     "b200moe_abi_version",

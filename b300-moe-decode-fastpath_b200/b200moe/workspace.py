@@ -148,6 +148,28 @@ class B300MoEWorkspace:
             return 0
         return int(self._scratch[:4].view(torch.int32).item()) & 0xFFFFFFFF
 
+    TIMELINE_KERNELS = ("routing", "gather", "gate_up", "down", "combine", "ep_reduce")
+
+    def timeline(self) -> dict[str, tuple[float, float]]:
+        """Device timeline of the last forward (synchronises): for each kernel the time its
+        first block started and its last block finished, in microseconds after the start of
+        the routing kernel, from ``%globaltimer`` stamps the kernels leave in the scratch
+        region.  ``*_first_data`` is when block 0 of a GEMM saw its first operands arrive."""
+
+        if self._scratch is None:
+            return {}
+        words = self._scratch[64:64 + 128].view(torch.int64).cpu().tolist()
+        origin = words[0]
+        result: dict[str, tuple[float, float]] = {}
+        for k, name in enumerate(self.TIMELINE_KERNELS):
+            start, end = words[2 * k], words[2 * k + 1]
+            if end:
+                result[name] = ((start - origin) / 1e3, (end - origin) / 1e3)
+        for k, name in ((6, "gate_up_first_data"), (7, "down_first_data")):
+            if words[2 * k]:
+                result[name] = ((words[2 * k] - origin) / 1e3, (words[2 * k] - origin) / 1e3)
+        return result
+
     def raise_for_status(self) -> None:
         """Raise if the last forward reported a device-side condition (synchronises).
 

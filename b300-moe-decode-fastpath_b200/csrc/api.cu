@@ -27,16 +27,19 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
                                   int64_t* perm_experts, void* perm_weights, int down_tiles,
                                   int down_kblocks, int target_ctas, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
-                          int num_assign, int num_tokens, int top_k, int hidden_size, bool pdl,
+                          int num_assign, int num_tokens, int top_k, int hidden_size,
+                          bool early_trigger, unsigned long long* trace, bool pdl,
                           cudaStream_t stream);
 cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
                            const float* partials, const int32_t* sched, void* out,
                            void* expert_out, int num_tokens, int top_k, int hidden_size,
-                           size_t slice_elems, bool f32_out, bool pdl, cudaStream_t stream);
+                           size_t slice_elems, bool f32_out, unsigned long long* trace, bool pdl,
+                           cudaStream_t stream);
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
-                           int inter, int hidden, int rows_cap, int grid, bool pdl,
-                           cudaStream_t stream);
+                           int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
+                           int num_assign, int num_experts, int id_base, int top_k,
+                           const CUtensorMap* map_hidden, bool pdl, cudaStream_t stream);
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
@@ -53,6 +56,7 @@ cudaError_t launch_router_topk(const void* logits, bool logits_f32, int num_toke
 
 extern int g_gemm_stage_kb;
 extern int g_gemm_evict_first;
+extern int g_early_mode;
 
 namespace {
 
@@ -189,7 +193,8 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
 }
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
-               int hidden, int inter, void* act_hi, const Scratch& s, bool pdl,
+               int hidden, int inter, void* act_hi, const Scratch& s, const int64_t* ids,
+               int id_base, int top_k, const void* hidden_states, bool pdl,
                cudaStream_t stream) {
   CUtensorMap map_w, map_x;
   {
@@ -205,8 +210,18 @@ int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int 
     if (rc) return rc;
   }
   const int grid = segment_bound(assignments, experts) * tiles128(inter);
+  // hidden_states [T,H] with one-row boxes: blocks with few rows fetch them from here
+  CUtensorMap map_hidden;
+  const bool have_hidden = ids != nullptr && hidden_states != nullptr && aligned16(hidden_states);
+  if (have_hidden) {
+    const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)(assignments / top_k)};
+    const uint32_t box[2] = {64, 1};
+    int rc = encode_bf16_map(&map_hidden, hidden_states, 2, dims, box);
+    if (rc) return rc;
+  }
   return (int)launch_gate_up(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, inter, hidden,
-                             rows_cap, grid, pdl, stream);
+                             rows_cap, grid, ids, assignments, experts, id_base, top_k,
+                             have_hidden ? &map_hidden : nullptr, pdl, stream);
 }
 
 int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, int experts,
@@ -231,6 +246,11 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   if (grid < 2 * dev.sm_count) grid = 2 * dev.sm_count;
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
                           rows_cap, grid, pdl, stream);
+}
+
+unsigned long long* trace_of(const Scratch& s) {
+  return reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(s.status) +
+                                               kTraceOffsetBytes);
 }
 
 struct Ctx {
@@ -271,7 +291,8 @@ int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (!a->hidden_states || !a->permutation || !a->permuted_hidden) return B200MOE_E_NULL;
   if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
   return (int)launch_gather(a->hidden_states, a->permutation, a->permuted_hidden, c.assignments,
-                            a->num_tokens, a->top_k, a->hidden_size, pdl, c.stream);
+                            a->num_tokens, a->top_k, a->hidden_size, g_early_mode >= 1,
+                            trace_of(c.s), pdl, c.stream);
 }
 
 int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
@@ -281,7 +302,9 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
     return B200MOE_E_ALIGN;
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
-                    pdl, c.stream);
+                    a->expert_indices,
+                    (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) ? a->expert_id_base : 0, a->top_k,
+                    a->hidden_states, pdl, c.stream);
 }
 
 int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {
@@ -298,7 +321,8 @@ int stage_combine(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   return (int)launch_combine(a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched,
                              a->output, a->expert_output, a->num_tokens, a->top_k,
                              a->hidden_size, (size_t)a->rows_cap * a->hidden_size,
-                             (a->flags & B200MOE_FLAG_F32_OUTPUT) != 0, pdl, c.stream);
+                             (a->flags & B200MOE_FLAG_F32_OUTPUT) != 0, trace_of(c.s), pdl,
+                             c.stream);
 }
 
 }  // namespace
@@ -392,6 +416,10 @@ int b200moe_tune(int knob, int value) {
       return 0;
     case B200MOE_TUNE_EVICT_FIRST:
       g_gemm_evict_first = value ? 1 : 0;
+      return 0;
+    case B200MOE_TUNE_EARLY_START:
+      if (value < 0 || value > 2) return B200MOE_E_SHAPE;
+      g_early_mode = value;
       return 0;
     default:
       return B200MOE_E_SHAPE;

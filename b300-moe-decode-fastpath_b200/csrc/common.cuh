@@ -77,6 +77,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// Timeline of one forward, kept in the status area of the scratch region: for kernel k,
+// word 2k = time block 0 started, word 2k+1 = time the last block finished
+// (%globaltimer, ns).  The routing kernel clears the end times when it starts.
+constexpr int kTraceKernels = 8;
+constexpr size_t kTraceOffsetBytes = 64;
+enum TraceKernel {
+  kTraceRouting = 0, kTraceGather = 1, kTraceGateUp = 2, kTraceDown = 3, kTraceCombine = 4,
+  kTraceEpReduce = 5, kTraceGateUpFirstData = 6, kTraceDownFirstData = 7,
+};
+__device__ __forceinline__ void trace_start(unsigned long long* t, int k) {
+  if (t && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) t[2 * k] = global_timer_ns();
+}
+__device__ __forceinline__ void trace_end(unsigned long long* t, int k) {
+  if (t && threadIdx.x == 0) atomicMax(&t[2 * k + 1], (unsigned long long)global_timer_ns());
+}
+
 // Programmatic dependent launch: wait until the grids this one depends on have
 // completed and their writes are visible.  A no-op when the kernel was not
 // launched with the programmatic-serialization attribute.

@@ -36,11 +36,12 @@ namespace b200moe {
 
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kStageBudget = 108u * 1024u;           // default bytes of pipeline stages
 constexpr uint32_t kMaxStageBudget = 220u * 1024u;        // one block per SM
 constexpr int kTileM = 128;   // weight rows per unit
 constexpr int kTileK = 64;    // elements per pipeline stage along K (128 bytes)
 constexpr uint64_t kAbortDrainNs = 1000000ull;
+constexpr int kOwnRoutingMaxAssign = 2048;  // gate+up blocks derive their unit themselves up to here
+constexpr int kDirectRowsMax = 32;  // ... and fetch the token rows themselves up to this many
 
 struct GemmParams {
   const int32_t* sched;
@@ -52,6 +53,11 @@ struct GemmParams {
   int k_total;             // reduction length: H (gate+up) or I (down)
   int m_tiles;             // ceil(m_total / 128)
   int rows_cap;
+  const int64_t* ids;      // gate+up: the call's expert ids [num_assign] (or null)
+  int num_assign, num_experts, id_base, top_k;
+  int hidden_map_valid;    // gate+up: the third tensor map describes hidden_states [T,H]
+  int early_mode;          // gate+up: 0 wait for routing, 1 own routing, 2 own routing + own rows
+  unsigned long long* trace;
   uint32_t stage_budget;   // bytes of shared memory the stage ring may use
   int evict_first;         // stream the weight tiles with an L2 evict-first hint
 };
@@ -67,6 +73,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   __shared__ __align__(8) uint64_t s_acc;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_hist[B200MOE_MAX_EXPERTS];
+  __shared__ int s_unit[5];
+  __shared__ int s_tokens[kDirectRowsMax];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -81,32 +90,106 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     fence_mbar_init();
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_b0);
-    if (!kGateUp) prefetch_tensormap(&map_b1);
+    prefetch_tensormap(&map_b1);
   }
 
-  // ---- decode this block's unit from the device-built schedule -------------
-  // The schedule is final before this grid can start: with programmatic dependent
-  // launch a grid only starts after every block of its predecessor has passed its own
-  // dependency wait, i.e. after the routing kernel completed.  So the unit and the
-  // weight tiles (caller inputs) may be touched before this grid's own wait; only the
-  // token rows written by the previous kernel may not.
-  const int n_seg = p.sched[kSchedNumSegments];
+  // ---- find this block's unit --------------------------------------------------
+  // down: the schedule is final before this grid can start (a dependent grid starts
+  // only after every block of gate+up has passed its own dependency wait, hence after
+  // the routing kernel completed), so it is read before this grid's own wait.
+  // gate+up: routing and gather let their dependents start at once, so this grid can
+  // be running while the routing kernel still is.  For decode-sized calls each block
+  // therefore derives its unit from the expert ids itself (a histogram and a scan over
+  // <= 256 experts: the routing kernel's segment rule, restated), starts streaming its
+  // weight tiles, and only then waits for routing and gather to complete.
   int unit = blockIdx.x;
   int split = 0, n_split = 1;
-  if (!kGateUp) {
-    n_split = p.sched[kSchedDownSplits];
-    split = unit % n_split;
-    unit /= n_split;
+  int expert = 0, row_start = 0, n_rows = 0;
+  bool waited = false;
+  const bool own_routing = kGateUp && p.early_mode >= 1 && p.ids != nullptr &&
+                           p.num_assign <= kOwnRoutingMaxAssign;
+  if (own_routing) {
+    for (int e = threadIdx.x; e < p.num_experts; e += kGemmThreads) s_hist[e] = 0;
+    __syncthreads();
+    for (int a = threadIdx.x; a < p.num_assign; a += kGemmThreads) {
+      const long long e = p.ids[a] - p.id_base;
+      if (e >= 0 && e < (long long)p.num_experts) atomicAdd(&s_hist[(int)e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int seg = unit / p.m_tiles;
+      int segs = 0, rows = 0, found = 0;
+      for (int e = 0; e < p.num_experts; ++e) {
+        const int cnt = s_hist[e];
+        const int chunks = (cnt + kSegRows - 1) / kSegRows;
+        if (!found && seg < segs + chunks) {
+          const int done = (seg - segs) * kSegRows;
+          s_unit[0] = e;
+          s_unit[1] = rows + done;
+          s_unit[2] = min(kSegRows, cnt - done);
+          s_unit[4] = done;  // rows of this expert that belong to earlier segments
+          found = 1;
+        }
+        segs += chunks;
+        rows += cnt;
+      }
+      s_unit[3] = found;
+    }
+    __syncthreads();
+    if (!s_unit[3]) {
+      // No such unit in this call.  Leave only after the dependency is resolved: the down
+      // grid may start once every block here has triggered or exited, and it reads the
+      // schedule straight away, so no block may exit while routing could still be running.
+      pdl_wait();
+      return;
+    }
+    expert = s_unit[0];
+    row_start = s_unit[1];
+    n_rows = s_unit[2];
+  } else {
+    if (kGateUp && p.early_mode >= 1) {
+      pdl_wait();  // this grid was started early: the schedule may still be in the making
+      waited = true;
+    }
+    const int n_seg = p.sched[kSchedNumSegments];
+    if (!kGateUp) {
+      n_split = p.sched[kSchedDownSplits];
+      split = unit % n_split;
+      unit /= n_split;
+    }
+    const int seg = unit / p.m_tiles;
+    if (seg >= n_seg) return;
+    const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
+    expert = seg_words[0];
+    row_start = seg_words[1];
+    n_rows = seg_words[2];
   }
   const int tile = unit % p.m_tiles;
-  const int seg = unit / p.m_tiles;
-  if (seg >= n_seg) return;
-
-  const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
-  const int expert = seg_words[0];
-  const int row_start = seg_words[1];
-  const int n_rows = seg_words[2];
   const int n_mma = (n_rows + 15) & ~15;  // accumulator columns: 16..128
+  trace_start(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
+
+  // Few rows: the block also finds the tokens of its rows (the stable order of the
+  // expert's assignments) and loads their activations straight from hidden_states, row
+  // by row, so nothing it needs comes from the routing or gather kernels.
+  const bool direct = own_routing && p.early_mode >= 2 && p.hidden_map_valid &&
+                      n_rows <= kDirectRowsMax;
+  if (direct) {
+    if (warp == 0) {
+      const int skip = s_unit[4];
+      int found = 0;
+      for (int base = 0; base < p.num_assign && found < skip + n_rows; base += 32) {
+        const int a = base + lane;
+        const bool mine = a < p.num_assign && (p.ids[a] - p.id_base) == (long long)expert;
+        const unsigned votes = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int pos = found + __popc(votes & ((1u << lane) - 1u)) - skip;
+          if (pos >= 0 && pos < n_rows) s_tokens[pos] = a / p.top_k;
+        }
+        found += __popc(votes);
+      }
+    }
+    __syncthreads();
+  }
 
   const int kblocks = (p.k_total + kTileK - 1) / kTileK;
   int kb0 = 0, num_kb = kblocks;
@@ -120,6 +203,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   constexpr uint32_t kABytes = kGateUp ? 2u * kTileM * 128u : kTileM * 128u;
   const uint32_t b_bytes = (uint32_t)n_mma * 128u * (kGateUp ? 1u : 2u);
   const uint32_t stage_bytes = kABytes + b_bytes;
+  // bytes one stage receives: row-by-row loads bring only the real rows
+  const uint32_t stage_tx = direct ? kABytes + (uint32_t)n_rows * 128u : stage_bytes;
   const int num_stages = min((int)(p.stage_budget / stage_bytes), kMaxStages);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
@@ -134,6 +219,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     }
   };
 
+  auto load_tokens = [&](uint32_t b_dst, uint32_t bar, int kc) {
+    if (direct) {
+      for (int r = 0; r < n_rows; ++r)
+        tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b1, bar, kc, s_tokens[r]);
+    } else {
+      for (int r = 0; r < n_mma; r += 16) {
+        tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b0, bar, kc, row_start + r);
+        if (!kGateUp)
+          tma_load_2d(b_dst + (uint32_t)(n_mma + r) * 128u, &map_b1, bar, kc, row_start + r);
+      }
+    }
+  };
+
   // ---- weight prefetch: fill the first stages' weight tiles while the previous
   // kernel is still finishing; the token rows of those stages follow after the wait.
   const int prefetched = min(num_stages, num_kb);
@@ -142,13 +240,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       const uint32_t bar = smem_u32(&s_full[i]);
       const uint32_t a_dst = smem_base + (uint32_t)i * stage_bytes;
       const int kc = (kb0 + i) * kTileK;
-      mbar_expect_tx(bar, stage_bytes);
+      mbar_expect_tx(bar, stage_tx);
       load_weights(a_dst, bar, kc);
+      if (direct) load_tokens(a_dst + kABytes, bar, kc);
     }
   }
 
-  pdl_wait();
-  pdl_launch_dependents();
+  // The dependency wait.  A block in direct mode has nothing to wait for before its
+  // main loop; its epilogue warps, idle until the accumulators are complete, do the wait
+  // (and only then let the down grid start, which reads the schedule at once).
+  auto check_own_routing = [&]() {
+    // The routing kernel's schedule is authoritative; a block whose own derivation
+    // disagreed with it would have used the wrong tiles.  Never observed; reported.
+    const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * (unit / p.m_tiles);
+    if (seg_words[0] != expert || seg_words[1] != row_start || seg_words[2] != n_rows)
+      s_abort = 1;
+  };
+  if (!direct) {
+    if (!waited) pdl_wait();
+    pdl_launch_dependents();
+    if (own_routing) check_own_routing();
+  }
 
   // ---- tensor memory ------------------------------------------------------------
   const uint32_t cols_needed = (uint32_t)n_mma * (kGateUp ? 2u : 1u);
@@ -178,14 +290,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         const uint32_t b_dst = a_dst + kABytes;
         const int kc = (kb0 + i) * kTileK;
         if (i >= prefetched) {
-          mbar_expect_tx(bar, stage_bytes);
+          mbar_expect_tx(bar, stage_tx);
           load_weights(a_dst, bar, kc);
         }
-        for (int r = 0; r < n_mma; r += 16) {
-          tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b0, bar, kc, row_start + r);
-          if (!kGateUp)
-            tma_load_2d(b_dst + (uint32_t)(n_mma + r) * 128u, &map_b1, bar, kc, row_start + r);
-        }
+        if (i >= prefetched || !direct) load_tokens(b_dst, bar, kc);
       }
     }
   } else if (warp == 1) {
@@ -201,6 +309,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
           break;
         }
         tc_fence_after_sync();
+        if (i == 0 && p.trace && blockIdx.x == 0)
+          p.trace[2 * (kGateUp ? kTraceGateUpFirstData : kTraceDownFirstData)] = global_timer_ns();
         const uint32_t a_addr = smem_base + (uint32_t)s * stage_bytes;
         const uint32_t b_addr = a_addr + kABytes;
         const uint64_t a0 = umma_smem_desc_sw128(a_addr);
@@ -229,6 +339,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     }
   } else {
     // ===== epilogue: TMEM -> registers -> global =====
+    if (direct) {
+      pdl_wait();
+      pdl_launch_dependents();
+      check_own_routing();
+    }
     const int quarter = warp & 3;
     const int m = tile * kTileM + quarter * 32 + lane;  // weight row of this thread
     const bool m_ok = m < p.m_total;
@@ -287,6 +402,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
+  trace_end(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem, tmem_cols);
@@ -296,6 +412,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
 // Tuning knobs (b200moe_tune): process-wide, meant for benchmarking sweeps.
 int g_gemm_stage_kb = 108;
 int g_gemm_evict_first = 0;
+int g_early_mode = 0;
 static uint32_t gemm_stage_budget() {
   uint32_t b = (uint32_t)g_gemm_stage_kb * 1024u;
   if (b < 48u * 1024u) b = 48u * 1024u;
@@ -333,9 +450,19 @@ static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_
 
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
-                           int inter, int hidden, int rows_cap, int grid, bool pdl,
-                           cudaStream_t stream) {
-  GemmParams p;
+                           int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
+                           int num_assign, int num_experts, int id_base, int top_k,
+                           const CUtensorMap* map_hidden, bool pdl, cudaStream_t stream) {
+  GemmParams p = {};
+  p.ids = ids;
+  p.num_assign = num_assign;
+  p.num_experts = num_experts;
+  p.id_base = id_base;
+  p.top_k = top_k;
+  p.hidden_map_valid = map_hidden != nullptr ? 1 : 0;
+  p.early_mode = g_early_mode;
+  p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
+                                                  kTraceOffsetBytes);
   p.stage_budget = gemm_stage_budget();
   p.evict_first = g_gemm_evict_first;
   p.sched = sched;
@@ -347,16 +474,18 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
   p.k_total = hidden;
   p.m_tiles = (inter + kTileM - 1) / kTileM;
   p.rows_cap = rows_cap;
-  return launch_gemm<true>(map_w, map_x, map_x, p, grid, pdl, stream);
+  return launch_gemm<true>(map_w, map_x, map_hidden ? *map_hidden : map_x, p, grid, pdl, stream);
 }
 
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
                         cudaStream_t stream) {
-  GemmParams p;
+  GemmParams p = {};
   p.stage_budget = gemm_stage_budget();
   p.evict_first = g_gemm_evict_first;
+  p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
+                                                  kTraceOffsetBytes);
   p.sched = sched;
   p.status = status;
   p.act_hi = nullptr;

@@ -55,7 +55,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
                int64_t* __restrict__ perm_tokens, int64_t* __restrict__ perm_experts,
                __nv_bfloat16* __restrict__ perm_weights, int32_t* __restrict__ sched,
                uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas,
-               int id_base, int foreign_ids_allowed) {
+               int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace) {
   __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
   __shared__ int s_cursor[B200MOE_MAX_EXPERTS];
   __shared__ int s_whist[kRoutingWarps][B200MOE_MAX_EXPERTS];
@@ -73,6 +73,10 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   if (tid == 0) {
     s_bad = 0;
     *status = 0u;  // the status word describes the forward this launch begins
+    if (trace) {
+      for (int k = 0; k < kTraceKernels; ++k) trace[2 * k + 1] = 0ull;
+      trace[2 * kTraceRouting] = global_timer_ns();
+    }
   }
   __syncthreads();
 
@@ -183,6 +187,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     // On an expert-parallel rank, ids outside the local range are other ranks' experts.
     if (tid == 0 && !foreign_ids_allowed) atomicOr(status, B200MOE_STATUS_BAD_EXPERT_ID);
   }
+  trace_end(trace, kTraceRouting);
 }
 
 cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assign, int top_k,
@@ -201,7 +206,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
       ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
       offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
-      target_ctas, id_base, foreign_ids_allowed ? 1 : 0);
+      target_ctas, id_base, foreign_ids_allowed ? 1 : 0,
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) + kTraceOffsetBytes));
   return cudaGetLastError();
 }
 

@@ -13,9 +13,14 @@ constexpr int kRowThreads = 256;
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
                    uint4* __restrict__ out, int num_assign, int num_tokens, int top_k,
-                   int vec_per_row) {
+                   int vec_per_row, int early_trigger, unsigned long long* __restrict__ trace) {
+  // early_trigger: let the gate+up grid start right away (its blocks then find their work
+  // from the expert ids themselves); otherwise it starts once routing has completed and
+  // may read the schedule at once.
+  if (early_trigger) pdl_launch_dependents();
   pdl_wait();
-  pdl_launch_dependents();
+  if (!early_trigger) pdl_launch_dependents();
+  trace_start(trace, kTraceGather);
   const int row = blockIdx.x;
   const int64_t a = permutation[row];
   const bool valid = a >= 0 && a < (int64_t)num_assign && (a / top_k) < (int64_t)num_tokens;
@@ -26,6 +31,7 @@ gather_rows_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__
     if (valid) x = __ldg(src + v);
     dst[v] = x;
   }
+  trace_end(trace, kTraceGather);
 }
 
 __device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
@@ -46,9 +52,10 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
                     const __nv_bfloat16* __restrict__ weights, const float* __restrict__ partials,
                     const int32_t* __restrict__ sched, uint4* __restrict__ out,
                     uint4* __restrict__ expert_out, int num_assign, int top_k, int hidden,
-                    size_t slice_elems, int f32_out) {
+                    size_t slice_elems, int f32_out, unsigned long long* __restrict__ trace) {
   pdl_wait();
   pdl_launch_dependents();
+  trace_start(trace, kTraceCombine);
   const int token = blockIdx.x;
   const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (col >= hidden) return;
@@ -107,6 +114,7 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
   } else {
     out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
   }
+  trace_end(trace, kTraceCombine);
 }
 
 static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void** args,
@@ -125,12 +133,15 @@ static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void
 }
 
 cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
-                          int num_assign, int num_tokens, int top_k, int hidden_size, bool pdl,
+                          int num_assign, int num_tokens, int top_k, int hidden_size,
+                          bool early_trigger, unsigned long long* trace, bool pdl,
                           cudaStream_t stream) {
   int vec_per_row = hidden_size / 8;
   const uint4* h = static_cast<const uint4*>(hidden);
   uint4* o = static_cast<uint4*>(out);
-  void* args[] = {&h, &permutation, &o, &num_assign, &num_tokens, &top_k, &vec_per_row};
+  int early = early_trigger ? 1 : 0;
+  void* args[] = {&h, &permutation, &o, &num_assign, &num_tokens, &top_k, &vec_per_row, &early,
+                  &trace};
   return launch_with_pdl(reinterpret_cast<const void*>(&gather_rows_kernel), dim3(num_assign),
                          dim3(kRowThreads), args, pdl, stream);
 }
@@ -138,14 +149,15 @@ cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* 
 cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
                            const float* partials, const int32_t* sched, void* out,
                            void* expert_out, int num_tokens, int top_k, int hidden_size,
-                           size_t slice_elems, bool f32_out, bool pdl, cudaStream_t stream) {
+                           size_t slice_elems, bool f32_out, unsigned long long* trace, bool pdl,
+                           cudaStream_t stream) {
   int num_assign = num_tokens * top_k;
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weights);
   uint4* o = static_cast<uint4*>(out);
   uint4* eo = static_cast<uint4*>(expert_out);
   int f32 = f32_out ? 1 : 0;
   void* args[] = {&reverse_mapping, &w, &partials, &sched, &o, &eo, &num_assign, &top_k,
-                  &hidden_size, &slice_elems, &f32};
+                  &hidden_size, &slice_elems, &f32, &trace};
   const int vecs = hidden_size / 8;
   dim3 grid(num_tokens, (vecs + 127) / 128);
   return launch_with_pdl(reinterpret_cast<const void*>(&combine_rows_kernel), grid, dim3(128),

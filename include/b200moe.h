@@ -293,10 +293,15 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              1 = 128 B, 2 = 256 B (default)
  *   B200MOE_TUNE_EVICT_FIRST   1: weight tiles are loaded with an L2
  *                              evict-first hint (default 0)
+ *   B200MOE_TUNE_EARLY_START   how early the gate+up grid starts: 0 after routing
+ *                              (default), 1 at once, each block deriving its work
+ *                              unit from the expert ids itself, 2 as 1 and blocks
+ *                              with <= 32 rows also fetch their token rows themselves
  */
 #define B200MOE_TUNE_STAGE_KB     1
 #define B200MOE_TUNE_L2_PROMOTION 2
 #define B200MOE_TUNE_EVICT_FIRST  3
+#define B200MOE_TUNE_EARLY_START  4
 int b200moe_tune(int knob, int value);
 
 #ifdef __cplusplus
