@@ -52,7 +52,7 @@ METRIC = "moe_layer_decode_p50_us_mean_over_T1_2_4_8_16_32_64"
 
 # The default (and the only configuration the driver's line is quoted on) is the
 # Mixtral-shaped sweep.  The others are the remaining benchmark configurations, run by
-# hand with --config for the numbers recorded in DESIGN.md / profiles/.
+# hand with --config.
 CONFIGS = {
     "mixtral": dict(hidden=4096, inter=14336, experts=8, top_k=2, sweep=(1, 2, 4, 8, 16, 32, 64),
                     routing="uniform", weight_kind="softmax"),

@@ -356,3 +356,37 @@ def test_router_then_layer_end_to_end(cuda_device) -> None:
     ref, _ = moe_oracle.routed_moe(hidden.cpu(), ref_ids, ref_w, gate_up.cpu(), down.cpu(),
                                    num_experts=E, top_k=K)
     assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2
+
+
+def test_early_start_modes_agree_bitwise_and_timeline_is_ordered(cuda_device) -> None:
+    """The three ways the gate+up grid can start (after routing; at once with its own
+    derivation of the work units; additionally fetching its token rows itself) are
+    scheduling choices only: outputs are bit-identical.  The in-kernel timeline reports the
+    five kernels in dependency order."""
+
+    from b200moe import B300MoEWorkspace, _lib, b300_moe_forward, workloads
+
+    lib = _lib.load()
+    cases = [
+        workloads.make_case(5, 512, 768, 16, 4, routing="zipf", std=None, device=cuda_device),
+        workloads.make_case(64, 256, 384, 8, 8, routing="concentrated", std=None,
+                            device=cuda_device),  # 64 rows per expert: above the own-rows limit
+    ]
+    try:
+        for tensors in cases:
+            E, K = tensors[3].shape[0], tensors[1].shape[1]
+            outputs = []
+            for mode in (0, 1, 2):
+                assert lib.b200moe_tune(_lib.TUNE_EARLY_START, mode) == 0
+                workspace = B300MoEWorkspace(device=cuda_device)
+                outputs.append(b300_moe_forward(*tensors, num_experts=E, top_k=K,
+                                                workspace=workspace, check_status=True))
+                timeline = workspace.timeline()
+                assert set(timeline) >= {"routing", "gather", "gate_up", "down", "combine"}
+                assert timeline["routing"][0] == 0.0
+                assert timeline["gate_up"][1] <= timeline["down"][1] <= timeline["combine"][1]
+                assert timeline["down_first_data"][0] >= timeline["gate_up"][1]
+                assert 0.0 < timeline["combine"][1] < 1e5
+            assert torch.equal(outputs[0], outputs[1]) and torch.equal(outputs[0], outputs[2])
+    finally:
+        lib.b200moe_tune(_lib.TUNE_EARLY_START, 0)
