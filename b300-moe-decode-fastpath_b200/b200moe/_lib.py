@@ -16,7 +16,7 @@ from pathlib import Path
 from typing import Mapping
 
 LIBRARY_NAME = "libb200moe.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 STATUS_BAD_EXPERT_ID = 0x1
 STATUS_PIPE_TIMEOUT = 0x2
@@ -46,6 +46,7 @@ EXPORTS = (
     "b200moe_combine",
     "b200moe_forward",
     "b200moe_ep_reduce",
+    "b200moe_ep_push",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
     "b200moe_tune",
@@ -84,6 +85,10 @@ class B200MoeArgs(ctypes.Structure):
         ("output", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
         ("expert_id_base", ctypes.c_int32),
+        ("ep_wait_flags", ctypes.c_void_p),
+        ("ep_world", ctypes.c_int32),
+        ("ep_epoch", ctypes.c_uint32),
+        ("ep_wait_limit_us", ctypes.c_uint32),
     ]
 
 
@@ -102,6 +107,27 @@ class B200MoeEpReduceArgs(ctypes.Structure):
         ("output", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
+    ]
+
+
+class B200MoeEpPushArgs(ctypes.Structure):
+    """Mirror of ``struct B200MoeEpPushArgs`` in include/b200moe.h."""
+
+    _fields_ = [
+        ("hidden_states", ctypes.c_void_p),
+        ("expert_indices", ctypes.c_void_p),
+        ("expert_weights", ctypes.c_void_p),
+        ("hidden_dst", ctypes.POINTER(ctypes.c_void_p)),
+        ("indices_dst", ctypes.POINTER(ctypes.c_void_p)),
+        ("weights_dst", ctypes.POINTER(ctypes.c_void_p)),
+        ("flag_ptrs", ctypes.POINTER(ctypes.c_void_p)),
+        ("block_counter", ctypes.c_void_p),
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("tokens_local", ctypes.c_int32),
+        ("top_k", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32),
     ]
 
 
@@ -142,6 +168,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.argtypes = [args_p, ctypes.c_void_p]
     lib.b200moe_ep_reduce.restype = ctypes.c_int
     lib.b200moe_ep_reduce.argtypes = [ctypes.POINTER(B200MoeEpReduceArgs), ctypes.c_void_p]
+    lib.b200moe_ep_push.restype = ctypes.c_int
+    lib.b200moe_ep_push.argtypes = [ctypes.POINTER(B200MoeEpPushArgs), ctypes.c_void_p]
     lib.b200moe_status_ptr.restype = ctypes.c_int
     lib.b200moe_status_ptr.argtypes = [
         ctypes.c_void_p,

@@ -134,9 +134,61 @@ class ExpertParallelMoE:
             for parity in (0, 1)
         ]
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in flag_handle.buffer_ptrs])
-        self._handles = (partial_handle, flag_handle)
+        # dispatch of sharded tokens: gathered activations / ids / weights, two sets
+        cap, H, K = self.capacity_tokens, self.hidden_size, self.top_k
+        self._g_hidden = symm_mem.empty((2, cap, H), dtype=torch.bfloat16, device=device)
+        self._g_ids = symm_mem.empty((2, cap, K), dtype=torch.int64, device=device)
+        self._g_weights = symm_mem.empty((2, cap, K), dtype=torch.bfloat16, device=device)
+        self._g_flags = symm_mem.empty((_lib.EP_MAX_WORLD,), dtype=torch.int32, device=device)
+        self._g_flags.zero_()
+        self._push_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        handles = [symm_mem.rendezvous(t, group)
+                   for t in (self._g_hidden, self._g_ids, self._g_weights, self._g_flags)]
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
+        self._g_ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
+        self._handles = (partial_handle, flag_handle, *handles)
 
-    def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype) -> torch.Tensor:
+    def _peer_dispatch(self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor):
+        """Store this rank's token shard into every rank's gathered buffers (one launch of
+        peer stores plus a flag), and return this rank's gathered views and the wait tuple
+        for the routing kernel."""
+
+        t_local = hidden.shape[0]
+        total = t_local * self.world
+        if total > self.capacity_tokens:
+            raise ValueError(
+                f"{total} tokens exceed the peer buffers' capacity ({self.capacity_tokens})")
+        parity = self._epoch & 1
+        cap, H, K = self.capacity_tokens, self.hidden_size, self.top_k
+        row_bytes = (H * 2, K * 8, K * 2)
+        arrays = []
+        for which in range(3):
+            set_bytes = cap * row_bytes[which]
+            offset = parity * set_bytes + self.rank * t_local * row_bytes[which]
+            arrays.append((ctypes.c_void_p * self.world)(
+                *[base + offset for base in self._g_ptrs[which]]))
+        flag_array = (ctypes.c_void_p * self.world)(*self._g_ptrs[3])
+        args = _lib.B200MoeEpPushArgs()
+        args.hidden_states = hidden.data_ptr()
+        args.expert_indices = ids.data_ptr()
+        args.expert_weights = weights.data_ptr()
+        cast = lambda a: ctypes.cast(a, ctypes.POINTER(ctypes.c_void_p))  # noqa: E731
+        args.hidden_dst, args.indices_dst, args.weights_dst = (cast(a) for a in arrays)
+        args.flag_ptrs = cast(flag_array)
+        args.block_counter = self._push_counter.data_ptr()
+        args.world, args.rank = self.world, self.rank
+        args.tokens_local, args.top_k, args.hidden_size = t_local, K, H
+        args.epoch = self._epoch & 0xFFFFFFFF
+        code = _enqueue(_lib.load().b200moe_ep_push, args, hidden.device)
+        if code:
+            _lib.check(code, "b200moe_ep_push")
+        gathered = (self._g_hidden[parity][:total], self._g_ids[parity][:total],
+                    self._g_weights[parity][:total])
+        return gathered, (self._g_flags.data_ptr(), self.world, self._epoch & 0xFFFFFFFF)
+
+    def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype,
+                     first_token: int = 0) -> torch.Tensor:
         """One launch: publish, wait for the peers (bounded), add the ranks' partial outputs
         in rank order over NVLink, round to BF16."""
 
@@ -144,7 +196,11 @@ class ExpertParallelMoE:
         device = self.gate_up.device
         output = torch.empty(tokens, self.hidden_size, dtype=dtype, device=device)
         args = _lib.B200MoeEpReduceArgs()
-        args.partial_ptrs = ctypes.cast(self._partial_ptrs[parity], ctypes.POINTER(ctypes.c_void_p))
+        partial_ptrs = self._partial_ptrs[parity]
+        if first_token:
+            skip = first_token * self.hidden_size * 4
+            partial_ptrs = (ctypes.c_void_p * self.world)(*[int(p) + skip for p in partial_ptrs])
+        args.partial_ptrs = ctypes.cast(partial_ptrs, ctypes.POINTER(ctypes.c_void_p))
         args.flag_ptrs = ctypes.cast(self._flag_ptrs, ctypes.POINTER(ctypes.c_void_p))
         args.world, args.rank = self.world, self.rank
         args.num_tokens, args.hidden_size = tokens, self.hidden_size
@@ -160,7 +216,8 @@ class ExpertParallelMoE:
 
     # ------------------------------------------------------------------ local compute
     def _native_local_forward(
-        self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
+        self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+        ep_wait: tuple[int, int, int] | None = None,
     ) -> torch.Tensor:
         """FP32 ``[T,H]`` sum over this rank's assignments, by the sm_100a kernels."""
 
@@ -178,7 +235,7 @@ class ExpertParallelMoE:
         partial, call = local_partial_forward(
             hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
             expert_id_base=self.base, num_experts_global=self.num_experts,
-            workspace=self.workspace, use_pdl=self.use_pdl, out=out,
+            workspace=self.workspace, use_pdl=self.use_pdl, out=out, ep_wait=ep_wait,
         )
         self._last_call = call
         return partial
@@ -232,7 +289,14 @@ class ExpertParallelMoE:
         if expert_indices.shape[1] != self.top_k:
             raise ValueError("top_k must match expert_indices.shape[1]")
         local_tokens = hidden_states.shape[0]
-        if tokens == "sharded" and self.world > 1:
+        self._epoch += 1
+        sharded = tokens == "sharded" and self.world > 1
+        ep_wait = None
+        if sharded and self.transport == "p2p":
+            (hidden_all, ids_all, weights_all), ep_wait = self._peer_dispatch(
+                hidden_states.contiguous(), expert_indices.contiguous(),
+                expert_weights.contiguous())
+        elif sharded:
             hidden_all = self._all_gather(hidden_states)
             ids_all = self._all_gather(expert_indices)
             weights_all = self._all_gather(expert_weights)
@@ -240,15 +304,19 @@ class ExpertParallelMoE:
             hidden_all, ids_all, weights_all = hidden_states, expert_indices, expert_weights
         self.last_tokens = hidden_all.shape[0]
 
-        self._epoch += 1
-        partial = self._local_forward(hidden_all, ids_all, weights_all)
-        if self.transport == "p2p":
-            output = self._peer_reduce(hidden_all.shape[0], self._epoch & 1, hidden_states.dtype)
+        if ep_wait is not None:
+            partial = self._local_forward(hidden_all, ids_all, weights_all, ep_wait=ep_wait)
         else:
-            if self.world > 1:
-                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-            output = partial.to(hidden_states.dtype)
-        if tokens == "sharded" and self.world > 1:
+            partial = self._local_forward(hidden_all, ids_all, weights_all)
+        if self.transport == "p2p":
+            # a sharded caller only needs its own rows: reduce that slice of every partial
+            first = self.rank * local_tokens if sharded else 0
+            rows = local_tokens if sharded else hidden_all.shape[0]
+            return self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first)
+        if self.world > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        output = partial.to(hidden_states.dtype)
+        if sharded:
             output = output[self.rank * local_tokens:(self.rank + 1) * local_tokens]
         return output
 
@@ -298,6 +366,7 @@ def local_partial_forward(
     workspace: B300MoEWorkspace,
     use_pdl: bool = True,
     out: torch.Tensor | None = None,
+    ep_wait: tuple[int, int, int] | None = None,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -330,6 +399,10 @@ def local_partial_forward(
             flags |= _lib.FLAG_PDL
         args = _native_args(hidden, ids, weights, gate_up_local, down_local, shape, workspace,
                             partial, flags, expert_id_base=expert_id_base)
+        if ep_wait is not None:
+            # (device address of this rank's dispatch flags, world size, epoch): the routing
+            # kernel waits for every rank's pushed shard before it reads ids or rows
+            args.ep_wait_flags, args.ep_world, args.ep_epoch = ep_wait
         code = _enqueue(_lib.load().b200moe_forward, args, hidden.device)
         if code:
             _lib.check(code, "b200moe_forward (expert-parallel rank)")

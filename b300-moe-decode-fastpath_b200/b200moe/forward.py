@@ -153,6 +153,10 @@ def _native_args(
     args.output = output.data_ptr()
     args.flags = flags
     args.expert_id_base = expert_id_base
+    args.ep_wait_flags = None  # expert-parallel callers set these after this call
+    args.ep_world = 0
+    args.ep_epoch = 0
+    args.ep_wait_limit_us = 0
     return args
 
 

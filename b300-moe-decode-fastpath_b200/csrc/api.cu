@@ -19,7 +19,13 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, int id_base, bool foreign_ids_allowed,
-                           cudaStream_t stream);
+                           const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
+                           unsigned long long wait_limit_ns, cudaStream_t stream);
+cudaError_t launch_ep_push(const void* hidden, const int64_t* ids, const void* weights,
+                           void* const* hidden_dst, void* const* ids_dst,
+                           void* const* weights_dst, void* const* flag_ptrs,
+                           unsigned int* block_counter, int world, int rank, int tokens_local,
+                           int top_k, int hidden_size, uint32_t epoch, cudaStream_t stream);
 cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int num_assign,
                                   int top_k, int num_experts, int64_t* counts, int64_t* offsets,
                                   int64_t* reverse_mapping, int64_t* permutation,
@@ -189,7 +195,12 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              a->permuted_token_indices, a->permuted_expert_indices,
                              a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
                              (a->intermediate_size + 63) / 64, 2 * dev.sm_count,
-                             local ? a->expert_id_base : 0, local, stream);
+                             local ? a->expert_id_base : 0, local,
+                             static_cast<const uint32_t*>(a->ep_wait_flags), a->ep_world,
+                             a->ep_epoch,
+                             (a->ep_wait_limit_us ? (unsigned long long)a->ep_wait_limit_us
+                                                  : 1000000ull) * 1000ull,
+                             stream);
 }
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
@@ -268,6 +279,8 @@ int prepare(const B200MoeArgs* a, void* stream, Ctx* c) {
                        a->intermediate_size, (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0);
   if (rc) return rc;
   if ((a->flags & B200MOE_FLAG_LOCAL_EXPERTS) && a->expert_id_base < 0) return B200MOE_E_SHAPE;
+  if (a->ep_wait_flags && (a->ep_world < 1 || a->ep_world > B200MOE_EP_MAX_WORLD))
+    return B200MOE_E_SHAPE;
   c->assignments = a->num_tokens * a->top_k;
   if (a->rows_cap < c->assignments) return B200MOE_E_SHAPE;
   rc = current_device_info(&c->dev);
@@ -302,7 +315,7 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
     return B200MOE_E_ALIGN;
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
-                    a->expert_indices,
+                    a->ep_wait_flags ? nullptr : a->expert_indices,
                     (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) ? a->expert_id_base : 0, a->top_k,
                     a->hidden_states, pdl, c.stream);
 }
@@ -496,6 +509,28 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
                                a->hidden_size, a->epoch, limit_ns, a->output, a->status,
                                (a->flags & B200MOE_FLAG_PDL) != 0,
                                static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_push(const B200MoeEpPushArgs* a, void* stream) {
+  if (!a || !a->hidden_states || !a->expert_indices || !a->expert_weights || !a->hidden_dst ||
+      !a->indices_dst || !a->weights_dst || !a->flag_ptrs || !a->block_counter)
+    return B200MOE_E_NULL;
+  if (a->world < 1 || a->world > B200MOE_EP_MAX_WORLD || a->rank < 0 || a->rank >= a->world ||
+      a->tokens_local < 1 || a->top_k < 1 || a->hidden_size < 8)
+    return B200MOE_E_SHAPE;
+  if (a->hidden_size % 8 || !aligned16(a->hidden_states)) return B200MOE_E_ALIGN;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->hidden_dst[r] || !a->indices_dst[r] || !a->weights_dst[r] || !a->flag_ptrs[r])
+      return B200MOE_E_NULL;
+    if (!aligned16(a->hidden_dst[r])) return B200MOE_E_ALIGN;
+  }
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_ep_push(a->hidden_states, a->expert_indices, a->expert_weights,
+                             a->hidden_dst, a->indices_dst, a->weights_dst, a->flag_ptrs,
+                             a->block_counter, a->world, a->rank, a->tokens_local, a->top_k,
+                             a->hidden_size, a->epoch, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_forward(const B200MoeArgs* a, void* stream) {

@@ -122,4 +122,94 @@ cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_
   return cudaLaunchKernelEx(&cfg, ep_reduce_kernel, p);
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel dispatch of sharded tokens: every rank stores its T/N token rows,
+// expert ids and routing weights into slot `rank` of every rank's gathered buffers
+// (peer stores over NVLink), and the block that finishes last publishes the epoch into
+// flags[rank] of every rank.  The consumer is the routing kernel of the same forward,
+// which waits (bounded) until its own flag array shows the epoch for every rank.
+// One launch replaces three all-gathers.
+// ---------------------------------------------------------------------------
+struct EpPushParams {
+  const uint4* hidden;        // this rank's [T_local, H] bf16 as 16-byte vectors
+  const int64_t* ids;         // this rank's [T_local, K]
+  const uint16_t* weights;    // this rank's [T_local, K] bf16 bit patterns
+  uint4* hidden_dst[kMaxEpWorld];     // slot `rank` inside rank r's gathered hidden buffer
+  int64_t* ids_dst[kMaxEpWorld];
+  uint16_t* weights_dst[kMaxEpWorld];
+  uint32_t* flags[kMaxEpWorld];       // rank r's dispatch flag array uint32[world]
+  unsigned int* block_counter;        // local, zero between launches
+  int world, rank;
+  int hidden_vecs, id_count;          // T_local*H/8 vectors, T_local*K ids (= weights)
+  uint32_t epoch;
+};
+
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const EpPushParams p) {
+  __shared__ int s_is_last;
+  pdl_launch_dependents();
+  const int stride = gridDim.x * blockDim.x;
+  const int first = blockIdx.x * blockDim.x + threadIdx.x;
+  for (int v = first; v < p.hidden_vecs; v += stride) {
+    const uint4 x = __ldg(p.hidden + v);
+#pragma unroll
+    for (int r = 0; r < kMaxEpWorld; ++r)
+      if (r < p.world) p.hidden_dst[r][v] = x;
+  }
+  for (int i = first; i < p.id_count; i += stride) {
+    const int64_t id = p.ids[i];
+    const uint16_t w = p.weights[i];
+#pragma unroll
+    for (int r = 0; r < kMaxEpWorld; ++r) {
+      if (r < p.world) {
+        p.ids_dst[r][i] = id;
+        p.weights_dst[r][i] = w;
+      }
+    }
+  }
+  // The last block to get here knows that every block's stores were issued and fenced.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(p.block_counter, 1u);
+    s_is_last = (done == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_is_last) {
+    if (threadIdx.x == 0) *p.block_counter = 0u;
+    if (threadIdx.x < p.world) {
+      __threadfence_system();
+      st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
+    }
+  }
+}
+
+cudaError_t launch_ep_push(const void* hidden, const int64_t* ids, const void* weights,
+                           void* const* hidden_dst, void* const* ids_dst,
+                           void* const* weights_dst, void* const* flag_ptrs,
+                           unsigned int* block_counter, int world, int rank, int tokens_local,
+                           int top_k, int hidden_size, uint32_t epoch, cudaStream_t stream) {
+  EpPushParams p = {};
+  p.hidden = static_cast<const uint4*>(hidden);
+  p.ids = ids;
+  p.weights = static_cast<const uint16_t*>(weights);
+  for (int r = 0; r < world; ++r) {
+    p.hidden_dst[r] = static_cast<uint4*>(hidden_dst[r]);
+    p.ids_dst[r] = static_cast<int64_t*>(ids_dst[r]);
+    p.weights_dst[r] = static_cast<uint16_t*>(weights_dst[r]);
+    p.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  p.block_counter = block_counter;
+  p.world = world;
+  p.rank = rank;
+  p.hidden_vecs = tokens_local * (hidden_size / 8);
+  p.id_count = tokens_local * top_k;
+  p.epoch = epoch;
+  int blocks = (p.hidden_vecs + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 64) blocks = 64;
+  ep_push_kernel<<<blocks, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 }  // namespace b200moe

@@ -55,7 +55,9 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
                int64_t* __restrict__ perm_tokens, int64_t* __restrict__ perm_experts,
                __nv_bfloat16* __restrict__ perm_weights, int32_t* __restrict__ sched,
                uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas,
-               int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace) {
+               int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace,
+               const uint32_t* __restrict__ wait_flags, int wait_world, uint32_t wait_epoch,
+               unsigned long long wait_limit_ns) {
   __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
   __shared__ int s_cursor[B200MOE_MAX_EXPERTS];
   __shared__ int s_whist[kRoutingWarps][B200MOE_MAX_EXPERTS];
@@ -64,6 +66,37 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int threads = blockDim.x, num_warps = blockDim.x >> 5;
+  __shared__ int s_peers_ready;
+
+  // Expert parallel with sharded tokens: the ids, weights and token rows of the other
+  // ranks arrive by peer stores; wait (bounded) until every rank has published this
+  // forward's epoch.  If a peer never arrives the call routes nothing and reports it.
+  if (wait_flags) {
+    if (tid == 0) s_peers_ready = 1;
+    __syncthreads();
+    if (tid < wait_world) {
+      const uint64_t t0 = global_timer_ns();
+      while (true) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(wait_flags + tid) : "memory");
+        if ((int32_t)(seen - wait_epoch) >= 0) break;
+        if (global_timer_ns() - t0 > wait_limit_ns) {
+          s_peers_ready = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+    if (!s_peers_ready) {
+      // route nothing: every assignment is marked dropped, so the combine adds nothing
+      for (int a = tid; a < num_assign; a += threads) {
+        reverse_mapping[a] = -1;
+        permutation[a] = -1;
+      }
+      num_assign = 0;
+    }
+  }
 
   // Everything the next kernel needs from this one is written before this grid
   // completes, and it waits for completion; let its launch overlap this one.
@@ -72,7 +105,8 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   if (tid < B200MOE_MAX_EXPERTS) s_cnt[tid] = 0;
   if (tid == 0) {
     s_bad = 0;
-    *status = 0u;  // the status word describes the forward this launch begins
+    // the status word describes the forward this launch begins
+    *status = (wait_flags && !s_peers_ready) ? B200MOE_STATUS_PEER_TIMEOUT : 0u;
     if (trace) {
       for (int k = 0; k < kTraceKernels; ++k) trace[2 * k + 1] = 0ull;
       trace[2 * kTraceRouting] = global_timer_ns();
@@ -196,7 +230,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, int id_base, bool foreign_ids_allowed,
-                           cudaStream_t stream) {
+                           const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
+                           unsigned long long wait_limit_ns, cudaStream_t stream) {
   // One thread per expert and per assignment of a round, in whole warps; fewer warps make
   // the block-wide barriers of a decode-sized call cheaper.
   int threads = num_assign > num_experts ? num_assign : num_experts;
@@ -207,7 +242,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
       offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
       target_ctas, id_base, foreign_ids_allowed ? 1 : 0,
-      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) + kTraceOffsetBytes));
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) + kTraceOffsetBytes),
+      wait_flags, wait_world, wait_epoch, wait_limit_ns);
   return cudaGetLastError();
 }
 
@@ -275,7 +311,7 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
                         reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
                         perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
                         reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas, 0,
-                        false, stream);
+                        false, nullptr, 0, 0u, 0ull, stream);
 }
 
 }  // namespace b200moe

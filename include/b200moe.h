@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 /* host-side contract errors */
 #define B200MOE_E_NULL        (-1)  /* a required pointer is NULL */
@@ -122,6 +122,13 @@ typedef struct B200MoeArgs {
   void*    output;                   /* [T,H] bf16 (fp32 with B200MOE_FLAG_F32_OUTPUT) */
   uint32_t flags;                    /* B200MOE_FLAG_* */
   int32_t  expert_id_base;           /* first global expert id of this rank (B200MOE_FLAG_LOCAL_EXPERTS) */
+  /* Expert parallel with sharded tokens: when ep_wait_flags is non-NULL the routing kernel
+   * first waits (at most ep_wait_limit_us, 0 = 1 s) until ep_wait_flags[r] >= ep_epoch for
+   * r < ep_world, i.e. until every rank's b200moe_ep_push of this forward has landed. */
+  const void* ep_wait_flags;         /* uint32[ep_world] on this device, or NULL */
+  int32_t  ep_world;
+  uint32_t ep_epoch;
+  uint32_t ep_wait_limit_us;
 } B200MoeArgs;
 
 /*
@@ -251,6 +258,34 @@ typedef struct B200MoeEpReduceArgs {
 #define B200MOE_EP_MAX_WORLD 8
 
 int b200moe_ep_reduce(const B200MoeEpReduceArgs* args, void* stream);
+
+/*
+ * Expert-parallel dispatch of sharded tokens over NVLink peer memory.  No counterpart
+ * in the reference.  Every rank holds T/N tokens; one launch stores this rank's token
+ * rows, expert ids and routing weights into slot `rank` of every rank's gathered
+ * buffers (plain peer stores) and then publishes `epoch` into flags[rank] of every rank.
+ * The consumer is the b200moe_forward of the same layer call with ep_wait_flags set.
+ *   hidden_dst[r] / indices_dst[r] / weights_dst[r]   device pointers, valid on THIS device,
+ *       to where this rank's shard goes inside rank r's gathered [T,H] / [T,K] / [T,K] buffers
+ *   flag_ptrs[r]      rank r's dispatch flag array uint32[world]
+ *   block_counter     one zero-initialised uint32 in this device's memory
+ * The pointer arrays are read on the host.  Alternate two sets of gathered buffers by
+ * epoch parity so a fast rank never overwrites what a slow rank still reads.
+ */
+typedef struct B200MoeEpPushArgs {
+  const void*    hidden_states;      /* [T_local,H] bf16 */
+  const int64_t* expert_indices;     /* [T_local,K] */
+  const void*    expert_weights;     /* [T_local,K] bf16 */
+  void* const*   hidden_dst;
+  void* const*   indices_dst;
+  void* const*   weights_dst;
+  void* const*   flag_ptrs;
+  unsigned int*  block_counter;
+  int32_t  world, rank, tokens_local, top_k, hidden_size;
+  uint32_t epoch;
+} B200MoeEpPushArgs;
+
+int b200moe_ep_push(const B200MoeEpPushArgs* args, void* stream);
 
 /*
  * Device address of the 32-bit status word inside a scratch region, so a

@@ -390,3 +390,74 @@ def test_early_start_modes_agree_bitwise_and_timeline_is_ordered(cuda_device) ->
             assert torch.equal(outputs[0], outputs[1]) and torch.equal(outputs[0], outputs[2])
     finally:
         lib.b200moe_tune(_lib.TUNE_EARLY_START, 0)
+
+
+def test_peer_dispatch_kernel_and_routing_wait_on_one_gpu(cuda_device) -> None:
+    """Sharded-token dispatch with both "ranks'" buffers on this GPU: the push kernel lands
+    this rank's shard in slot `rank` of every gathered buffer and publishes its flag; the
+    forward waits on the flags, and a flag nothing sets ends the wait with a status bit and
+    an all-zero result instead of a hang."""
+
+    import ctypes
+
+    from b200moe import B300MoEWorkspace, _lib, workloads
+    from b200moe.expert_parallel import local_partial_forward
+
+    world, rank, t_local, H, I, E, K = 2, 1, 3, 128, 192, 8, 2
+    total = world * t_local
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        total, H, I, E, K, std=None, device=cuda_device)
+    mine = slice(rank * t_local, (rank + 1) * t_local)
+    g_hidden = [torch.zeros(total, H, dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    g_ids = [torch.full((total, K), -1, dtype=torch.int64, device=cuda_device) for _ in range(world)]
+    g_w = [torch.zeros(total, K, dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+
+    def ptrs(tensors, row_bytes):
+        return (ctypes.c_void_p * world)(*[t.data_ptr() + rank * t_local * row_bytes
+                                           for t in tensors])
+
+    args = _lib.B200MoeEpPushArgs()
+    srcs = (hidden[mine].contiguous(), ids[mine].contiguous(), weights[mine].contiguous())
+    args.hidden_states, args.expert_indices, args.expert_weights = (t.data_ptr() for t in srcs)
+    keep = (ptrs(g_hidden, H * 2), ptrs(g_ids, K * 8), ptrs(g_w, K * 2),
+            (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags]))
+    cast = lambda a: ctypes.cast(a, ctypes.POINTER(ctypes.c_void_p))  # noqa: E731
+    args.hidden_dst, args.indices_dst, args.weights_dst, args.flag_ptrs = (cast(a) for a in keep)
+    args.block_counter = counter.data_ptr()
+    args.world, args.rank, args.tokens_local, args.top_k, args.hidden_size = world, rank, t_local, K, H
+    args.epoch = 7
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+    _lib.check(_lib.load().b200moe_ep_push(ctypes.byref(args), stream), "b200moe_ep_push")
+    torch.cuda.synchronize(cuda_device)
+    for r in range(world):
+        assert torch.equal(g_hidden[r][mine], hidden[mine])
+        assert torch.equal(g_ids[r][mine], ids[mine])
+        assert torch.equal(g_w[r][mine], weights[mine])
+        assert int(g_ids[r][: rank * t_local].max()) == -1  # other slots untouched
+        assert int(flags[r][rank]) == 7
+    assert int(counter.item()) == 0
+
+    # the consumer: rank 1's forward over the gathered inputs waits on its own flag array
+    g_hidden[rank].copy_(hidden)
+    g_ids[rank].copy_(ids)
+    g_w[rank].copy_(weights)
+    workspace = B300MoEWorkspace(device=cuda_device)
+    wait = (flags[rank].data_ptr(), world, 7)
+    partial, (native_args, _) = local_partial_forward(
+        g_hidden[rank], g_ids[rank], g_w[rank], gate_up, down, top_k=K, expert_id_base=0,
+        num_experts_global=E, workspace=workspace, ep_wait=wait)
+    # rank 0 never published: bounded wait (default 1 s), status bit, nothing routed
+    torch.cuda.synchronize(cuda_device)
+    assert workspace.status() & 0x4
+    assert float(partial.abs().max()) == 0.0
+    flags[rank][0] = 7  # now "rank 0" has arrived
+    partial, _ = local_partial_forward(
+        g_hidden[rank], g_ids[rank], g_w[rank], gate_up, down, top_k=K, expert_id_base=0,
+        num_experts_global=E, workspace=workspace, ep_wait=wait)
+    torch.cuda.synchronize(cuda_device)
+    assert workspace.status() == 0
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
+                                   down.cpu(), num_experts=E, top_k=K)
+    assert moe_oracle.relative_max_error(partial.to(torch.bfloat16).float().cpu(), ref) <= 2e-2
