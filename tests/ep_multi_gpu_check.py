@@ -1,0 +1,76 @@
+"""Multi-GPU check of the expert-parallel layer, run under torchrun (one rank per GPU).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29533 tests/ep_multi_gpu_check.py
+
+Every rank builds the same seeded problem, keeps its experts' weights, runs the layer with
+both token layouts (replicated, sharded) and both transports (NCCL baseline, NVLink peer
+memory) and compares with the CPU oracle of the whole layer; the assembled routing tensors
+must be bit-exact against the single-rank ones.  Prints one line per rank, "EP_CHECK_OK".
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+REPO = Path(__file__).resolve().parent.parent
+for entry in (str(REPO / "b300-moe-decode-fastpath_b200"), str(REPO)):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+
+def main() -> int:
+    from b200moe import workloads
+    from b200moe.expert_parallel import ExpertParallelMoE, expert_range
+    from oracle import moe_oracle
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    try:
+        T, H, I, E, K = 8 * world, 512, 768, 8 * world, 4
+        hidden, ids, weights, gate_up, down = workloads.make_case(
+            T, H, I, E, K, routing="zipf", weight_kind="raw", std=None, seed=321)
+        ref, routing = moe_oracle.routed_moe(hidden, ids, weights, gate_up, down,
+                                             num_experts=E, top_k=K)
+        base, count = expert_range(rank, world, E)
+        gu = gate_up[base:base + count].to(device).contiguous()
+        dn = down[base:base + count].to(device).contiguous()
+        dev = tuple(t.to(device) for t in (hidden, ids, weights))
+        per = T // world
+        mine = slice(rank * per, (rank + 1) * per)
+        shard = tuple(t[mine].contiguous() for t in dev)
+        worst = 0.0
+        for transport in ("nccl", "p2p"):
+            layer = ExpertParallelMoE(gu, dn, num_experts=E, top_k=K, capacity_tokens=T,
+                                      transport=transport)
+            for repeat in range(3):  # several epochs: both buffer parities, flag reuse
+                out = layer.forward(*dev, tokens="replicated")
+                err = moe_oracle.relative_max_error(out.float().cpu(), ref)
+                assembled = layer.global_routing()
+                for key in ("expert_counts", "expert_offsets", "permutation", "reverse_mapping"):
+                    assert np.array_equal(assembled[key].cpu().numpy(), getattr(routing, key)), \
+                        (transport, key)
+                out_s = layer.forward(*shard, tokens="sharded")
+                err_s = moe_oracle.relative_max_error(out_s.float().cpu(), ref[mine])
+                worst = max(worst, err, err_s)
+                assert err <= 2e-2 and err_s <= 2e-2, (transport, repeat, err, err_s)
+                assert layer.workspace.status() == 0
+        torch.cuda.synchronize(device)
+        print(f"EP_CHECK_OK rank={rank} world={world} worst_err_over_rms={worst:.5f} "
+              f"floor={moe_oracle.bf16_floor(ref):.5f}", flush=True)
+    finally:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
