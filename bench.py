@@ -82,7 +82,7 @@ FALLBACK_HBM_GBS = 6650.0
 STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch at T=1 from
 # the committed ncu capture (profiles/); None until a capture exists.
-GATE_UP_T1_DRAM_TRAFFIC_BYTES = 476_054_016  # 469.82 MB read + 6.24 MB written
+GATE_UP_T1_DRAM_TRAFFIC_BYTES = 473_528_320  # 469.84 MB read + 3.69 MB written
 
 
 def percentile(sorted_values: list[float], q: float) -> float:
