@@ -139,3 +139,44 @@ def test_full_size_token_permutation_equivariance(cuda_device) -> None:
          gate_up, down), E, K, cuda_device,
     )
     assert torch.equal(moved, base[order])
+
+
+FULL_SIZE = [
+    # (label, T, H, I, E, K, routing, weight_kind)
+    ("deepseek_full_E256_T64_hotspot", 64, 7168, 2048, 256, 8, "hotspot", "softmax"),
+    ("wide_full_E64_T64_zipf", 64, 4096, 14336, 64, 8, "zipf", "raw"),
+]
+
+
+@pytest.mark.parametrize("spec", FULL_SIZE, ids=lambda s: s[0])
+def test_full_size_configurations_spot_checked_against_naive_oracle(spec, cuda_device) -> None:
+    """The two ~21 GiB configurations at their full expert count.  The FP32 oracle of the
+    whole layer would need every expert's weights on the host, so three tokens are checked
+    against the token/slot loop oracle using only the experts those tokens route to; the
+    routing tensors of the whole call are checked bit-exact; two runs are bit-identical."""
+
+    from b200moe import workloads
+
+    label, T, H, I, E, K, routing, weight_kind = spec
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing=routing, weight_kind=weight_kind, device=cuda_device)
+    out, metadata = _forward((hidden, ids, weights, gate_up, down), E, K, cuda_device,
+                             return_metadata=True, check_status=True)
+    again = _forward((hidden, ids, weights, gate_up, down), E, K, cuda_device)
+    assert torch.equal(out, again)
+    _check_routing(metadata, moe_oracle.group_tokens(ids.cpu(), E))
+
+    tokens = [0, T // 2, T - 1]
+    picked = ids[tokens].cpu()
+    experts = sorted(set(picked.reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(experts)}
+    small_ids = torch.tensor([[remap[int(e)] for e in row] for row in picked])
+    index = torch.tensor(experts, device=cuda_device)
+    ref = moe_oracle.routed_moe_naive(
+        hidden[tokens].cpu(), small_ids, weights[tokens].cpu(),
+        gate_up.index_select(0, index).cpu(), down.index_select(0, index).cpu())
+    got = out[tokens].float().cpu()
+    err = float((got - ref).abs().max()) / moe_oracle.rms(ref)
+    floor = moe_oracle.bf16_floor(ref)
+    print(f"{label}: err/rms={err:.5f} floor={floor:.5f} over tokens {tokens}")
+    assert err <= TOLERANCE, (err, floor)
