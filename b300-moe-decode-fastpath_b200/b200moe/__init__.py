@@ -8,6 +8,7 @@ Public names follow the reference package (fastpath/__init__.py:3-9) so that
 from ._lib import available as cuda_extension_available
 from ._lib import build_info
 from .forward import ARCHITECTURE, b300_moe_forward
+from .ops import DispatchResult, combine_tokens, dispatch_tokens
 from .router import topk_routing
 from .stages import StagedLayer
 from .validation import RoutedMoEShape, validate_routed_moe_inputs
@@ -16,11 +17,14 @@ from .workspace import B300MoEWorkspace
 __all__ = [
     "ARCHITECTURE",
     "B300MoEWorkspace",
+    "DispatchResult",
     "RoutedMoEShape",
     "StagedLayer",
     "b300_moe_forward",
     "build_info",
+    "combine_tokens",
     "cuda_extension_available",
+    "dispatch_tokens",
     "topk_routing",
     "validate_routed_moe_inputs",
 ]

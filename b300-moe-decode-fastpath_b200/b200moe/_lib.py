@@ -45,6 +45,8 @@ EXPORTS = (
     "b200moe_down",
     "b200moe_combine",
     "b200moe_forward",
+    "b200moe_dispatch",
+    "b200moe_combine_bf16",
     "b200moe_ep_reduce",
     "b200moe_ep_push",
     "b200moe_status_ptr",
@@ -162,12 +164,18 @@ def _declare(lib: ctypes.CDLL) -> None:
         "b200moe_down",
         "b200moe_combine",
         "b200moe_forward",
+        "b200moe_dispatch",
     ):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [args_p, ctypes.c_void_p]
     lib.b200moe_ep_reduce.restype = ctypes.c_int
     lib.b200moe_ep_reduce.argtypes = [ctypes.POINTER(B200MoeEpReduceArgs), ctypes.c_void_p]
+    lib.b200moe_combine_bf16.restype = ctypes.c_int
+    lib.b200moe_combine_bf16.argtypes = [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+        ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+    ]
     lib.b200moe_ep_push.restype = ctypes.c_int
     lib.b200moe_ep_push.argtypes = [ctypes.POINTER(B200MoeEpPushArgs), ctypes.c_void_p]
     lib.b200moe_status_ptr.restype = ctypes.c_int

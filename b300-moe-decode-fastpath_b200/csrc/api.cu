@@ -51,6 +51,9 @@ cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
                         cudaStream_t stream);
 
+cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
+                                const void* weights, void* out, int num_tokens, int top_k,
+                                int hidden_size, cudaStream_t stream);
 cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_ptrs, int world,
                              int rank, int num_tokens, int hidden, uint32_t epoch,
                              unsigned long long wait_limit_ns, void* output, uint32_t* status,
@@ -509,6 +512,56 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
                                a->hidden_size, a->epoch, limit_ns, a->output, a->status,
                                (a->flags & B200MOE_FLAG_PDL) != 0,
                                static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_dispatch(const B200MoeArgs* a, void* stream) {
+  if (!a) return B200MOE_E_NULL;
+  if (!a->hidden_states || !a->expert_indices || !a->expert_counts || !a->expert_offsets ||
+      !a->expert_offsets_i32 || !a->permutation || !a->reverse_mapping || !a->permuted_hidden ||
+      !a->scratch)
+    return B200MOE_E_NULL;
+  int rc = check_shape(a->num_tokens, a->top_k, a->num_experts, a->hidden_size, 8,
+                       (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0);
+  if (rc) return rc;
+  const int assignments = a->num_tokens * a->top_k;
+  if (a->rows_cap < assignments) return B200MOE_E_SHAPE;
+  if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(a->scratch) % kScratchAlign) return B200MOE_E_ALIGN;
+  const size_t need = kStatusBytes + sizeof(int32_t) * (kSchedHeaderWords +
+                                                        (size_t)kSchedSegWords *
+                                                            max_segments(a->rows_cap,
+                                                                         a->num_experts));
+  if (a->scratch_bytes < need) return B200MOE_E_SCRATCH;
+  Ctx c;
+  rc = current_device_info(&c.dev);
+  if (rc) return rc;
+  char* b = static_cast<char*>(a->scratch);
+  c.s.status = reinterpret_cast<uint32_t*>(b);
+  c.s.sched = reinterpret_cast<int32_t*>(b + kStatusBytes);
+  c.s.act_lo = nullptr;
+  c.s.partials = nullptr;
+  c.assignments = assignments;
+  c.pdl = (a->flags & B200MOE_FLAG_PDL) != 0;
+  c.stream = static_cast<cudaStream_t>(stream);
+  if ((rc = stage_routing(a, c))) return rc;
+  return stage_gather(a, c, c.pdl);
+}
+
+int b200moe_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
+                         const void* routing_weights, int num_tokens, int top_k, int hidden_size,
+                         void* output, void* stream) {
+  if (!expert_rows || !assignment_to_permuted || !routing_weights || !output)
+    return B200MOE_E_NULL;
+  if (num_tokens < 1 || hidden_size < 8 ||
+      !(top_k == 1 || top_k == 2 || top_k == 4 || top_k == 8))
+    return B200MOE_E_SHAPE;
+  if (hidden_size % 8 || !aligned16(expert_rows) || !aligned16(output)) return B200MOE_E_ALIGN;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_combine_bf16(expert_rows, assignment_to_permuted, routing_weights, output,
+                                  num_tokens, top_k, hidden_size,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_ep_push(const B200MoeEpPushArgs* a, void* stream) {

@@ -117,6 +117,48 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
   trace_end(trace, kTraceCombine);
 }
 
+// Legacy combine: out[t, :] = bf16( sum_k float(w[t,k]) * float(rows[map[t*K+k], :]) ) on BF16
+// expert rows, FP32 accumulation in slot order, rows with an invalid mapping skipped
+// (csrc/combine_cuda.cu:23-52).
+__global__ void __launch_bounds__(128)
+combine_bf16_rows_kernel(const uint4* __restrict__ expert_rows,
+                         const int64_t* __restrict__ assignment_to_permuted,
+                         const __nv_bfloat16* __restrict__ weights, uint4* __restrict__ out,
+                         int num_assign, int top_k, int hidden) {
+  const int token = blockIdx.x;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (col >= hidden) return;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int k = 0; k < top_k; ++k) {
+    const int a = token * top_k + k;
+    const int64_t row = assignment_to_permuted[a];
+    if (row < 0 || row >= (int64_t)num_assign) continue;
+    const float w = __bfloat162float(weights[a]);
+    const uint4 packed = __ldg(expert_rows + (((size_t)row * hidden + col) >> 3));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      acc[2 * i] = fmaf(v.x, w, acc[2 * i]);
+      acc[2 * i + 1] = fmaf(v.y, w, acc[2 * i + 1]);
+    }
+  }
+  out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
+}
+
+cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
+                                const void* weights, void* out, int num_tokens, int top_k,
+                                int hidden_size, cudaStream_t stream) {
+  const dim3 grid(num_tokens, (hidden_size / 8 + 127) / 128);
+  combine_bf16_rows_kernel<<<grid, 128, 0, stream>>>(
+      static_cast<const uint4*>(expert_rows), assignment_to_permuted,
+      static_cast<const __nv_bfloat16*>(weights), static_cast<uint4*>(out),
+      num_tokens * top_k, top_k, hidden_size);
+  return cudaGetLastError();
+}
+
 static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void** args,
                                    bool pdl, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};

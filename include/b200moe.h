@@ -218,6 +218,27 @@ int b200moe_down(const B200MoeArgs* args, void* stream);
 int b200moe_combine(const B200MoeArgs* args, void* stream);
 
 /*
+ * Stages 1 + 2 on their own: the legacy "dispatch" operation.  Replaces dispatch_cuda
+ * (csrc/dispatch_cuda.cu:24-201, bound as fastpath._C.dispatch and used by
+ * fastpath/ops.py:150-178): counts, offsets, both mappings and the gathered rows.
+ * Needs only the head of a scratch region: 256 bytes + the schedule
+ * (4 * (8 + 4 * (min(rows_cap, E) + rows_cap / 128 + 1)) bytes), 256-byte aligned.
+ * intermediate_size, swiglu_output, the weights and output are not read.
+ */
+int b200moe_dispatch(const B200MoeArgs* args, void* stream);
+
+/*
+ * The legacy "combine" operation on BF16 expert rows.  Replaces combine_cuda
+ * (csrc/combine_cuda.cu:23-141, fastpath/ops.py:242-271):
+ *   output[t, :] = bf16( sum_k float(w[t,k]) * float(expert_rows[map[t*K+k], :]) )
+ * FP32 accumulation in slot order; entries of the mapping outside [0, T*K) are skipped.
+ */
+int b200moe_combine_bf16(const void* expert_rows /*[T*K,H] bf16*/,
+                         const int64_t* assignment_to_permuted /*[T*K]*/,
+                         const void* routing_weights /*[T,K] bf16*/, int num_tokens, int top_k,
+                         int hidden_size, void* output /*[T,H] bf16*/, void* stream);
+
+/*
  * The whole layer: stages 1..5 enqueued back to back on `stream` by one call.
  * Replaces _call_compiled_bf16 (fastpath/b300_moe.py:620-760).  No allocation,
  * no synchronisation, no host read-back.

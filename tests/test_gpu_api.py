@@ -461,3 +461,40 @@ def test_peer_dispatch_kernel_and_routing_wait_on_one_gpu(cuda_device) -> None:
     ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
                                    down.cpu(), num_experts=E, top_k=K)
     assert moe_oracle.relative_max_error(partial.to(torch.bfloat16).float().cpu(), ref) <= 2e-2
+
+
+@pytest.mark.parametrize("tokens, experts, top_k", [(1, 256, 1), (7, 16, 2), (64, 64, 8),
+                                                     (300, 32, 4)])
+def test_legacy_dispatch_and_combine(tokens, experts, top_k, cuda_device) -> None:
+    """The older dispatch/combine API (tests/test_cuda_ops.py:25-133 of the reference):
+    mappings equal the stable argsort and its inverse, the gather is exact, the combine
+    matches the FP32 formula of fastpath/ops.py:264-268."""
+
+    from b200moe import combine_tokens, dispatch_tokens, workloads
+
+    H = 256
+    g = torch.Generator().manual_seed(tokens * 31 + top_k)
+    hidden = torch.randn(tokens, H, generator=g).to(device=cuda_device, dtype=torch.bfloat16)
+    ids = workloads.make_routing(tokens, experts, top_k, "duplicates", 5).to(cuda_device)
+    weights = torch.randn(tokens, top_k, generator=g).to(device=cuda_device,
+                                                         dtype=torch.bfloat16)
+    result = dispatch_tokens(hidden, ids, experts)
+    want = moe_oracle.group_tokens(ids.cpu(), experts)
+    assert result.permuted_to_assignment.cpu().tolist() == want.permutation.tolist()
+    assert result.assignment_to_permuted.cpu().tolist() == want.reverse_mapping.tolist()
+    assert result.expert_counts.cpu().tolist() == want.expert_counts.tolist()
+    assert result.expert_offsets.cpu().tolist() == want.expert_offsets.tolist()
+    rows = hidden.cpu()[torch.from_numpy(want.permuted_token_indices)]
+    assert torch.equal(result.permuted_hidden.cpu(), rows)
+
+    expert_rows = torch.randn(tokens * top_k, H, generator=g).to(device=cuda_device,
+                                                                 dtype=torch.bfloat16)
+    out = combine_tokens(expert_rows, result.assignment_to_permuted, weights)
+    ordered = expert_rows.cpu().float()[result.assignment_to_permuted.cpu()]
+    expected = (ordered.reshape(tokens, top_k, H) * weights.cpu().float().unsqueeze(-1)).sum(1)
+    torch.testing.assert_close(out.float().cpu(), expected, atol=1e-2 * max(1.0, top_k ** 0.5),
+                               rtol=1e-2)
+    with pytest.raises(RuntimeError, match="oracle"):
+        dispatch_tokens(hidden, ids, experts, backend="torch")
+    with pytest.raises(TypeError, match="int64"):
+        dispatch_tokens(hidden, ids.int(), experts)
