@@ -7,7 +7,7 @@ Public names follow the reference package (fastpath/__init__.py:3-9) so that
 
 from ._lib import available as cuda_extension_available
 from ._lib import build_info
-from .forward import ARCHITECTURE, b300_moe_forward
+from .forward import ARCHITECTURE, b300_moe_forward, b300_moe_forward_pinned
 from .ops import DispatchResult, combine_tokens, dispatch_tokens
 from .router import topk_routing
 from .stages import StagedLayer
@@ -21,6 +21,7 @@ __all__ = [
     "RoutedMoEShape",
     "StagedLayer",
     "b300_moe_forward",
+    "b300_moe_forward_pinned",
     "build_info",
     "combine_tokens",
     "cuda_extension_available",

@@ -338,3 +338,69 @@ def b300_moe_forward(
         return output, metadata
     return output
 
+
+
+def b300_moe_forward_pinned(
+    hidden_states: torch.Tensor,
+    expert_indices: torch.Tensor,
+    expert_weights: torch.Tensor,
+    gate_up_weight: torch.Tensor,
+    down_weight: torch.Tensor,
+    *,
+    num_experts: int,
+    top_k: int,
+    workspace: B300MoEWorkspace,
+    out: torch.Tensor | None = None,
+    use_pdl: bool = True,
+) -> torch.Tensor:
+    """The layer with its per-step tensors in pinned host memory (no counterpart in the
+    reference, whose compiled path takes device tensors only).
+
+    A decode step's activations ``[T,H]``, routes and routing weights are a few KB to a few
+    hundred KB.  Copying them with four separate DMA transfers costs more in launch latency
+    than in bytes; pinned host memory is mapped into the device address space, so the
+    routing and gather kernels read the inputs, and the combine kernel writes the result,
+    directly over PCIe.  ``hidden_states``, ``expert_indices``, ``expert_weights`` (and
+    ``out``, allocated pinned when omitted) must be pinned CPU tensors; the expert weights
+    stay resident on the GPU that ``workspace`` is, or will be, bound to.  The result is
+    valid after the current stream of that device has been synchronised.  Same contract
+    checks as :func:`b300_moe_forward`.
+    """
+
+    device = gate_up_weight.device
+    if device.type != "cuda":
+        raise ValueError("expert weights must be CUDA tensors")
+    per_step = (hidden_states, expert_indices, expert_weights) + ((out,) if out is not None else ())
+    for tensor in per_step:
+        if tensor.device.type != "cpu" or not tensor.is_pinned():
+            raise ValueError("per-step tensors must be pinned host tensors")
+    if not isinstance(workspace, B300MoEWorkspace):
+        raise TypeError("workspace must be a B300MoEWorkspace")
+    shape = validate_routed_moe_inputs(
+        hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight,
+        num_experts=num_experts, top_k=top_k, expert_weights_on_other_device=True,
+    )
+    _resolve_native_backend("b200_bf16", gate_up_weight, gate_up_weight, gate_up_weight,
+                            down_weight, shape)
+    if hidden_states.dtype != torch.bfloat16:
+        raise TypeError("b200_bf16 requires bfloat16 inputs and weights")
+    if out is None:
+        out = torch.empty(shape.num_tokens, shape.hidden_size, dtype=hidden_states.dtype,
+                          pin_memory=True)
+    elif tuple(out.shape) != (shape.num_tokens, shape.hidden_size) or \
+            out.dtype != hidden_states.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [T, H] tensor of the input dtype")
+    with workspace._lock:
+        workspace.reserve(
+            num_tokens=shape.num_tokens, num_experts=shape.num_experts, top_k=shape.top_k,
+            hidden_size=shape.hidden_size, intermediate_size=shape.intermediate_size,
+            device=device, dtype=hidden_states.dtype, backend="b200_bf16", quant_mode="bf16",
+        )
+        args = _native_args(hidden_states, expert_indices, expert_weights, gate_up_weight,
+                            down_weight, shape, workspace, out, _lib.FLAG_PDL if use_pdl else 0)
+        code = _enqueue(_lib.load().b200moe_forward, args, device)
+        if code:
+            _lib.check(code, "b200moe_forward")
+        workspace._record_use()
+    return out
+

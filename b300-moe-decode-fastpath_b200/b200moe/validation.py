@@ -118,8 +118,14 @@ def validate_routed_moe_inputs(
     num_experts: int,
     top_k: int,
     check_range_on_device: bool = False,
+    expert_weights_on_other_device: bool = False,
 ) -> RoutedMoEShape:
-    """Full tensor contract (reference.py:109-183); returns the dimensions."""
+    """Full tensor contract (reference.py:109-183); returns the dimensions.
+
+    ``expert_weights_on_other_device`` relaxes the one-device rule for the pinned-host
+    entry point: the three per-step tensors share a device and the two weight tensors share
+    a device.
+    """
 
     named = {
         "hidden_states": hidden_states,
@@ -171,8 +177,11 @@ def validate_routed_moe_inputs(
     for other in (expert_weights, gate_up_weight, down_weight):
         if other.dtype != hidden_states.dtype:
             raise TypeError("all floating-point inputs must have the same dtype")
-    for value in named.values():
-        if value.device != hidden_states.device:
+    for name, value in named.items():
+        anchor = hidden_states
+        if expert_weights_on_other_device and name in ("gate_up_weight", "down_weight"):
+            anchor = gate_up_weight
+        if value.device != anchor.device:
             raise ValueError("all inputs must be on the same device")
     for value in named.values():
         if not value.is_contiguous():

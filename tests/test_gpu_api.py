@@ -498,3 +498,32 @@ def test_legacy_dispatch_and_combine(tokens, experts, top_k, cuda_device) -> Non
         dispatch_tokens(hidden, ids, experts, backend="torch")
     with pytest.raises(TypeError, match="int64"):
         dispatch_tokens(hidden, ids.int(), experts)
+
+
+def test_pinned_host_io_matches_device_io(cuda_device) -> None:
+    """Per-step tensors in pinned host memory, read and written by the kernels directly:
+    same bits as the device-tensor entry point."""
+
+    from b200moe import B300MoEWorkspace, b300_moe_forward, b300_moe_forward_pinned, workloads
+
+    T, H, I, E, K = 9, 512, 768, 16, 4
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing="zipf", std=None, device=cuda_device)
+    want = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K)
+    host = tuple(t.cpu().pin_memory() for t in (hidden, ids, weights))
+    workspace = B300MoEWorkspace(capacity_tokens=16, device=cuda_device)
+    for _ in range(2):
+        got = b300_moe_forward_pinned(*host, gate_up, down, num_experts=E, top_k=K,
+                                      workspace=workspace)
+        torch.cuda.synchronize(cuda_device)
+        assert got.is_pinned() and got.device.type == "cpu"
+        assert torch.equal(got, want.cpu())
+    assert workspace.status() == 0
+    with pytest.raises(ValueError, match="pinned"):
+        b300_moe_forward_pinned(hidden.cpu(), *host[1:], gate_up, down, num_experts=E, top_k=K,
+                                workspace=workspace)
+    bad = host[1].clone().pin_memory()
+    bad[0, 0] = E
+    with pytest.raises(ValueError, match="out-of-range"):
+        b300_moe_forward_pinned(host[0], bad, host[2], gate_up, down, num_experts=E, top_k=K,
+                                workspace=workspace)
