@@ -287,7 +287,8 @@ class B300MoEWorkspace:
                 top_k,
                 hidden_size,
                 intermediate_size,
-                backend,
+                # the two names of the native path share one layout
+                "b200_bf16" if backend in _NATIVE_BACKENDS else backend,
                 quant_mode,
             )
             new_layout = signature != self._signature

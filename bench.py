@@ -290,6 +290,27 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     pinned_samples = timed_pass(forward_pinned, args.steps)
     torch.cuda.synchronize(device)
 
+    # the same forward captured once in a CUDA graph and replayed (how decode loops usually
+    # run it): no Python and no per-kernel launch call inside the timed region
+    graph_samples = {}
+    for T in sweep:
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(device)
+        with torch.cuda.graph(graph):
+            forward(T)
+        pairs = []
+        for _ in range(max(10, min(args.steps, 50))):
+            flush_l2()
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            pairs.append((a, b))
+        torch.cuda.synchronize(device)
+        graph_samples[T] = [a.elapsed_time(b) * 1e3 for a, b in pairs]
+        del graph
+
     # host cost of one call: enqueue 20 forwards back to back without synchronising
     host_us = {}
     for T in sweep:
@@ -329,6 +350,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "total_us": total,
             "e2e_us": summary(e2e_samples[T]),
             "e2e_pinned_io_us": summary(pinned_samples[T]),
+            "graph_replay_us": summary(graph_samples[T]),
             "host_enqueue_us": round(host_us[T], 1),
             "stages_us": {
                 "routing": stage_us["routing"],
