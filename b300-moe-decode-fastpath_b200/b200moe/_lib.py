@@ -32,6 +32,8 @@ TUNE_STAGE_KB = 1
 TUNE_L2_PROMOTION = 2
 TUNE_EVICT_FIRST = 3
 TUNE_EARLY_START = 4
+TUNE_DOWN_TARGET = 5
+TUNE_DOWN_SPLITS = 6
 
 EXPORTS = (
     "b200moe_abi_version",

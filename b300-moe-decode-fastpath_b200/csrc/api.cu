@@ -70,6 +70,15 @@ extern int g_early_mode;
 namespace {
 
 int g_l2_promotion = 2;  // 0 none, 1 128 B, 2 256 B
+int g_down_target = 0;   // blocks the down projection's split-K aims at (0: 2 per SM)
+
+int g_down_splits = 0;   // forced split-K factor of the down projection (0: chosen on the device)
+
+int down_target(int sm_count) { return g_down_target > 0 ? g_down_target : 2 * sm_count; }
+// what the routing kernel receives: the target, or minus the forced split factor
+int down_split_request(int sm_count) {
+  return g_down_splits > 0 ? -g_down_splits : down_target(sm_count);
+}
 
 constexpr int kMaxDevices = 64;
 
@@ -197,7 +206,7 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              a->reverse_mapping, a->permutation, a->expert_offsets_i32,
                              a->permuted_token_indices, a->permuted_expert_indices,
                              a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
-                             (a->intermediate_size + 63) / 64, 2 * dev.sm_count,
+                             (a->intermediate_size + 63) / 64, down_split_request(dev.sm_count),
                              local ? a->expert_id_base : 0, local,
                              static_cast<const uint32_t*>(a->ep_wait_flags), a->ep_world,
                              a->ep_epoch,
@@ -254,10 +263,20 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   if (rc) return rc;
   rc = encode_bf16_map(&map_lo, s.act_lo, 2, dims, box);
   if (rc) return rc;
-  // Without split-K there are at most bound*tiles units; with it the routing
-  // kernel keeps units*splits <= 2 * SM count.
+  // Without split-K there are at most bound*tiles units.
   int grid = segment_bound(assignments, experts) * tiles128(hidden);
-  if (grid < 2 * dev.sm_count) grid = 2 * dev.sm_count;
+  // The routing kernel picks the split factor from the number of segments it finds; size
+  // the grid for the worst case over every possible segment count.
+  const int tiles = tiles128(hidden), kblocks = (inter + 63) / 64;
+  if (g_down_splits > 0) {
+    grid *= g_down_splits;
+  } else {
+    const int target = down_target(dev.sm_count);
+    for (int segs = 1; segs <= segment_bound(assignments, experts); ++segs) {
+      const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
+      if (n > grid) grid = n;
+    }
+  }
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
                           rows_cap, grid, pdl, stream);
 }
@@ -432,6 +451,14 @@ int b200moe_tune(int knob, int value) {
       return 0;
     case B200MOE_TUNE_EVICT_FIRST:
       g_gemm_evict_first = value ? 1 : 0;
+      return 0;
+    case B200MOE_TUNE_DOWN_TARGET:
+      if (value < 0 || value > 4096) return B200MOE_E_SHAPE;
+      g_down_target = value;
+      return 0;
+    case B200MOE_TUNE_DOWN_SPLITS:
+      if (value < 0 || value > kDownSplitMax) return B200MOE_E_SHAPE;
+      g_down_splits = value;
       return 0;
     case B200MOE_TUNE_EARLY_START:
       if (value < 0 || value > 2) return B200MOE_E_SHAPE;

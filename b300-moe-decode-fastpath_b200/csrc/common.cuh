@@ -29,6 +29,42 @@ enum SchedWord {
   kSchedDownSplits = 3,     // split-K factor chosen for the down projection
 };
 
+// Split-K factor of the down projection for `units` (segment, tile) work units, each of
+// `kblocks` K blocks, when `resident` blocks fit on the GPU at once.  Cost model fitted to
+// measurements, in units of one full wave of unsplit blocks: full waves each take 1/s; the
+// last, partial wave of r blocks cannot go faster than ~0.67 of a full wave however few
+// blocks it has (a block alone on its SM streams ~33 GB/s against a fair share of ~22),
+// nor than ~0.75 once some SMs hold two blocks and others one; every extra split adds a
+// little fixed work per block.
+// Above four waves of units the tail no longer matters and nothing is split.  Shared by
+// the routing kernel (which decides) and the host (which sizes the grid for the worst case).
+__host__ __device__ inline int choose_down_splits(int units, int resident, int kblocks) {
+  if (units <= 0 || units >= 4 * resident) return 1;
+  int max_splits = kblocks / 4;
+  if (max_splits > kDownSplitMax) max_splits = kDownSplitMax;
+  if (max_splits < 1) max_splits = 1;
+  int splits = 1;
+  float best = 3.0e38f;
+  for (int s = 1; s <= max_splits; ++s) {
+    const int n = units * s;
+    const int full = n / resident;
+    const int rest = n - full * resident;
+    float tail = 0.0f;
+    if (rest > 0) {
+      tail = (float)rest / (float)resident;
+      const float floor_ = 2 * rest > resident ? 0.75f : 0.67f;
+      if (tail < floor_) tail = floor_;
+    }
+    float cost = ((float)full + tail) / (float)s;
+    cost *= 1.0f + 1.5f * (float)s / (float)kblocks;
+    if (cost < best * 0.995f) {
+      best = cost;
+      splits = s;
+    }
+  }
+  return splits;
+}
+
 constexpr size_t kScratchAlign = 256;
 constexpr size_t kStatusBytes = 256;  // status word lives in the first 256 bytes
 

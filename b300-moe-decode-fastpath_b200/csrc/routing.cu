@@ -155,9 +155,13 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     // exist, cut K so that about `target_ctas` blocks stream weights at once.
     int splits = 1;
     const int units = n_seg * down_tiles;
-    if (units > 0 && units < target_ctas) splits = target_ctas / units;
-    splits = min(splits, kDownSplitMax);
-    splits = min(splits, max(1, down_kblocks / 4));
+    if (target_ctas < 0) {
+      splits = -target_ctas;  // forced by the caller (tuning)
+    } else {
+      splits = choose_down_splits(units, target_ctas, down_kblocks);
+    }
+    splits = max(1, min(splits, kDownSplitMax));
+    splits = min(splits, max(1, down_kblocks));
     sched[kSchedNumSegments] = n_seg;
     sched[kSchedNumActive] = n_active;
     sched[kSchedNumValidRows] = n_valid;

@@ -353,11 +353,17 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              (default), 1 at once, each block deriving its work
  *                              unit from the expert ids itself, 2 as 1 and blocks
  *                              with <= 32 rows also fetch their token rows themselves
+ *   B200MOE_TUNE_DOWN_SPLITS   force the split-K factor of the down projection (1..8;
+ *                              0 = chosen on the device from the routing result)
+ *   B200MOE_TUNE_DOWN_TARGET   number of blocks the split-K of the down projection aims
+ *                              at when few (segment, tile) units exist (0 = default)
  */
 #define B200MOE_TUNE_STAGE_KB     1
 #define B200MOE_TUNE_L2_PROMOTION 2
 #define B200MOE_TUNE_EVICT_FIRST  3
 #define B200MOE_TUNE_EARLY_START  4
+#define B200MOE_TUNE_DOWN_TARGET  5
+#define B200MOE_TUNE_DOWN_SPLITS  6
 int b200moe_tune(int knob, int value);
 
 #ifdef __cplusplus
