@@ -198,6 +198,169 @@ def dist_setup(n_gpus: int):
 # -----------------------------------------------------------------------------
 # our arm
 # -----------------------------------------------------------------------------
+def library_gemm_baseline(case, gate_up, down, flush_l2, reps: int) -> dict[str, object]:
+    """The two GEMMs as the reference's compiled path runs them, on this GPU.
+
+    The reference calls PyTorch's BF16 grouped GEMM (csrc/grouped_gemm_sm103.cu:47-52) or
+    a loop of ``torch.matmul(..., out=)`` over the active experts
+    (fastpath/gemm_dispatch.py:100-150); its own GEMM-only comparison
+    (results/b300_goal1b_20260720/step4_02_gemm_only.py:187-209) times exactly these two.
+    They are library kernels, timed here only to be reported beside this library's stages:
+    same permuted rows, same weights, same L2 flush, one CUDA-event pair per launch group.
+    """
+
+    ws = case["workspace"]
+    rows = case["dev"][1].numel()
+    buffers = ws.buffers
+    x = buffers["permuted_hidden"][:rows]
+    offsets = buffers["expert_offsets"][: EXPERTS + 1].to("cpu").tolist()  # outside the timed region
+    ends_i32 = buffers["expert_offsets"][1: EXPERTS + 1].to(torch.int32)
+    act = buffers["swiglu_output"][:rows]
+    gu_out = torch.empty(rows, 2 * INTER, dtype=torch.bfloat16, device=x.device)
+    dn_out = torch.empty(rows, HIDDEN, dtype=torch.bfloat16, device=x.device)
+    active = [(e, offsets[e], offsets[e + 1]) for e in range(EXPERTS) if offsets[e + 1] > offsets[e]]
+
+    def grouped(a, w):
+        return torch._grouped_mm(a, w.transpose(1, 2), offs=ends_i32)
+
+    def per_expert(a, w, out):
+        for e, lo, hi in active:
+            torch.matmul(a[lo:hi], w[e].t(), out=out[lo:hi])
+
+    variants = {
+        "grouped_mm": {"gate_up": lambda: grouped(x, gate_up), "down": lambda: grouped(act, down)},
+        "per_expert_matmul": {"gate_up": lambda: per_expert(x, gate_up, gu_out),
+                              "down": lambda: per_expert(act, down, dn_out)},
+    }
+    report: dict[str, object] = {}
+    for name, stages in variants.items():
+        entry: dict[str, object] = {}
+        for stage, fn in stages.items():
+            try:
+                for _ in range(3):
+                    fn()
+                pairs = []
+                for _ in range(reps):
+                    flush_l2()
+                    a = torch.cuda.Event(enable_timing=True)
+                    b = torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    fn()
+                    b.record()
+                    pairs.append((a, b))
+                torch.cuda.synchronize(x.device)
+                entry[stage] = summary([a.elapsed_time(b) * 1e3 for a, b in pairs])
+            except (RuntimeError, AttributeError, TypeError) as error:
+                entry[stage] = {"unavailable": str(error).splitlines()[0][:200]}
+        report[name] = entry
+    return report
+
+
+# Column names of the reference's result files (benchmark/benchmark_goal_1b.py:77-122), so
+# tooling written for those files reads this benchmark's output unchanged.
+REFERENCE_CSV_FIELDS = (
+    "backend_set_requested", "requested_backend", "actual_backend", "device", "gpu_name",
+    "gpu_capability", "architecture", "dtype", "workload", "num_tokens", "num_experts", "top_k",
+    "hidden_size", "intermediate_size", "quant_mode", "used_fallback", "gemm_policy",
+    "gate_up_gemm_strategy", "down_gemm_strategy", "stage", "stage_status", "measurement",
+    "samples", "p50_us", "p90_us", "p99_us", "cold_start_us", "cold_start_scope", "warmup",
+    "repetitions", "timing_method", "weights_prepared_outside_timing", "torch_version",
+    "torch_cuda_version", "torch_arch_list", "cuda_toolkit_version",
+    "cuda_toolkit_version_source", "cutlass_version", "cutlass_version_source", "cutlass_path",
+    "wrapper_compiled_architecture", "grouped_gemm_provider",
+    "grouped_gemm_provider_architecture", "pytorch_cxx_version",
+)
+# reference stage name -> key of this benchmark's per-T record
+REFERENCE_CSV_STAGES = (
+    ("routing_us", "routing"), ("permutation_us", "permutation"), ("quantization_us", None),
+    ("gate_up_gemm_us", "gate_up"), ("swiglu_us", "swiglu"), ("down_gemm_us", "down"),
+    ("combine_us", "combine"), ("total_us", "total"),
+)
+
+
+def write_reference_csv(path: str, result: dict[str, object], args, device) -> int:
+    """One row per (T, stage) in the reference's CSV schema; returns the row count.
+
+    ``quantization_us`` is ``not_applicable`` (BF16 inputs are consumed as they are, as in
+    benchmark_goal_1b.py:601-606) and ``swiglu_us`` is 0 with status ``fused_in_gate_up``:
+    the activation runs in the gate+up kernel's epilogue and has no launch of its own.
+    ``total_us`` is the layer call only; the reference's also holds the router's top-k.
+    """
+
+    import csv
+
+    from b200moe import build_info
+
+    info = build_info()
+    props = torch.cuda.get_device_properties(device)
+    common = {
+        "backend_set_requested": "cutlass_bf16",
+        "requested_backend": "cutlass_bf16",
+        "actual_backend": "cutlass_bf16",
+        "device": str(device),
+        "gpu_name": props.name,
+        "gpu_capability": f"{props.major}.{props.minor}",
+        "architecture": "sm_100a",
+        "dtype": "bfloat16",
+        "workload": ROUTING,
+        "num_experts": EXPERTS,
+        "top_k": TOP_K,
+        "hidden_size": HIDDEN,
+        "intermediate_size": INTER,
+        "quant_mode": "bf16",
+        "used_fallback": "false",
+        "gemm_policy": "auto",
+        "gate_up_gemm_strategy": "grouped",
+        "down_gemm_strategy": "grouped",
+        "measurement": "steady_state",
+        "cold_start_scope": "first_forward_after_input_setup",
+        "warmup": args.warmup,
+        "repetitions": args.steps,
+        "timing_method": "cuda_events",
+        "weights_prepared_outside_timing": "true",
+        "torch_version": torch.__version__,
+        "torch_cuda_version": str(torch.version.cuda),
+        "torch_arch_list": ",".join(torch.cuda.get_arch_list()),
+        "cuda_toolkit_version": str(info.get("cuda_runtime_version", "unavailable")),
+        "cuda_toolkit_version_source": "extension_cudart_header",
+        "cutlass_version": "not_used",
+        "cutlass_version_source": "not_used",
+        "cutlass_path": "not_used",
+        "wrapper_compiled_architecture": str(info.get("compiled_architecture", "sm_100a")),
+        "grouped_gemm_provider": str(info.get("bf16_grouped_gemm_provider", "unavailable")),
+        "grouped_gemm_provider_architecture": str(info.get("compiled_architecture", "sm_100a")),
+        "pytorch_cxx_version": "not_linked",
+    }
+    rows = []
+    for T, record in result["per_T"].items():
+        for stage, key in REFERENCE_CSV_STAGES:
+            if key is None:
+                stats, status, samples = {"p50": 0.0, "p90": 0.0, "p99": 0.0}, "not_applicable", args.steps
+            elif key == "total":
+                stats, status, samples = record["total_us"], "measured", args.steps
+            else:
+                stats = record["stages_us"][key]
+                status = stats.get("status", "measured")
+                samples = record.get("stage_samples", args.steps)
+            rows.append(common | {
+                "num_tokens": T,
+                "stage": stage,
+                "stage_status": status,
+                "samples": samples,
+                "p50_us": f"{stats.get('p50', 0.0):.9f}",
+                "p90_us": f"{stats.get('p90', 0.0):.9f}",
+                "p99_us": f"{stats.get('p99', 0.0):.9f}",
+                "cold_start_us": f"{record.get('cold_start_us', 0.0):.9f}",
+            })
+    out = Path(path)
+    out.parent.mkdir(parents=True, exist_ok=True)
+    with out.open("w", newline="", encoding="utf-8") as handle:
+        writer = csv.DictWriter(handle, fieldnames=REFERENCE_CSV_FIELDS)
+        writer.writeheader()
+        writer.writerows(rows)
+    return len(rows)
+
+
 def run_ours(args: argparse.Namespace) -> dict[str, object]:
     from b200moe import (B300MoEWorkspace, StagedLayer, b300_moe_forward,
                          b300_moe_forward_pinned, workloads)
@@ -272,6 +435,15 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
                 events[T].append((start, stop))
         torch.cuda.synchronize(device)
         return {T: [a.elapsed_time(b) * 1e3 for a, b in pairs] for T, pairs in events.items()}
+
+    # cold start: the very first forward of each case (tensor maps encoded, caches cold)
+    cold_us = {}
+    for T in sweep:
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        forward(T)
+        torch.cuda.synchronize(device)
+        cold_us[T] = (time.perf_counter() - t0) * 1e6
 
     # warm-up (untimed), then the timed region bracketed by synchronisation
     timed_pass(forward, args.warmup)
@@ -352,6 +524,8 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "e2e_pinned_io_us": summary(pinned_samples[T]),
             "graph_replay_us": summary(graph_samples[T]),
             "host_enqueue_us": round(host_us[T], 1),
+            "cold_start_us": round(cold_us[T], 1),
+            "stage_samples": stage_reps,
             "stages_us": {
                 "routing": stage_us["routing"],
                 "permutation": stage_us["gather"],
@@ -366,6 +540,9 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "gate_up_gbs": round(wb["gate_up"] / stage_us["gate_up_swiglu"]["p50"] / 1e3, 1),
             "down_gbs": round(wb["down"] / stage_us["down"]["p50"] / 1e3, 1),
         }
+        if args.library_gemm_baseline:
+            per_t[str(T)]["library_gemm_us"] = library_gemm_baseline(
+                c, gate_up, down, flush_l2, stage_reps)
 
     p50s = [per_t[str(T)]["total_us"]["p50"] for T in sweep]
     e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in sweep]
@@ -435,6 +612,9 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     }
     if not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(gate_up, down, cases, budget_s=20.0)
+    if args.csv:
+        result["csv"] = {"path": args.csv,
+                         "rows": write_reference_csv(args.csv, result, args, device)}
     return result
 
 
@@ -743,6 +923,11 @@ def main() -> int:
                         help="N > 1: combine over NVLink peer memory (default) or NCCL")
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
+    parser.add_argument("--csv", default=None,
+                        help="N=1: also write per-stage rows in the reference's CSV schema")
+    parser.add_argument("--library-gemm-baseline", action="store_true",
+                        help="N=1: also time torch._grouped_mm and the per-expert matmul loop "
+                             "(the library GEMMs the reference's compiled path calls)")
     args = parser.parse_args()
     apply_config(args.config)
     if args.config in ("wide", "deepseek", "deepseek_hotspot"):

@@ -6,6 +6,8 @@ suite pins (tests/test_goal_1b_cuda.py:139-175, 213-247, 316-400).
 
 from __future__ import annotations
 
+from pathlib import Path
+
 import pytest
 import torch
 
@@ -527,3 +529,40 @@ def test_pinned_host_io_matches_device_io(cuda_device) -> None:
     with pytest.raises(ValueError, match="out-of-range"):
         b300_moe_forward_pinned(host[0], bad, host[2], gate_up, down, num_experts=E, top_k=K,
                                 workspace=workspace)
+
+
+@pytest.mark.gpu
+def test_bench_writes_reference_csv_schema(tmp_path):
+    """``bench.py --csv`` emits the column set and stage names of the reference's result
+    files (benchmark/benchmark_goal_1b.py:55-64, 77-122), one row per (T, stage)."""
+
+    import csv
+    import json
+    import subprocess
+    import sys
+
+    repo = Path(__file__).resolve().parents[1]
+    out = tmp_path / "stages.csv"
+    proc = subprocess.run(
+        [sys.executable, str(repo / "bench.py"), "--only-tokens", "1", "4", "--steps", "3",
+         "--warmup", "3", "--no-cpu-baseline", "--csv", str(out)],
+        capture_output=True, text=True, timeout=600, check=True,
+    )
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["csv"]["rows"] == 16
+    with out.open(newline="", encoding="utf-8") as handle:
+        rows = list(csv.DictReader(handle))
+    assert len(rows) == 16
+    assert list(rows[0].keys())[:5] == ["backend_set_requested", "requested_backend",
+                                        "actual_backend", "device", "gpu_name"]
+    assert len(rows[0]) == 44
+    stages = [r["stage"] for r in rows[:8]]
+    assert stages == ["routing_us", "permutation_us", "quantization_us", "gate_up_gemm_us",
+                      "swiglu_us", "down_gemm_us", "combine_us", "total_us"]
+    by_stage = {r["stage"]: r for r in rows[:8]}
+    assert by_stage["quantization_us"]["stage_status"] == "not_applicable"
+    assert by_stage["swiglu_us"]["stage_status"] == "fused_in_gate_up"
+    assert by_stage["total_us"]["stage_status"] == "measured"
+    assert float(by_stage["total_us"]["p50_us"]) > 50.0
+    assert all(r["used_fallback"] == "false" and r["architecture"] == "sm_100a" for r in rows)
+    assert {r["num_tokens"] for r in rows} == {"1", "4"}
