@@ -126,8 +126,53 @@ class ClockSampler:
         self.device_index = device_index
         self.proc: subprocess.Popen | None = None
         self.file = None
+        self._thread = None
+        self._stop = None
+        self._nvml_samples: list[tuple[float, int]] = []
+        self._nvml_max = None
+
+    # NVML in a background thread is the primary source (a sample every 20 ms, no process
+    # start-up inside a timed region that may last well under a second); nvidia-smi -lms is
+    # the fall-back when the NVML binding is missing.  Both only read.
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+
+    def _nvml_read(self, pynvml, handle) -> None:
+        clock = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        reader = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+            pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        self._nvml_samples.append((float(clock), int(reader(handle))))
 
     def start(self) -> None:
+        import threading
+
+        try:
+            pynvml, handle = self._nvml_handle()
+            self._nvml_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._stop = threading.Event()
+
+            def loop() -> None:
+                while not self._stop.is_set():
+                    try:
+                        self._nvml_read(pynvml, handle)
+                    except Exception:
+                        return
+                    self._stop.wait(0.02)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
@@ -138,7 +183,27 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _stop_nvml(self) -> dict[str, object]:
+        self._stop.set()
+        self._thread.join(timeout=2)
+        # NVML's reason bits (nvml.h): sw_power_cap 0x4, hw_slowdown 0x8,
+        # sw_thermal_slowdown 0x20, hw_thermal_slowdown 0x40
+        bits = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+                "hw_thermal_slowdown": 0x40}
+        clocks = sorted(c for c, _ in self._nvml_samples)
+        reasons = sorted(name for name, bit in bits.items()
+                         if any(mask & bit for _, mask in self._nvml_samples))
+        return {
+            "sm_mhz": percentile(clocks, 0.5) if clocks else None,
+            "sm_max_mhz": self._nvml_max,
+            "samples": len(clocks),
+            "source": "nvml, 20 ms period",
+            "reasons": reasons,
+        }
+
     def stop(self) -> dict[str, object]:
+        if self._thread is not None:
+            return self._stop_nvml()
         if self.proc is None or self.file is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -170,6 +235,7 @@ class ClockSampler:
             "sm_mhz": percentile(clocks, 0.5) if clocks else None,
             "sm_max_mhz": max_clock,
             "samples": len(clocks),
+            "source": "nvidia-smi -lms 100",
             "reasons": sorted(reasons),
         }
 
@@ -718,6 +784,43 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         timed_pass(forward_nccl, 3)
         nccl_samples = max_over_ranks(timed_pass(forward_nccl, max(5, args.steps // 2)))
 
+    # Sharded tokens (data-parallel attention in front of the layer): each rank holds T/N
+    # tokens, stores its shard into every rank's gathered buffers over NVLink (one launch of
+    # peer stores + a flag), computes its experts' share for all T tokens and reduces only
+    # its own T/N output rows.  Timed for every T of the sweep that divides evenly.
+    sharded_T = [T for T in SWEEP if T % world == 0]
+    sharded_samples, sharded_nccl_samples = {}, {}
+    if sharded_T:
+        def shard(T):
+            lo, hi = rank * (T // world), (rank + 1) * (T // world)
+            return tuple(t[lo:hi].contiguous() for t in cases[T]["dev"])
+
+        shards = {T: shard(T) for T in sharded_T}
+
+        def timed_sharded(engine, steps):
+            events = {T: [] for T in sharded_T}
+            for _ in range(steps):
+                for T in sharded_T:
+                    flush.fill_(1)
+                    drain.sum()
+                    a = torch.cuda.Event(enable_timing=True)
+                    b = torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    engine.forward(*shards[T], tokens="sharded")
+                    b.record()
+                    events[T].append((a, b))
+            torch.cuda.synchronize(device)
+            flat = torch.tensor([[a.elapsed_time(b) * 1e3 for a, b in events[T]]
+                                 for T in sharded_T], dtype=torch.float64, device=device)
+            dist.all_reduce(flat, op=dist.ReduceOp.MAX)
+            return {T: flat[i].tolist() for i, T in enumerate(sharded_T)}
+
+        timed_sharded(layer, 3)
+        sharded_samples = timed_sharded(layer, args.steps)
+        if layer is not baseline:
+            timed_sharded(baseline, 3)
+            sharded_nccl_samples = timed_sharded(baseline, max(5, args.steps // 2))
+
     host_us = {}
     for T in SWEEP:
         torch.cuda.synchronize(device)
@@ -766,6 +869,10 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         }
         if nccl_samples is not None:
             per_t[str(T)]["nccl_allreduce_baseline_us"] = summary(nccl_samples[T])
+        if T in sharded_samples:
+            per_t[str(T)]["sharded_tokens_us"] = summary(sharded_samples[T])
+        if T in sharded_nccl_samples:
+            per_t[str(T)]["sharded_tokens_nccl_baseline_us"] = summary(sharded_nccl_samples[T])
     p50s = [per_t[str(T)]["total_us"]["p50"] for T in SWEEP]
     e2e_p50s = [per_t[str(T)]["e2e_us"]["p50"] for T in SWEEP]
     gu_bytes = weight_bytes(max(r[-1] for r in active_by_rank))["gate_up"]
