@@ -8,6 +8,8 @@ Public names follow the reference package (fastpath/__init__.py:3-9) so that
 from ._lib import available as cuda_extension_available
 from ._lib import build_info
 from .forward import ARCHITECTURE, b300_moe_forward, b300_moe_forward_pinned
+from .fp8 import (Fp8ExpertWeights, b300_moe_forward_fp8, dequantize_expert_weights_fp8,
+                  dequantize_rows_fp8, quantize_expert_weights_fp8, quantize_rows_fp8)
 from .ops import DispatchResult, combine_tokens, dispatch_tokens
 from .router import topk_routing
 from .stages import StagedLayer
@@ -18,14 +20,20 @@ __all__ = [
     "ARCHITECTURE",
     "B300MoEWorkspace",
     "DispatchResult",
+    "Fp8ExpertWeights",
     "RoutedMoEShape",
     "StagedLayer",
     "b300_moe_forward",
+    "b300_moe_forward_fp8",
     "b300_moe_forward_pinned",
     "build_info",
     "combine_tokens",
     "cuda_extension_available",
+    "dequantize_expert_weights_fp8",
+    "dequantize_rows_fp8",
     "dispatch_tokens",
+    "quantize_expert_weights_fp8",
+    "quantize_rows_fp8",
     "topk_routing",
     "validate_routed_moe_inputs",
 ]

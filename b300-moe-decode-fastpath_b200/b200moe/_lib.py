@@ -16,7 +16,7 @@ from pathlib import Path
 from typing import Mapping
 
 LIBRARY_NAME = "libb200moe.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 STATUS_BAD_EXPERT_ID = 0x1
 STATUS_PIPE_TIMEOUT = 0x2
@@ -25,6 +25,7 @@ STATUS_PEER_TIMEOUT = 0x4
 FLAG_PDL = 0x1
 FLAG_LOCAL_EXPERTS = 0x2
 FLAG_F32_OUTPUT = 0x4
+FLAG_FP8_WEIGHTS = 0x8
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
@@ -34,6 +35,7 @@ TUNE_EVICT_FIRST = 3
 TUNE_EARLY_START = 4
 TUNE_DOWN_TARGET = 5
 TUNE_DOWN_SPLITS = 6
+TUNE_FP8_SEG_ROWS = 7
 
 EXPORTS = (
     "b200moe_abi_version",
@@ -48,6 +50,7 @@ EXPORTS = (
     "b200moe_combine",
     "b200moe_forward",
     "b200moe_dispatch",
+    "b200moe_dispatch_scratch_bytes",
     "b200moe_combine_bf16",
     "b200moe_ep_reduce",
     "b200moe_ep_push",
@@ -55,6 +58,8 @@ EXPORTS = (
     "b200moe_nvfp4_available",
     "b200moe_tune",
     "b200moe_router_topk",
+    "b200moe_fp8_quantize_rows",
+    "b200moe_fp8_dequantize_rows",
 )
 
 
@@ -93,6 +98,8 @@ class B200MoeArgs(ctypes.Structure):
         ("ep_world", ctypes.c_int32),
         ("ep_epoch", ctypes.c_uint32),
         ("ep_wait_limit_us", ctypes.c_uint32),
+        ("gate_up_scale", ctypes.c_void_p),
+        ("down_scale", ctypes.c_void_p),
     ]
 
 
@@ -171,6 +178,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [args_p, ctypes.c_void_p]
+    lib.b200moe_dispatch_scratch_bytes.restype = ctypes.c_int
+    lib.b200moe_dispatch_scratch_bytes.argtypes = [ctypes.c_int, ctypes.c_int,
+                                                   ctypes.POINTER(ctypes.c_size_t)]
     lib.b200moe_ep_reduce.restype = ctypes.c_int
     lib.b200moe_ep_reduce.argtypes = [ctypes.POINTER(B200MoeEpReduceArgs), ctypes.c_void_p]
     lib.b200moe_combine_bf16.restype = ctypes.c_int
@@ -192,6 +202,16 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200moe_router_topk.argtypes = [
         ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+    ]
+    lib.b200moe_fp8_quantize_rows.restype = ctypes.c_int
+    lib.b200moe_fp8_quantize_rows.argtypes = [
+        ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p,
+    ]
+    lib.b200moe_fp8_dequantize_rows.restype = ctypes.c_int
+    lib.b200moe_fp8_dequantize_rows.argtypes = [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p,
+        ctypes.c_void_p,
     ]
     lib.b200moe_tune.restype = ctypes.c_int
     lib.b200moe_tune.argtypes = [ctypes.c_int, ctypes.c_int]
@@ -265,6 +285,13 @@ def build_info() -> Mapping[str, object]:
     buffer = ctypes.create_string_buffer(1024)
     lib.b200moe_build_info(buffer, len(buffer))
     return json.loads(buffer.value.decode())
+
+
+def dispatch_scratch_bytes(rows_cap: int, num_experts: int) -> int:
+    size = ctypes.c_size_t(0)
+    check(load().b200moe_dispatch_scratch_bytes(rows_cap, num_experts, ctypes.byref(size)),
+          "b200moe_dispatch_scratch_bytes")
+    return int(size.value)
 
 
 def scratch_bytes(

@@ -94,7 +94,7 @@ def dispatch_tokens(
     assignment_to_permuted = torch.empty(rows, **long)
     permuted_to_assignment = torch.empty(rows, **long)
     permuted_hidden = torch.empty(rows, hidden, dtype=hidden_states.dtype, device=device)
-    need = 256 + 4 * (8 + 4 * (min(rows, num_experts) + rows // 128 + 1))
+    need = _lib.dispatch_scratch_bytes(rows, num_experts)
     base = torch.empty(need + _SCRATCH_ALIGN, dtype=torch.uint8, device=device)
     skew = (-base.data_ptr()) % _SCRATCH_ALIGN
 

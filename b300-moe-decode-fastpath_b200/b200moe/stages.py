@@ -29,26 +29,41 @@ class StagedLayer:
         hidden_states: torch.Tensor,
         expert_indices: torch.Tensor,
         expert_weights: torch.Tensor,
-        gate_up_weight: torch.Tensor,
-        down_weight: torch.Tensor,
+        gate_up_weight: torch.Tensor | None,
+        down_weight: torch.Tensor | None,
         *,
         num_experts: int,
         top_k: int,
         workspace: B300MoEWorkspace | None = None,
         use_pdl: bool = True,
+        fp8_weights=None,
     ) -> None:
-        self.shape = validate_routed_moe_inputs(
-            hidden_states,
-            expert_indices,
-            expert_weights,
-            gate_up_weight,
-            down_weight,
-            num_experts=num_experts,
-            top_k=top_k,
-        )
-        _resolve_native_backend(
-            "b200_bf16", hidden_states, expert_weights, gate_up_weight, down_weight, self.shape
-        )
+        """``fp8_weights`` (an ``Fp8ExpertWeights``) selects the FP8-weight kernels; the two
+        BF16 weight arguments are then ignored and may be ``None``."""
+
+        flags = _lib.FLAG_PDL if use_pdl else 0
+        if fp8_weights is not None:
+            from .fp8 import _validate as validate_fp8
+
+            self.shape = validate_fp8(hidden_states, expert_indices, expert_weights, fp8_weights,
+                                      num_experts, top_k)
+            gate_up_weight, down_weight = fp8_weights.gate_up_q, fp8_weights.down_q
+            _resolve_native_backend("b200_fp8", hidden_states, expert_weights,
+                                    fp8_weights.gate_up_scale, fp8_weights.down_scale, self.shape)
+            flags |= _lib.FLAG_FP8_WEIGHTS
+        else:
+            self.shape = validate_routed_moe_inputs(
+                hidden_states,
+                expert_indices,
+                expert_weights,
+                gate_up_weight,
+                down_weight,
+                num_experts=num_experts,
+                top_k=top_k,
+            )
+            _resolve_native_backend(
+                "b200_bf16", hidden_states, expert_weights, gate_up_weight, down_weight, self.shape
+            )
         self.device = hidden_states.device
         self.workspace = workspace or B300MoEWorkspace(device=self.device)
         self.workspace.reserve(
@@ -64,7 +79,8 @@ class StagedLayer:
         )
         self.output = torch.empty_like(hidden_states)
         # keep the inputs alive for as long as their addresses sit in the struct
-        self._inputs = (hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight)
+        self._inputs = (hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight,
+                        fp8_weights)
         # a private struct: the workspace keeps its own bound struct for forward calls
         self._args = _lib.B200MoeArgs()
         bound = _native_args(
@@ -76,9 +92,12 @@ class StagedLayer:
             self.shape,
             self.workspace,
             self.output,
-            _lib.FLAG_PDL if use_pdl else 0,
+            flags,
         )
         ctypes.memmove(ctypes.byref(self._args), ctypes.byref(bound), ctypes.sizeof(bound))
+        if fp8_weights is not None:
+            self._args.gate_up_scale = fp8_weights.gate_up_scale.data_ptr()
+            self._args.down_scale = fp8_weights.down_scale.data_ptr()
         lib = _lib.load()
         self._calls = {
             "routing": lib.b200moe_routing,

@@ -20,7 +20,8 @@ from pathlib import Path
 PACKAGE_ROOT = Path(__file__).resolve().parent
 CSRC = PACKAGE_ROOT / "csrc"
 INCLUDE = PACKAGE_ROOT.parent / "include"
-SOURCES = ("api.cu", "routing.cu", "rows.cu", "grouped_gemm.cu", "ep_reduce.cu", "router.cu")
+SOURCES = ("api.cu", "routing.cu", "rows.cu", "grouped_gemm.cu", "grouped_gemm_fp8.cu",
+           "quant.cu", "ep_reduce.cu", "router.cu")
 HEADERS = (CSRC / "common.cuh", INCLUDE / "b200moe.h")
 LIBRARY = PACKAGE_ROOT / "b200moe" / "libb200moe.so"
 GENCODE = "arch=compute_100a,code=sm_100a"

@@ -18,7 +18,7 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
-                           int target_ctas, int id_base, bool foreign_ids_allowed,
+                           int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
                            unsigned long long wait_limit_ns, cudaStream_t stream);
 cudaError_t launch_ep_push(const void* hidden, const int64_t* ids, const void* weights,
@@ -51,6 +51,29 @@ cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
                         cudaStream_t stream);
 
+cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
+                               const int32_t* sched, uint32_t* status, void* act_hi,
+                               void* act_lo, uint32_t* act_amax, const float* row_scale,
+                               const float* token_scale, int inter, int hidden, int rows_cap,
+                               int grid, bool pdl, cudaStream_t stream);
+cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
+                            const int32_t* sched, uint32_t* status, float* partials,
+                            const float* row_scale, const float* token_scale, int hidden,
+                            int inter, int rows_cap, int grid, bool pdl, cudaStream_t stream);
+cudaError_t launch_gather_fp8(const void* hidden, const int64_t* permutation, void* out,
+                              uint8_t* planes, float* row_scale, uint32_t* act_amax,
+                              int num_assign, int num_tokens, int top_k, int hidden_size,
+                              int rows_cap, unsigned long long* trace, bool pdl,
+                              cudaStream_t stream);
+cudaError_t launch_act_planes_fp8(const void* act_hi, const void* act_lo,
+                                  const uint32_t* act_amax, uint8_t* planes, float* row_scale,
+                                  int num_assign, int inter, int rows_cap, bool pdl,
+                                  cudaStream_t stream);
+cudaError_t launch_fp8_quantize_rows(const void* w, long long rows, int cols, uint8_t* q,
+                                     float* scale, cudaStream_t stream);
+cudaError_t launch_fp8_dequantize_rows(const uint8_t* q, const float* scale, long long rows,
+                                       int cols, void* out, cudaStream_t stream);
+
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
                                 const void* weights, void* out, int num_tokens, int top_k,
                                 int hidden_size, cudaStream_t stream);
@@ -72,6 +95,7 @@ namespace {
 int g_l2_promotion = 2;  // 0 none, 1 128 B, 2 256 B
 int g_down_target = 0;   // blocks the down projection's split-K aims at (0: 2 per SM)
 
+int g_fp8_seg_rows = kSegRowsFp8;  // segment length of the FP8-weight path (16, 32, 48 or 64)
 int g_down_splits = 0;   // forced split-K factor of the down projection (0: chosen on the device)
 
 int down_target(int sm_count) { return g_down_target > 0 ? g_down_target : 2 * sm_count; }
@@ -127,17 +151,17 @@ int resolve_encoder() {
   return g_encode ? 0 : B200MOE_E_DRIVER;
 }
 
-// BF16 tensor map, innermost dimension first, 128-byte swizzle, zero fill
-// outside the tensor.  `dims`/`box` have `rank` entries.
-int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                    const uint32_t* box) {
+// Tensor map of BF16 (or, with `bytes`, one-byte) elements, innermost dimension first,
+// 128-byte swizzle, zero fill outside the tensor.  `dims`/`box` have `rank` entries.
+int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+               const uint32_t* box, bool bytes) {
   int rc = resolve_encoder();
   if (rc) return rc;
   cuuint64_t gdim[5];
   cuuint64_t gstride[4];
   cuuint32_t bdim[5];
   cuuint32_t estride[5];
-  uint64_t stride = sizeof(__nv_bfloat16);
+  uint64_t stride = bytes ? 1 : sizeof(__nv_bfloat16);
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     bdim[i] = box[i];
@@ -149,11 +173,17 @@ int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t
       g_l2_promotion == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
                           : (g_l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
                                                  : CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
+  CUresult r = g_encode(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        (cuuint32_t)rank,
                         const_cast<void*>(base), gdim, gstride, bdim, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
+}
+
+int encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint32_t* box) {
+  return encode_map(map, base, rank, dims, box, false);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -171,9 +201,11 @@ int check_shape(int tokens, int top_k, int experts, int hidden, int inter,
 }
 
 // Upper bound on the number of segments `rows` assignments can produce.
-int segment_bound(int rows, int experts) {
-  return (rows < experts ? rows : experts) + rows / kSegRows;
+int segment_bound(int rows, int experts, int seg_rows = kSegRows) {
+  return (rows < experts ? rows : experts) + rows / seg_rows;
 }
+
+bool fp8_weights(const B200MoeArgs* a) { return (a->flags & B200MOE_FLAG_FP8_WEIGHTS) != 0; }
 
 int tiles128(int n) { return (n + 127) / 128; }
 
@@ -182,6 +214,10 @@ struct Scratch {
   int32_t* sched;
   void* act_lo;
   float* partials;
+  uint8_t* q_planes;   // FP8-weight path: token operand as three E4M3 planes
+  float* x_scale;
+  float* a_scale;
+  uint32_t* a_amax;
 };
 
 int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts, int hidden,
@@ -195,6 +231,10 @@ int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts
   out->sched = reinterpret_cast<int32_t*>(b + l.sched);
   out->act_lo = b + l.act_lo;
   out->partials = reinterpret_cast<float*>(b + l.partials);
+  out->q_planes = reinterpret_cast<uint8_t*>(b + l.q_planes);
+  out->x_scale = reinterpret_cast<float*>(b + l.x_scale);
+  out->a_scale = reinterpret_cast<float*>(b + l.a_scale);
+  out->a_amax = reinterpret_cast<uint32_t*>(b + l.a_amax);
   return 0;
 }
 
@@ -206,7 +246,10 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              a->reverse_mapping, a->permutation, a->expert_offsets_i32,
                              a->permuted_token_indices, a->permuted_expert_indices,
                              a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
-                             (a->intermediate_size + 63) / 64, down_split_request(dev.sm_count),
+                             fp8_weights(a) ? (a->intermediate_size + 127) / 128
+                                            : (a->intermediate_size + 63) / 64,
+                             down_split_request(dev.sm_count),
+                             fp8_weights(a) ? g_fp8_seg_rows : kSegRows,
                              local ? a->expert_id_base : 0, local,
                              static_cast<const uint32_t*>(a->ep_wait_flags), a->ep_world,
                              a->ep_epoch,
@@ -235,7 +278,8 @@ int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int 
   const int grid = segment_bound(assignments, experts) * tiles128(inter);
   // hidden_states [T,H] with one-row boxes: blocks with few rows fetch them from here
   CUtensorMap map_hidden;
-  const bool have_hidden = ids != nullptr && hidden_states != nullptr && aligned16(hidden_states);
+  const bool have_hidden = g_early_mode >= 2 && ids != nullptr && hidden_states != nullptr &&
+                           aligned16(hidden_states);
   if (have_hidden) {
     const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)(assignments / top_k)};
     const uint32_t box[2] = {64, 1};
@@ -271,14 +315,89 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   if (g_down_splits > 0) {
     grid *= g_down_splits;
   } else {
+    // remembered per thread: a decode loop asks for the same geometry every step
+    struct Memo { int bound, tiles, kblocks, target, grid; };
+    static thread_local Memo memo = {0, 0, 0, 0, 0};
+    const int bound = segment_bound(assignments, experts);
     const int target = down_target(dev.sm_count);
-    for (int segs = 1; segs <= segment_bound(assignments, experts); ++segs) {
-      const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
-      if (n > grid) grid = n;
+    if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
+        memo.target != target) {
+      int worst = grid;
+      for (int segs = 1; segs <= bound; ++segs) {
+        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
+        if (n > worst) worst = n;
+      }
+      memo = {bound, tiles, kblocks, target, worst};
     }
+    grid = memo.grid;
   }
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
                           rows_cap, grid, pdl, stream);
+}
+
+// FP8 weights: one-byte tensor maps of the weights and of the token planes.
+int encode_plane_map(CUtensorMap* map, const uint8_t* planes, int cols, int rows_cap) {
+  const uint64_t dims[3] = {(uint64_t)cols, (uint64_t)rows_cap, (uint64_t)kFp8Planes};
+  const uint32_t box[3] = {128, 16, 1};
+  return encode_map(map, planes, 3, dims, box, true);
+}
+
+int do_gate_up_fp8(const void* w, const float* row_scale, int rows_cap, int assignments,
+                   int experts, int hidden, int inter, void* act_hi, const Scratch& s, bool pdl,
+                   cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  {
+    const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
+    const uint32_t box[4] = {128, 64, 2, 1};  // 64 gate rows + the 64 matching up rows
+    int rc = encode_map(&map_w, w, 4, dims, box, true);
+    if (rc) return rc;
+  }
+  int rc = encode_plane_map(&map_x, s.q_planes, hidden, rows_cap);
+  if (rc) return rc;
+  const int grid = segment_bound(assignments, experts, g_fp8_seg_rows) * ((inter + 63) / 64);
+  return (int)launch_gate_up_fp8(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, s.a_amax,
+                                 row_scale, s.x_scale, inter, hidden, rows_cap, grid, pdl,
+                                 stream);
+}
+
+int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int rows_cap,
+                int assignments, int experts, int hidden, int inter, const Scratch& s,
+                const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
+  CUtensorMap map_w, map_act;
+  {
+    const uint64_t dims[3] = {(uint64_t)inter, (uint64_t)hidden, (uint64_t)experts};
+    const uint32_t box[3] = {128, 128, 1};
+    int rc = encode_map(&map_w, w, 3, dims, box, true);
+    if (rc) return rc;
+  }
+  int rc = encode_plane_map(&map_act, s.q_planes, inter, rows_cap);
+  if (rc) return rc;
+  const int bound = segment_bound(assignments, experts, g_fp8_seg_rows);
+  const int tiles = tiles128(hidden), kblocks = (inter + 127) / 128;
+  int grid = bound * tiles;
+  if (g_down_splits > 0) {
+    grid *= g_down_splits;
+  } else {
+    struct Memo { int bound, tiles, kblocks, target, grid; };
+    static thread_local Memo memo = {0, 0, 0, 0, 0};
+    const int target = down_target(dev.sm_count);
+    if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
+        memo.target != target) {
+      int worst = grid;
+      for (int segs = 1; segs <= bound; ++segs) {
+        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
+        if (n > worst) worst = n;
+      }
+      memo = {bound, tiles, kblocks, target, worst};
+    }
+    grid = memo.grid;
+  }
+  // the activation rows become planes (in the bytes the gathered rows occupied), then the GEMM
+  rc = (int)launch_act_planes_fp8(act_hi, s.act_lo, s.a_amax, s.q_planes, s.a_scale, assignments,
+                                  inter, rows_cap, pdl, stream);
+  if (rc) return rc;
+  return (int)launch_down_fp8(map_w, map_act, s.sched, s.status, s.partials, row_scale,
+                              s.a_scale, hidden, inter, rows_cap, grid, pdl, stream);
 }
 
 unsigned long long* trace_of(const Scratch& s) {
@@ -325,6 +444,11 @@ int stage_routing(const B200MoeArgs* a, const Ctx& c) {
 int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (!a->hidden_states || !a->permutation || !a->permuted_hidden) return B200MOE_E_NULL;
   if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
+  if (fp8_weights(a))
+    return (int)launch_gather_fp8(a->hidden_states, a->permutation, a->permuted_hidden,
+                                  c.s.q_planes, c.s.x_scale, c.s.a_amax, c.assignments,
+                                  a->num_tokens, a->top_k, a->hidden_size, a->rows_cap,
+                                  trace_of(c.s), pdl, c.stream);
   return (int)launch_gather(a->hidden_states, a->permutation, a->permuted_hidden, c.assignments,
                             a->num_tokens, a->top_k, a->hidden_size, g_early_mode >= 1,
                             trace_of(c.s), pdl, c.stream);
@@ -335,6 +459,13 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (!aligned16(a->permuted_hidden) || !aligned16(a->gate_up_weight) ||
       !aligned16(a->swiglu_output))
     return B200MOE_E_ALIGN;
+  if (fp8_weights(a)) {
+    if (!a->gate_up_scale) return B200MOE_E_NULL;
+    if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
+    return do_gate_up_fp8(a->gate_up_weight, a->gate_up_scale, a->rows_cap, c.assignments,
+                          a->num_experts, a->hidden_size, a->intermediate_size,
+                          a->swiglu_output, c.s, pdl, c.stream);
+  }
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
                     a->ep_wait_flags ? nullptr : a->expert_indices,
@@ -345,6 +476,13 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
 int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (!a->swiglu_output || !a->down_weight) return B200MOE_E_NULL;
   if (!aligned16(a->swiglu_output) || !aligned16(a->down_weight)) return B200MOE_E_ALIGN;
+  if (fp8_weights(a)) {
+    if (!a->down_scale) return B200MOE_E_NULL;
+    if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
+    return do_down_fp8(a->swiglu_output, a->down_weight, a->down_scale, a->rows_cap,
+                       c.assignments, a->num_experts, a->hidden_size, a->intermediate_size, c.s,
+                       c.dev, pdl, c.stream);
+  }
   return do_down(a->swiglu_output, a->down_weight, a->rows_cap, c.assignments, a->num_experts,
                  a->hidden_size, a->intermediate_size, c.s, c.dev, pdl, c.stream);
 }
@@ -378,6 +516,7 @@ int b200moe_build_info(char* json, size_t cap) {
       "\"bf16_grouped_gemm_provider\": \"b200moe tcgen05 grouped GEMM (in-tree, hand-written)\", "
       "\"bf16_provider_implementation\": \"tcgen05.mma kind::f16, TMEM accumulators, TMA 128B-swizzle loads\", "
       "\"cutlass_version\": null, \"cuda_runtime_version\": %d, \"nvfp4_compiled\": false, "
+      "\"fp8_weights_compiled\": true, "
       "\"abi_version\": %d, \"segment_rows\": %d, \"down_split_max\": %d}",
       (int)CUDART_VERSION, B200MOE_ABI_VERSION, kSegRows, kDownSplitMax);
   if (json && cap > 0) {
@@ -439,6 +578,30 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
                                  static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_fp8_quantize_rows(const void* weights_bf16, long long rows, int cols, uint8_t* q_out,
+                              float* scale_out, void* stream) {
+  if (!weights_bf16 || !q_out || !scale_out) return B200MOE_E_NULL;
+  if (rows < 1 || rows > 0x7fffffffll || cols < 16) return B200MOE_E_SHAPE;
+  if (cols % 16 || !aligned16(weights_bf16) || !aligned16(q_out)) return B200MOE_E_ALIGN;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_fp8_quantize_rows(weights_bf16, rows, cols, q_out, scale_out,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_fp8_dequantize_rows(const uint8_t* q, const float* scale, long long rows, int cols,
+                                void* out_bf16, void* stream) {
+  if (!q || !out_bf16) return B200MOE_E_NULL;
+  if (rows < 1 || rows > 0x7fffffffll || cols < 16) return B200MOE_E_SHAPE;
+  if (cols % 16 || !aligned16(q) || !aligned16(out_bf16)) return B200MOE_E_ALIGN;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_fp8_dequantize_rows(q, scale, rows, cols, out_bf16,
+                                         static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_tune(int knob, int value) {
   switch (knob) {
     case B200MOE_TUNE_STAGE_KB:
@@ -459,6 +622,10 @@ int b200moe_tune(int knob, int value) {
     case B200MOE_TUNE_DOWN_SPLITS:
       if (value < 0 || value > kDownSplitMax) return B200MOE_E_SHAPE;
       g_down_splits = value;
+      return 0;
+    case B200MOE_TUNE_FP8_SEG_ROWS:
+      if (value < 16 || value > kSegRowsFp8 || value % 16) return B200MOE_E_SHAPE;
+      g_fp8_seg_rows = value;
       return 0;
     case B200MOE_TUNE_EARLY_START:
       if (value < 0 || value > 2) return B200MOE_E_SHAPE;
@@ -541,6 +708,18 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
                                static_cast<cudaStream_t>(stream));
 }
 
+static size_t dispatch_scratch_need(int rows_cap, int experts) {
+  return kStatusBytes +
+         sizeof(int32_t) * (kSchedHeaderWords + (size_t)kSchedSegWords * max_segments(rows_cap, experts));
+}
+
+int b200moe_dispatch_scratch_bytes(int rows_cap, int num_experts, size_t* bytes) {
+  if (!bytes) return B200MOE_E_NULL;
+  if (rows_cap < 1 || num_experts < 1 || num_experts > B200MOE_MAX_EXPERTS) return B200MOE_E_SHAPE;
+  *bytes = dispatch_scratch_need(rows_cap, num_experts);
+  return 0;
+}
+
 int b200moe_dispatch(const B200MoeArgs* a, void* stream) {
   if (!a) return B200MOE_E_NULL;
   if (!a->hidden_states || !a->expert_indices || !a->expert_counts || !a->expert_offsets ||
@@ -554,10 +733,7 @@ int b200moe_dispatch(const B200MoeArgs* a, void* stream) {
   if (a->rows_cap < assignments) return B200MOE_E_SHAPE;
   if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
   if (reinterpret_cast<uintptr_t>(a->scratch) % kScratchAlign) return B200MOE_E_ALIGN;
-  const size_t need = kStatusBytes + sizeof(int32_t) * (kSchedHeaderWords +
-                                                        (size_t)kSchedSegWords *
-                                                            max_segments(a->rows_cap,
-                                                                         a->num_experts));
+  const size_t need = dispatch_scratch_need(a->rows_cap, a->num_experts);
   if (a->scratch_bytes < need) return B200MOE_E_SCRATCH;
   Ctx c;
   rc = current_device_info(&c.dev);
@@ -628,6 +804,10 @@ int b200moe_forward(const B200MoeArgs* a, void* stream) {
       !aligned16(a->swiglu_output) || !aligned16(a->output) ||
       (a->expert_output && !aligned16(a->expert_output)))
     return B200MOE_E_ALIGN;
+  if (fp8_weights(a)) {
+    if (!a->gate_up_scale || !a->down_scale) return B200MOE_E_NULL;
+    if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
+  }
   if ((rc = stage_routing(a, c))) return rc;
   if ((rc = stage_gather(a, c, c.pdl))) return rc;
   if ((rc = stage_gate_up(a, c, c.pdl))) return rc;

@@ -19,6 +19,8 @@ namespace b200moe {
 // one tcgen05 accumulator tile.
 // ---------------------------------------------------------------------------
 constexpr int kSegRows = 128;        // max token rows per segment (MMA N <= 128)
+constexpr int kSegRowsFp8 = 64;      // ... when the weights are FP8: the converted-tile buffers
+                                     // take the shared memory the longer token tiles would need
 constexpr int kDownSplitMax = 8;     // max split-K factor of the down projection
 constexpr int kSchedHeaderWords = 8;
 constexpr int kSchedSegWords = 4;    // {expert, row_start, n_rows, reserved}
@@ -27,6 +29,7 @@ enum SchedWord {
   kSchedNumActive = 1,      // experts with at least one row
   kSchedNumValidRows = 2,   // rows with an in-range expert id
   kSchedDownSplits = 3,     // split-K factor chosen for the down projection
+  kSchedSegRows = 4,        // segment length this schedule was built with
 };
 
 // Split-K factor of the down projection for `units` (segment, tile) work units, each of
@@ -72,7 +75,7 @@ __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a -
 
 __host__ __device__ inline int max_segments(int rows, int experts) {
   int active = rows < experts ? rows : experts;
-  return active + rows / kSegRows + 1;
+  return active + rows / 16 + 1;  // sized for the shortest segment length any path uses
 }
 
 // Byte offsets of the private scratch region for `rows_cap` expert-major rows.
@@ -81,8 +84,17 @@ struct ScratchLayout {
   size_t sched;      // int32[kSchedHeaderWords + kSchedSegWords * max_segments]
   size_t act_lo;     // bf16 [rows_cap, I]   low-order halves of the SwiGLU activations
   size_t partials;   // fp32 [kDownSplitMax, rows_cap, H]
+  // FP8-weight path only: the token operand of both GEMMs as three E4M3 planes per row
+  // (first the gathered hidden rows [3][rows_cap][H], later, in the same bytes, the
+  // activations [3][rows_cap][I]) and the per-row scales that go with them
+  size_t q_planes;   // uint8 [3, rows_cap, max(H, I)]
+  size_t x_scale;    // fp32 [rows_cap]
+  size_t a_scale;    // fp32 [rows_cap]
+  size_t a_amax;     // uint32 [rows_cap]  bit pattern of max |activation| per row
   size_t total;
 };
+
+constexpr int kFp8Planes = 3;
 
 __host__ __device__ inline ScratchLayout scratch_layout(int rows_cap, int experts, int hidden,
                                                         int inter) {
@@ -93,8 +105,13 @@ __host__ __device__ inline ScratchLayout scratch_layout(int rows_cap, int expert
       sizeof(int32_t) * (kSchedHeaderWords + (size_t)kSchedSegWords * max_segments(rows_cap, experts));
   l.act_lo = align_up(l.sched + sched_bytes, kScratchAlign);
   l.partials = align_up(l.act_lo + (size_t)rows_cap * inter * sizeof(__nv_bfloat16), kScratchAlign);
-  l.total = align_up(l.partials + (size_t)kDownSplitMax * rows_cap * hidden * sizeof(float),
-                     kScratchAlign);
+  l.q_planes = align_up(l.partials + (size_t)kDownSplitMax * rows_cap * hidden * sizeof(float),
+                        kScratchAlign);
+  const size_t widest = (size_t)(hidden > inter ? hidden : inter);
+  l.x_scale = align_up(l.q_planes + (size_t)kFp8Planes * rows_cap * widest, kScratchAlign);
+  l.a_scale = align_up(l.x_scale + (size_t)rows_cap * sizeof(float), kScratchAlign);
+  l.a_amax = align_up(l.a_scale + (size_t)rows_cap * sizeof(float), kScratchAlign);
+  l.total = align_up(l.a_amax + (size_t)rows_cap * sizeof(uint32_t), kScratchAlign);
   return l;
 }
 
@@ -307,6 +324,39 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16_m128(uint32_t n) {
          | ((128u >> 4) << 24);  // M / 16
 }
 
+// D[tmem] (+)= A[smem] * B[smem]^T with 8-bit floating-point inputs (formats in the
+// instruction descriptor), FP32 accumulate, K = 32 per instruction, issued by ONE thread.
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor: E4M3 x E4M3 -> FP32, both operands K-major, M=128.
+__device__ __forceinline__ uint32_t umma_idesc_e4m3_m128(uint32_t n) {
+  return (1u << 4)             // accumulator format FP32
+         | (0u << 7)           // A format E4M3
+         | (0u << 10)          // B format E4M3
+         | ((n >> 3) << 17)    // N / 8
+         | ((128u >> 4) << 24);  // M / 16
+}
 
+// Four E4M3 bytes (K order k0..k3 from the low byte up) -> two packed BF16 pairs (k0,k1)
+// and (k2,k3).  An E4M3 byte s.eeee.mmm placed at BF16 bits [15] and [10:4] reads as the
+// same value times 2^-120 (a BF16 subnormal where the E4M3 exponent field is zero); one
+// packed multiply by 2^120 restores it exactly.  Bytes 0x7F/0xFF (E4M3 NaN, never
+// produced by the quantiser here) come out as +-480.
+__device__ __forceinline__ void e4m3x4_to_bf16x4(uint32_t w, uint32_t& p01, uint32_t& p23) {
+  const uint32_t y0 = __byte_perm(w, 0u, 0x1404);  // (b0 << 8) | (b1 << 24)
+  const uint32_t y1 = __byte_perm(w, 0u, 0x3424);  // (b2 << 8) | (b3 << 24)
+  const uint32_t r0 = (y0 & 0x80008000u) | ((y0 >> 4) & 0x07F007F0u);
+  const uint32_t r1 = (y1 & 0x80008000u) | ((y1 >> 4) & 0x07F007F0u);
+  const uint32_t two120 = 0x7B807B80u;             // BF16 2^120, twice
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(p01) : "r"(r0), "r"(two120));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(p23) : "r"(r1), "r"(two120));
+}
 
 }  // namespace b200moe

@@ -1,0 +1,398 @@
+// Stages 3 and 4 with FP8 (E4M3) expert weights, on tcgen05.mma kind::f8f6f4.
+//
+// No counterpart in the reference, which lists quantised expert weights as future work
+// (docs/goal_1b_report.md:313-314).  The layer is bound by streaming each active expert's
+// weights once, so storing them as one E4M3 byte per element (plus an FP32 scale per
+// weight row) halves the time of both GEMMs.
+//
+// The tensor core has no FP8 x BF16 mode, and converting the weight stream in shared
+// memory costs more than the bytes it saves (measured: slower than the BF16 kernels).
+// So the weights go from TMA straight into the MMA, and the small operand -- the token
+// rows -- is what gets converted, once per row and not once per weight byte: every row r
+// is held as three E4M3 planes and a scale s_r with
+//     x[r, k] ~= s_r * (p0[r,k] + p1[r,k] / 16 + p2[r,k] / 256),
+// twelve significant bits relative to the row maximum (BF16 has eight).  Each plane is
+// multiplied with the weight tile into its own FP32 accumulator in tensor memory; the
+// epilogue adds the three with their weights and applies s_r and the weight row's scale.
+//
+// Same structure as the BF16 kernels otherwise: one block = (segment of <= 64 rows,
+// 128-row weight tile[, K split]); warp 0 = TMA producer, warp 1 = TMEM allocation + MMA
+// issue, warps 2..5 = epilogue; two blocks per SM; every wait bounded.
+//
+// gate+up: the 128 weight rows of a tile are 64 gate rows and the 64 matching up rows (one
+// 4-D TMA box over [E][2][I][H]), so accumulator lanes 0..63 hold gate and 64..127 hold up;
+// the up half crosses to the gate half's threads through shared memory.  Besides the
+// hi/lo BF16 activations it records each row's max |activation| (atomicMax on the bit
+// pattern), from which the rows are re-quantised into planes for the down projection.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kQThreads = 192;
+constexpr int kQStageK = 128;   // E4M3 elements (= bytes) per pipeline stage along K
+constexpr int kQTileM = 128;
+constexpr int kQMaxStages = 8;
+constexpr uint32_t kQABytes = kQTileM * kQStageK;  // 16 KB of weights per stage
+constexpr uint64_t kQAbortDrainNs = 1000000ull;
+
+struct QGemmParams {
+  const int32_t* sched;
+  uint32_t* status;
+  __nv_bfloat16* act_hi;      // gate+up output [rows_cap, I]
+  __nv_bfloat16* act_lo;
+  uint32_t* act_amax;         // gate+up output [rows_cap]: bit pattern of max |act| per row
+  float* partials;            // down output [splits][rows_cap][H]
+  const float* row_scale;     // weights: gate+up [E, 2I]; down [E, H]
+  const float* token_scale;   // planes: [rows_cap]
+  int m_total;                // I (gate+up) or H (down)
+  int k_total;                // H (gate+up) or I (down)
+  int m_tiles;                // ceil(I / 64) (gate+up) or ceil(H / 128) (down)
+  int rows_cap;
+  unsigned long long* trace;
+  uint32_t stage_budget;
+};
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(kQThreads, 2)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
+                        const __grid_constant__ CUtensorMap map_b, const QGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_full[kQMaxStages];
+  __shared__ __align__(8) uint64_t s_empty[kQMaxStages];
+  __shared__ __align__(8) uint64_t s_acc;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kQMaxStages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_acc), 1);
+    s_abort = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_b);
+  }
+
+  // ---- this block's unit (the schedule is final before this grid can start) ----------
+  int unit = blockIdx.x;
+  int split = 0, n_split = 1;
+  const int n_seg = p.sched[kSchedNumSegments];
+  if (!kGateUp) {
+    n_split = p.sched[kSchedDownSplits];
+    split = unit % n_split;
+    unit /= n_split;
+  }
+  const int seg = unit / p.m_tiles;
+  if (seg >= n_seg) return;
+  const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
+  const int expert = seg_words[0];
+  const int row_start = seg_words[1];
+  const int n_rows = seg_words[2];
+  const int tile = unit % p.m_tiles;
+  const int n_mma = (n_rows + 15) & ~15;  // accumulator columns per plane: 16..64
+  trace_start(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
+
+  const int kblocks = (p.k_total + kQStageK - 1) / kQStageK;
+  int kb0 = 0, num_kb = kblocks;
+  if (!kGateUp) {
+    const int per = kblocks / n_split, rem = kblocks % n_split;
+    kb0 = split * per + min(split, rem);
+    num_kb = per + (split < rem ? 1 : 0);
+  }
+
+  // ---- shared-memory pipeline geometry ----------------------------------------------
+  const uint32_t plane_bytes = (uint32_t)n_mma * 128u;
+  const uint32_t stage_bytes = kQABytes + (uint32_t)kFp8Planes * plane_bytes;
+  const int num_stages = min((int)(p.stage_budget / stage_bytes), kQMaxStages);
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abort_flag = &s_abort;
+  if (num_stages < 2 || n_mma > kSegRowsFp8) {
+    // a schedule with segments longer than this kernel supports: a caller error; report
+    if (threadIdx.x == 0) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
+    return;
+  }
+
+  auto load_weights = [&](uint32_t dst, uint32_t bar, int kc) {
+    if (kGateUp) tma_load_4d(dst, &map_w, bar, kc, tile * 64, 0, expert);
+    else tma_load_3d(dst, &map_w, bar, kc, tile * kQTileM, expert);
+  };
+  auto load_tokens = [&](uint32_t b_dst, uint32_t bar, int kc) {
+    for (int pl = 0; pl < kFp8Planes; ++pl)
+      for (int r = 0; r < n_mma; r += 16)
+        tma_load_3d(b_dst + (uint32_t)pl * plane_bytes + (uint32_t)r * 128u, &map_b, bar, kc,
+                    row_start + r, pl);
+  };
+
+  // Weight prefetch: fill the first stages' weight tiles while the previous kernel is
+  // still finishing; the token planes of those stages follow after the dependency wait.
+  const int prefetched = min(num_stages, num_kb);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < prefetched; ++i) {
+      const uint32_t bar = smem_u32(&s_full[i]);
+      mbar_expect_tx(bar, stage_bytes);
+      load_weights(smem_base + (uint32_t)i * stage_bytes, bar, (kb0 + i) * kQStageK);
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // ---- tensor memory: three accumulators of n_mma columns ---------------------------------
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < (uint32_t)(kFp8Planes * n_mma)) tmem_cols <<= 1;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % num_stages;
+        const uint32_t round = (uint32_t)(i / num_stages);
+        if (i >= num_stages &&
+            !mbar_wait_bounded(smem_u32(&s_empty[s]), (round - 1u) & 1u, abort_flag))
+          break;
+        const uint32_t bar = smem_u32(&s_full[s]);
+        const uint32_t a_dst = smem_base + (uint32_t)s * stage_bytes;
+        const int kc = (kb0 + i) * kQStageK;
+        if (i >= prefetched) {
+          mbar_expect_tx(bar, stage_bytes);
+          load_weights(a_dst, bar, kc);
+        }
+        load_tokens(a_dst + kQABytes, bar, kc);
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      // The three planes of a stage lie one after another in shared memory, n_mma rows
+      // each: one K-major operand of 3 * n_mma rows.  A single MMA per K step therefore
+      // fills all three accumulators (columns [pl * n_mma, (pl + 1) * n_mma) of plane pl).
+      const uint32_t idesc = umma_idesc_e4m3_m128((uint32_t)(kFp8Planes * n_mma));
+      bool ok = true;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % num_stages;
+        if (!mbar_wait_bounded(smem_u32(&s_full[s]), (uint32_t)(i / num_stages) & 1u,
+                               abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (i == 0 && p.trace && blockIdx.x == 0)
+          p.trace[2 * (kGateUp ? kTraceGateUpFirstData : kTraceDownFirstData)] = global_timer_ns();
+        const uint32_t a_addr = smem_base + (uint32_t)s * stage_bytes;
+        const uint64_t a0 = umma_smem_desc_sw128(a_addr);
+        const uint64_t b0 = umma_smem_desc_sw128(a_addr + kQABytes);
+#pragma unroll
+        for (int k = 0; k < kQStageK / 32; ++k) {
+          // 32 one-byte elements along K = 32 bytes = 2 descriptor units
+          umma_f8(tmem, a0 + 2u * k, b0 + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_empty[s]));
+      }
+      if (ok && num_kb > 0) umma_commit(smem_u32(&s_acc));
+    }
+  } else {
+    // ===== epilogue: TMEM -> registers -> scales -> global =====
+    const int quarter = warp & 3;
+    const int trow = quarter * 32 + lane;  // accumulator lane = weight row of the tile
+    bool have_acc = true;
+    if (num_kb > 0) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
+    // all four epilogue warps must agree (they meet at a named barrier below)
+    {
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 p, %1, 0;\n\t"
+          "barrier.red.and.pred q, 1, 128, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(all_ok)
+          : "r"((uint32_t)have_acc)
+          : "memory");
+      have_acc = all_ok != 0;
+    }
+    if (have_acc) {
+      tc_fence_after_sync();
+      const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+      // sum of the three plane accumulators for 16 columns starting at c0, times the
+      // token rows' scales
+      auto load_columns = [&](int c0, float (&out)[16]) {
+        if (num_kb > 0) {
+          uint32_t a0[16], a1[16], a2[16];
+          tmem_ld_16(lane_base + (uint32_t)c0, a0);
+          tmem_ld_16(lane_base + (uint32_t)(n_mma + c0), a1);
+          tmem_ld_16(lane_base + (uint32_t)(2 * n_mma + c0), a2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float(a0[j]) + __uint_as_float(a1[j]) * 0.0625f +
+                            __uint_as_float(a2[j]) * 0.00390625f;
+            const float ts = (c0 + j < n_rows) ? p.token_scale[row_start + c0 + j] : 0.0f;
+            out[j] = v * ts;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) out[j] = 0.0f;
+        }
+      };
+      if (kGateUp) {
+        // lanes 0..63: gate rows, lanes 64..127: the matching up rows.  The up half goes
+        // through shared memory (the stage ring is idle now) as xchg[column][row], FP32.
+        const int idx = trow & 63;
+        const int m = tile * 64 + idx;
+        const bool m_ok = m < p.m_total;
+        const bool is_up = trow >= 64;
+        float scale = 0.0f;
+        if (m_ok)
+          scale = p.row_scale[(size_t)expert * 2 * p.m_total + (is_up ? p.m_total : 0) + m];
+        float* xchg = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+        float v[16];
+        if (is_up) {
+          for (int c0 = 0; c0 < n_mma; c0 += 16) {
+            load_columns(c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) xchg[(c0 + j) * 64 + idx] = v[j] * scale;
+          }
+        }
+        asm volatile("barrier.sync 1, 128;" ::: "memory");
+        if (!is_up) {
+          for (int c0 = 0; c0 < n_mma; c0 += 16) {
+            load_columns(c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float mag = 0.0f;
+              if (m_ok && c0 + j < n_rows) {
+                const float gate = v[j] * scale;
+                const float up = xchg[(c0 + j) * 64 + idx];
+                const float act = gate / (1.0f + __expf(-gate)) * up;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(act);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
+                const size_t o = (size_t)(row_start + c0 + j) * p.m_total + m;
+                p.act_hi[o] = hi;
+                p.act_lo[o] = lo;
+                // what the next kernel reads back is hi + lo
+                mag = fabsf(__bfloat162float(hi) + __bfloat162float(lo));
+              }
+              // non-negative floats order like their bit patterns
+              const uint32_t warp_max = __reduce_max_sync(0xffffffffu, __float_as_uint(mag));
+              if (lane == 0 && c0 + j < n_rows && warp_max != 0u)
+                atomicMax(p.act_amax + row_start + c0 + j, warp_max);
+            }
+          }
+        }
+      } else {
+        const int m = tile * kQTileM + trow;
+        const bool m_ok = m < p.m_total;
+        const float scale = m_ok ? p.row_scale[(size_t)expert * p.m_total + m] : 0.0f;
+        float* dst = p.partials + (size_t)split * p.rows_cap * p.m_total;
+        float v[16];
+        for (int c0 = 0; c0 < n_mma; c0 += 16) {
+          load_columns(c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (m_ok && c0 + j < n_rows)
+              dst[(size_t)(row_start + c0 + j) * p.m_total + m] = v[j] * scale;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < kQAbortDrainNs) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
+  trace_end(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem, tmem_cols);
+  }
+}
+
+constexpr uint32_t kQStageBudget = 111u * 1024u;  // five 22 KB stages at 16 rows; two blocks per SM
+
+template <bool kGateUp>
+static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b,
+                              const QGemmParams& params, int grid, bool pdl,
+                              cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    err = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kGateUp>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)(kQStageBudget + 1024u));
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kQThreads);
+  cfg.dynamicSmemBytes = kQStageBudget + 1024u;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_fp8_kernel<kGateUp>, map_w, map_b, params);
+}
+
+static QGemmParams fp8_params(const int32_t* sched, uint32_t* status, const float* row_scale,
+                              const float* token_scale, int m_total, int k_total, int m_tiles,
+                              int rows_cap) {
+  QGemmParams p = {};
+  p.sched = sched;
+  p.status = status;
+  p.row_scale = row_scale;
+  p.token_scale = token_scale;
+  p.m_total = m_total;
+  p.k_total = k_total;
+  p.m_tiles = m_tiles;
+  p.rows_cap = rows_cap;
+  p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
+                                                  kTraceOffsetBytes);
+  p.stage_budget = kQStageBudget;
+  return p;
+}
+
+cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
+                               const int32_t* sched, uint32_t* status, void* act_hi,
+                               void* act_lo, uint32_t* act_amax, const float* row_scale,
+                               const float* token_scale, int inter, int hidden, int rows_cap,
+                               int grid, bool pdl, cudaStream_t stream) {
+  QGemmParams p = fp8_params(sched, status, row_scale, token_scale, inter, hidden,
+                             (inter + 63) / 64, rows_cap);
+  p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
+  p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
+  p.act_amax = act_amax;
+  return launch_fp8<true>(map_w, map_x, p, grid, pdl, stream);
+}
+
+cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
+                            const int32_t* sched, uint32_t* status, float* partials,
+                            const float* row_scale, const float* token_scale, int hidden,
+                            int inter, int rows_cap, int grid, bool pdl, cudaStream_t stream) {
+  QGemmParams p = fp8_params(sched, status, row_scale, token_scale, hidden, inter,
+                             (hidden + 127) / 128, rows_cap);
+  p.partials = partials;
+  return launch_fp8<false>(map_w, map_act, p, grid, pdl, stream);
+}
+
+}  // namespace b200moe

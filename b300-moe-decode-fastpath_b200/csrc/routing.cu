@@ -55,7 +55,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
                int64_t* __restrict__ perm_tokens, int64_t* __restrict__ perm_experts,
                __nv_bfloat16* __restrict__ perm_weights, int32_t* __restrict__ sched,
                uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas,
-               int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace,
+               int seg_rows, int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace,
                const uint32_t* __restrict__ wait_flags, int wait_world, uint32_t wait_epoch,
                unsigned long long wait_limit_ns) {
   __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
@@ -130,7 +130,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   const int my_cnt = is_expert ? s_cnt[tid] : 0;
   int n_valid;
   const int my_off = block_exclusive_scan(my_cnt, s_tmp, n_valid);
-  const int my_chunks = (my_cnt + kSegRows - 1) / kSegRows;
+  const int my_chunks = (my_cnt + seg_rows - 1) / seg_rows;
   int n_seg;
   const int my_seg = block_exclusive_scan(my_chunks, s_tmp, n_seg);
   const int n_active = __syncthreads_count(my_cnt > 0);
@@ -142,10 +142,10 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     s_cursor[tid] = my_off;
     for (int c = 0; c < my_chunks; ++c) {
       int32_t* seg = sched + kSchedHeaderWords + kSchedSegWords * (my_seg + c);
-      const int done = c * kSegRows;
+      const int done = c * seg_rows;
       seg[0] = tid;
       seg[1] = my_off + done;
-      seg[2] = min(kSegRows, my_cnt - done);
+      seg[2] = min(seg_rows, my_cnt - done);
       seg[3] = 0;
     }
   }
@@ -166,7 +166,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     sched[kSchedNumActive] = n_active;
     sched[kSchedNumValidRows] = n_valid;
     sched[kSchedDownSplits] = splits;
-    sched[4] = 0;
+    sched[kSchedSegRows] = seg_rows;
     sched[5] = 0;
     sched[6] = 0;
     sched[7] = 0;
@@ -233,7 +233,7 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int64_t* reverse_mapping, int64_t* permutation, int32_t* offsets_i32,
                            int64_t* perm_tokens, int64_t* perm_experts, void* perm_weights,
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
-                           int target_ctas, int id_base, bool foreign_ids_allowed,
+                           int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
                            unsigned long long wait_limit_ns, cudaStream_t stream) {
   // One thread per expert and per assignment of a round, in whole warps; fewer warps make
@@ -245,7 +245,7 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
       ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
       offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
       static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
-      target_ctas, id_base, foreign_ids_allowed ? 1 : 0,
+      target_ctas, seg_rows, id_base, foreign_ids_allowed ? 1 : 0,
       reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) + kTraceOffsetBytes),
       wait_flags, wait_world, wait_epoch, wait_limit_ns);
   return cudaGetLastError();
@@ -314,8 +314,8 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
   return launch_routing(ids, weights, num_assign, top_k, num_experts, counts, offsets,
                         reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
                         perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
-                        reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas, 0,
-                        false, nullptr, 0, 0u, 0ull, stream);
+                        reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas,
+                        kSegRows, 0, false, nullptr, 0, 0u, 0ull, stream);
 }
 
 }  // namespace b200moe

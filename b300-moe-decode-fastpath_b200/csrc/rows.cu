@@ -1,6 +1,8 @@
 // Stage 2 (gather) and stage 5 (combine): the two row-moving kernels either
 // side of the grouped GEMMs.  Both are pure HBM traffic and use 16-byte
 // accesses throughout.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -148,6 +150,143 @@ combine_bf16_rows_kernel(const uint4* __restrict__ expert_rows,
   out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
 }
 
+// ---------------------------------------------------------------------------
+// FP8-weight path: token rows as three E4M3 planes plus a scale per row.
+//
+// r = x / s with s = max|row| / 448 (1 for an all-zero row), then
+//   p0 = e4m3(r), p1 = e4m3((r - p0) * 16), p2 = e4m3(((r - p0) * 16 - p1) * 16),
+// every rounding to nearest-even, saturating; x ~= s * (p0 + p1/16 + p2/256).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float e4m3_to_float(uint32_t code) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+__device__ __forceinline__ void split_e4m3x3(float r, uint32_t& c0, uint32_t& c1, uint32_t& c2) {
+  c0 = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+  const float r1 = (r - e4m3_to_float(c0)) * 16.0f;
+  c1 = __nv_cvt_float_to_fp8(r1, __NV_SATFINITE, __NV_E4M3);
+  const float r2 = (r1 - e4m3_to_float(c1)) * 16.0f;
+  c2 = __nv_cvt_float_to_fp8(r2, __NV_SATFINITE, __NV_E4M3);
+}
+
+// Block-wide maximum of a non-negative float; every thread gets the result.
+__device__ __forceinline__ float block_max(float v, float* tmp) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  if ((threadIdx.x & 31) == 0) tmp[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = 0.0f;
+  for (int i = 0; i < kRowThreads / 32; ++i) m = fmaxf(m, tmp[i]);
+  __syncthreads();
+  return m;
+}
+
+// Eight consecutive values of one row -> eight bytes in each of the three planes.
+__device__ __forceinline__ void store_planes8(const float (&r)[8], uint8_t* plane0,
+                                              size_t plane_stride, size_t offset) {
+  uint32_t lo[3] = {0u, 0u, 0u}, hi[3] = {0u, 0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t c[3];
+    split_e4m3x3(r[i], c[0], c[1], c[2]);
+#pragma unroll
+    for (int pl = 0; pl < 3; ++pl) {
+      if (i < 4) lo[pl] |= c[pl] << (8 * i);
+      else hi[pl] |= c[pl] << (8 * (i - 4));
+    }
+  }
+#pragma unroll
+  for (int pl = 0; pl < 3; ++pl)
+    *reinterpret_cast<uint2*>(plane0 + pl * plane_stride + offset) = make_uint2(lo[pl], hi[pl]);
+}
+
+// Gather for the FP8-weight path: the BF16 row goes to permuted_hidden as in
+// gather_rows_kernel, and its three planes and scale go to scratch.  Also clears the row's
+// activation maximum, which the gate+up kernel accumulates next.
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_fp8_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
+                       uint4* __restrict__ out, uint8_t* __restrict__ planes,
+                       float* __restrict__ row_scale, uint32_t* __restrict__ act_amax,
+                       int num_assign, int num_tokens, int top_k, int hidden_size, int rows_cap,
+                       unsigned long long* __restrict__ trace) {
+  __shared__ float s_tmp[kRowThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  trace_start(trace, kTraceGather);
+  const int row = blockIdx.x;
+  const int vec_per_row = hidden_size / 8;
+  const int64_t a = permutation[row];
+  const bool valid = a >= 0 && a < (int64_t)num_assign && (a / top_k) < (int64_t)num_tokens;
+  const uint4* src = hidden + (valid ? (size_t)(a / top_k) * vec_per_row : 0);
+  uint4* dst = out + (size_t)row * vec_per_row;
+  float amax = 0.0f;
+  for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) x = __ldg(src + v);
+    dst[v] = x;
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  amax = block_max(amax, s_tmp);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) {
+    row_scale[row] = scale;
+    act_amax[row] = 0u;
+  }
+  const size_t plane_stride = (size_t)rows_cap * hidden_size;
+  for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) x = __ldg(src + v);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      r[2 * i] = __fdiv_rn(f.x, scale);
+      r[2 * i + 1] = __fdiv_rn(f.y, scale);
+    }
+    store_planes8(r, planes, plane_stride, (size_t)row * hidden_size + (size_t)v * 8);
+  }
+  trace_end(trace, kTraceGather);
+}
+
+// Between the two FP8 GEMMs: activation rows (hi + lo BF16 halves, maximum already known)
+// -> three planes and a scale per row, into the bytes the gathered rows occupied.  One
+// block per (row, chunk of 8 * kRowThreads columns): the row maximum is known, so chunks
+// are independent.
+__global__ void __launch_bounds__(kRowThreads)
+act_planes_fp8_kernel(const uint4* __restrict__ act_hi, const uint4* __restrict__ act_lo,
+                      const uint32_t* __restrict__ act_amax, uint8_t* __restrict__ planes,
+                      float* __restrict__ row_scale, int inter, int rows_cap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const int vec_per_row = inter / 8;
+  const float amax = __uint_as_float(act_amax[row]);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  if (threadIdx.x == 0 && blockIdx.y == 0) row_scale[row] = scale;
+  const int v = blockIdx.y * kRowThreads + threadIdx.x;
+  if (v >= vec_per_row) return;
+  const size_t plane_stride = (size_t)rows_cap * inter;
+  const uint4 xh = act_hi[(size_t)row * vec_per_row + v];
+  const uint4 xl = act_lo[(size_t)row * vec_per_row + v];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xh);
+  const __nv_bfloat162* l = reinterpret_cast<const __nv_bfloat162*>(&xl);
+  float r[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fh = __bfloat1622float2(h[i]), fl = __bfloat1622float2(l[i]);
+    r[2 * i] = __fdiv_rn(fh.x + fl.x, scale);
+    r[2 * i + 1] = __fdiv_rn(fh.y + fl.y, scale);
+  }
+  store_planes8(r, planes, plane_stride, (size_t)row * inter + (size_t)v * 8);
+}
+
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
                                 const void* weights, void* out, int num_tokens, int top_k,
                                 int hidden_size, cudaStream_t stream) {
@@ -204,6 +343,31 @@ cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
   dim3 grid(num_tokens, (vecs + 127) / 128);
   return launch_with_pdl(reinterpret_cast<const void*>(&combine_rows_kernel), grid, dim3(128),
                          args, pdl, stream);
+}
+
+cudaError_t launch_gather_fp8(const void* hidden, const int64_t* permutation, void* out,
+                              uint8_t* planes, float* row_scale, uint32_t* act_amax,
+                              int num_assign, int num_tokens, int top_k, int hidden_size,
+                              int rows_cap, unsigned long long* trace, bool pdl,
+                              cudaStream_t stream) {
+  const uint4* h = static_cast<const uint4*>(hidden);
+  uint4* o = static_cast<uint4*>(out);
+  void* args[] = {&h, &permutation, &o, &planes, &row_scale, &act_amax, &num_assign, &num_tokens,
+                  &top_k, &hidden_size, &rows_cap, &trace};
+  return launch_with_pdl(reinterpret_cast<const void*>(&gather_rows_fp8_kernel),
+                         dim3(num_assign), dim3(kRowThreads), args, pdl, stream);
+}
+
+cudaError_t launch_act_planes_fp8(const void* act_hi, const void* act_lo,
+                                  const uint32_t* act_amax, uint8_t* planes, float* row_scale,
+                                  int num_assign, int inter, int rows_cap, bool pdl,
+                                  cudaStream_t stream) {
+  const uint4* hi = static_cast<const uint4*>(act_hi);
+  const uint4* lo = static_cast<const uint4*>(act_lo);
+  void* args[] = {&hi, &lo, &act_amax, &planes, &row_scale, &inter, &rows_cap};
+  const int chunks = (inter / 8 + kRowThreads - 1) / kRowThreads;
+  return launch_with_pdl(reinterpret_cast<const void*>(&act_planes_fp8_kernel),
+                         dim3(num_assign, chunks), dim3(kRowThreads), args, pdl, stream);
 }
 
 }  // namespace b200moe

@@ -240,11 +240,17 @@ class ClockSampler:
         }
 
 
+WEIGHT_ELEMENT_BYTES = 2  # 1 with --weights fp8
+
+
 def weight_bytes(active_experts: int) -> dict[str, int]:
     """Algorithmic expert-weight bytes one forward must stream from HBM."""
 
-    gate_up = active_experts * 4 * HIDDEN * INTER   # [2I,H] bf16 per active expert
-    down = active_experts * 2 * HIDDEN * INTER      # [H,I] bf16 per active expert
+    gate_up = active_experts * 2 * HIDDEN * INTER * WEIGHT_ELEMENT_BYTES  # [2I,H] per expert
+    down = active_experts * HIDDEN * INTER * WEIGHT_ELEMENT_BYTES         # [H,I] per expert
+    if WEIGHT_ELEMENT_BYTES == 1:  # + one FP32 scale per weight row
+        gate_up += active_experts * 2 * INTER * 4
+        down += active_experts * HIDDEN * 4
     return {"gate_up": gate_up, "down": down, "total": gate_up + down}
 
 
@@ -441,6 +447,15 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     gate_up, down = workloads.make_expert_weights(
         EXPERTS, HIDDEN, INTER, seed=1236, std=0.02, device=device
     )
+    fp8 = None
+    if args.weights == "fp8":
+        # quantised once, outside every timed region (weights are prepared at load time)
+        from b200moe import b300_moe_forward_fp8, quantize_expert_weights_fp8
+
+        global WEIGHT_ELEMENT_BYTES
+        WEIGHT_ELEMENT_BYTES = 1
+        fp8 = quantize_expert_weights_fp8(gate_up, down)
+        torch.cuda.synchronize(device)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=device)
 
@@ -467,21 +482,28 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "host_out": torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory(),
         }
 
+    def layer_call(inputs, workspace) -> torch.Tensor:
+        if fp8 is not None:
+            return b300_moe_forward_fp8(*inputs, fp8, num_experts=EXPERTS, top_k=TOP_K,
+                                        workspace=workspace)
+        return b300_moe_forward(*inputs, gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                                backend="cutlass_bf16", workspace=workspace)
+
     def forward(T: int) -> torch.Tensor:
         c = cases[T]
-        return b300_moe_forward(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                                backend="cutlass_bf16", workspace=c["workspace"])
+        return layer_call(c["dev"], c["workspace"])
 
     def forward_e2e(T: int) -> torch.Tensor:
         c = cases[T]
         for dst, src in zip(c["stage_in"], c["host"]):
             dst.copy_(src, non_blocking=True)
-        out = b300_moe_forward(*c["stage_in"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                               backend="cutlass_bf16", workspace=c["workspace"])
+        out = layer_call(c["stage_in"], c["workspace"])
         c["host_out"].copy_(out, non_blocking=True)
         return out
 
     def forward_pinned(T: int) -> torch.Tensor:
+        if fp8 is not None:  # the pinned-host entry point exists for BF16 weights only
+            return forward_e2e(T)
         # same end-to-end work without staging copies: the kernels read the pinned host
         # inputs and write the pinned host output themselves
         c = cases[T]
@@ -566,7 +588,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     for T in sweep:
         c = cases[T]
         layer = StagedLayer(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                            workspace=c["workspace"], use_pdl=False)
+                            workspace=c["workspace"], use_pdl=False, fp8_weights=fp8)
         layer.forward()
         stage_us: dict[str, dict[str, float]] = {}
         for name in STAGE_NAMES:
@@ -606,7 +628,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "gate_up_gbs": round(wb["gate_up"] / stage_us["gate_up_swiglu"]["p50"] / 1e3, 1),
             "down_gbs": round(wb["down"] / stage_us["down"]["p50"] / 1e3, 1),
         }
-        if args.library_gemm_baseline:
+        if args.library_gemm_baseline and fp8 is None:
             per_t[str(T)]["library_gemm_us"] = library_gemm_baseline(
                 c, gate_up, down, flush_l2, stage_reps)
 
@@ -619,10 +641,13 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     t1 = per_t[str(sweep[0])]
     gu_bytes = weight_bytes(t1["active_experts"])["gate_up"] + 2 * t1["active_experts"] * (
         HIDDEN * 2 + 2 * INTER * 2)  # + token rows in, hi/lo activations out (tiny)
+    kernel_name = ("grouped_gemm_fp8_kernel<gate_up> (tcgen05 kind::f8f6f4, SwiGLU epilogue)"
+                   if fp8 is not None else
+                   "grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue)")
     gu_us = [t1["stages_us"]["gate_up"]["p50"]]
     achieved = gu_bytes / gu_us[0] / 1e3
     roofline = {
-        "kernel": f"grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue), T={sweep[0]}",
+        "kernel": f"{kernel_name}, T={sweep[0]}",
         "bound": "hbm",
         "achieved": round(achieved, 1),
         "peak": peak,
@@ -630,14 +655,14 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "unit": "GB/s",
         "frac": round(achieved / peak, 3),
         "algorithmic_bytes": gu_bytes,
-        "traffic": GATE_UP_T1_DRAM_TRAFFIC_BYTES,
+        "traffic": GATE_UP_T1_DRAM_TRAFFIC_BYTES if fp8 is None else None,
         "frac_of_8000": round(achieved / 8000.0, 3),
     }
 
     h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in sweep)
     d2h = sum(cases[T]["host_out"].numel() * 2 for T in sweep)
     result = {
-        "metric": METRIC,
+        "metric": METRIC if fp8 is None else METRIC + "_fp8_weights",
         "value": round(value, 2),
         "unit": "us",
         "n_gpus": 1,
@@ -648,10 +673,10 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "higher_is_better": False,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "bf16",
+        "dtype": "bf16" if fp8 is None else "fp8_e4m3 weights x bf16 activations, fp32 accumulate",
         "data": "synthetic",
         "config": {
-            "workload": WORKLOAD,
+            "workload": WORKLOAD if fp8 is None else WORKLOAD.replace("_bf16_", "_fp8w_"),
             "tokens": list(sweep),
             "l2": "flushed before every timed forward: 256 MiB written, then 256 MiB read to push the dirty lines out; every forward also streams >= 704 MB of weights (> 126 MB L2)",
             "step": "one forward at each T of the sweep",
@@ -671,7 +696,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "what": "b300_moe_forward_pinned: the same host-resident inputs and output, read and "
                     "written by the kernels directly over PCIe (no staging copies)",
         },
-        "gpu_launches": 5 * len(sweep) * args.steps,
+        "gpu_launches": (5 if fp8 is None else 6) * len(sweep) * args.steps,
         "clocks": clocks,
         "roofline": roofline,
         "per_T": per_t,
@@ -1030,6 +1055,9 @@ def main() -> int:
                         help="N > 1: combine over NVLink peer memory (default) or NCCL")
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
+    parser.add_argument("--weights", choices=("bf16", "fp8"), default="bf16",
+                        help="N=1: bf16 (default, the configuration the metric is quoted on) or "
+                             "fp8: E4M3 expert weights through b300_moe_forward_fp8")
     parser.add_argument("--csv", default=None,
                         help="N=1: also write per-stage rows in the reference's CSV schema")
     parser.add_argument("--library-gemm-baseline", action="store_true",
@@ -1037,6 +1065,8 @@ def main() -> int:
                              "(the library GEMMs the reference's compiled path calls)")
     args = parser.parse_args()
     apply_config(args.config)
+    if args.weights == "fp8":
+        args.no_cpu_baseline = True  # the CPU port restates the reference's BF16 layer
     if args.config in ("wide", "deepseek", "deepseek_hotspot"):
         args.no_cpu_baseline = True  # ~21 GiB of weights: the CPU port is not timed on these
     if args.impl == "reference":

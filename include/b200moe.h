@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 3
+#define B200MOE_ABI_VERSION 4
 
 /* host-side contract errors */
 #define B200MOE_E_NULL        (-1)  /* a required pointer is NULL */
@@ -62,6 +62,13 @@ extern "C" {
 /* `output` is FP32 [T,H]: the combine stores the unrounded sums, so that partial outputs
  * of several ranks can be added before the single BF16 rounding. */
 #define B200MOE_FLAG_F32_OUTPUT    0x4u
+/* Expert weights are FP8: gate_up_weight / down_weight point to E4M3 bytes ([E,2I,H] and
+ * [E,H,I], one byte per element, produced by b200moe_fp8_quantize_rows) and gate_up_scale /
+ * down_scale hold one FP32 scale per weight row.  Activations, accumulation and output are
+ * as in the BF16 path.  Needs H and I divisible by 16.  No counterpart in the reference,
+ * which names quantised expert weights as future work (docs/goal_1b_report.md:313-314);
+ * the "cutlass_nvfp4" name keeps failing loudly (b200moe_nvfp4_available() == 0). */
+#define B200MOE_FLAG_FP8_WEIGHTS   0x8u
 
 /* ABI version of the loaded library (== B200MOE_ABI_VERSION it was built with). */
 int b200moe_abi_version(void);
@@ -129,6 +136,9 @@ typedef struct B200MoeArgs {
   int32_t  ep_world;
   uint32_t ep_epoch;
   uint32_t ep_wait_limit_us;
+  /* B200MOE_FLAG_FP8_WEIGHTS only: dequantised weight = E4M3 value * scale of its row */
+  const float* gate_up_scale;        /* [E, 2I] fp32 */
+  const float* down_scale;           /* [E, H]  fp32 */
 } B200MoeArgs;
 
 /*
@@ -221,11 +231,12 @@ int b200moe_combine(const B200MoeArgs* args, void* stream);
  * Stages 1 + 2 on their own: the legacy "dispatch" operation.  Replaces dispatch_cuda
  * (csrc/dispatch_cuda.cu:24-201, bound as fastpath._C.dispatch and used by
  * fastpath/ops.py:150-178): counts, offsets, both mappings and the gathered rows.
- * Needs only the head of a scratch region: 256 bytes + the schedule
- * (4 * (8 + 4 * (min(rows_cap, E) + rows_cap / 128 + 1)) bytes), 256-byte aligned.
+ * Needs only the head of a scratch region (status words + schedule), 256-byte aligned;
+ * b200moe_dispatch_scratch_bytes gives its size for rows_cap rows and E experts.
  * intermediate_size, swiglu_output, the weights and output are not read.
  */
 int b200moe_dispatch(const B200MoeArgs* args, void* stream);
+int b200moe_dispatch_scratch_bytes(int rows_cap, int num_experts, size_t* bytes);
 
 /*
  * The legacy "combine" operation on BF16 expert rows.  Replaces combine_cuda
@@ -323,6 +334,20 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status);
 int b200moe_nvfp4_available(void);
 
 /*
+ * FP8 (E4M3) weight preparation, run once when the model is loaded.  No counterpart in the
+ * reference.  Row r of a [rows, cols] BF16 matrix (rows = E*2I or E*H, cols = H or I) gets
+ * scale[r] = max|w[r,:]| / 448 (1 when the row is all zero) and
+ * q[r,c] = E4M3(round-to-nearest-even, saturating)(float(w[r,c]) / scale[r]).
+ * b200moe_fp8_dequantize_rows writes bf16(E4M3 value * scale[r]) (scale == NULL: the bare
+ * E4M3 values, which BF16 holds exactly) using the conversion the GEMM kernels use.
+ * cols must be a multiple of 16; pointers 16-byte aligned.
+ */
+int b200moe_fp8_quantize_rows(const void* weights_bf16, long long rows, int cols,
+                              uint8_t* q_out, float* scale_out, void* stream);
+int b200moe_fp8_dequantize_rows(const uint8_t* q, const float* scale, long long rows, int cols,
+                                void* out_bf16, void* stream);
+
+/*
  * Router front end (the step in front of the layer).  Replaces the two PyTorch
  * calls of topk_routing (baseline/routing.py:48-55), which the reference's
  * benchmark counts in routing_us and total_us (benchmark/benchmark_goal_1b.py:464,
@@ -355,6 +380,9 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              with <= 32 rows also fetch their token rows themselves
  *   B200MOE_TUNE_DOWN_SPLITS   force the split-K factor of the down projection (1..8;
  *                              0 = chosen on the device from the routing result)
+ *   B200MOE_TUNE_FP8_SEG_ROWS  longest segment of the FP8-weight path: 16, 32, 48 or 64 rows
+ *                              (default 64; shorter segments leave more shared memory to
+ *                              the weight stream and re-read weights of longer experts)
  *   B200MOE_TUNE_DOWN_TARGET   number of blocks the split-K of the down projection aims
  *                              at when few (segment, tile) units exist (0 = default)
  */
@@ -364,6 +392,7 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
 #define B200MOE_TUNE_EARLY_START  4
 #define B200MOE_TUNE_DOWN_TARGET  5
 #define B200MOE_TUNE_DOWN_SPLITS  6
+#define B200MOE_TUNE_FP8_SEG_ROWS 7
 int b200moe_tune(int knob, int value);
 
 #ifdef __cplusplus
