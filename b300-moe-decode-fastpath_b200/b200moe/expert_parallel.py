@@ -72,7 +72,12 @@ class ExpertParallelMoE:
         capacity_tokens: int = 64,
         use_pdl: bool = True,
         transport: str = "nccl",
+        fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
     ) -> None:
+        """``fp8_scales = (gate_up_scale [E_local, 2I], down_scale [E_local, H])`` marks the two
+        weight tensors as E4M3 codes (uint8) of the FP8-weight path (``b200moe.fp8``)."""
+
+        self.fp8_scales = fp8_scales
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -236,6 +241,7 @@ class ExpertParallelMoE:
             hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
             expert_id_base=self.base, num_experts_global=self.num_experts,
             workspace=self.workspace, use_pdl=self.use_pdl, out=out, ep_wait=ep_wait,
+            fp8_scales=self.fp8_scales,
         )
         self._last_call = call
         return partial
@@ -258,9 +264,21 @@ class ExpertParallelMoE:
             raise RuntimeError("expert-parallel native compute requires compute capability (10, 0)")
         if ids.dtype != torch.int64:
             raise TypeError("expert_indices must have dtype torch.int64")
-        for t in (hidden, weights, self.gate_up, self.down):
-            if t.dtype != torch.bfloat16:
-                raise TypeError("b200_bf16 requires bfloat16 inputs and weights")
+        weight_dtype = torch.uint8 if self.fp8_scales is not None else torch.bfloat16
+        for t, want in ((hidden, torch.bfloat16), (weights, torch.bfloat16),
+                        (self.gate_up, weight_dtype), (self.down, weight_dtype)):
+            if t.dtype != want:
+                raise TypeError("native expert-parallel compute requires bfloat16 inputs and "
+                                "bfloat16 (or, with fp8_scales, uint8 E4M3) weights")
+        if self.fp8_scales is not None:
+            gs, ds = self.fp8_scales
+            inter_ = self.gate_up.shape[1] // 2
+            if tuple(gs.shape) != (self.local_experts, 2 * inter_) or \
+                    tuple(ds.shape) != (self.local_experts, self.hidden_size) or \
+                    gs.dtype != torch.float32 or ds.dtype != torch.float32:
+                raise ValueError("fp8_scales must be float32 [E_local, 2I] and [E_local, H]")
+            if self.hidden_size % 16 or inter_ % 16:
+                raise ValueError("the FP8-weight path requires H and I divisible by 16")
         for t in (hidden, ids, weights, self.gate_up, self.down):
             if not t.is_contiguous():
                 raise ValueError("all inputs must be contiguous")
@@ -367,6 +385,7 @@ def local_partial_forward(
     use_pdl: bool = True,
     out: torch.Tensor | None = None,
     ep_wait: tuple[int, int, int] | None = None,
+    fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -397,8 +416,13 @@ def local_partial_forward(
         flags = _lib.FLAG_LOCAL_EXPERTS | _lib.FLAG_F32_OUTPUT
         if use_pdl:
             flags |= _lib.FLAG_PDL
+        if fp8_scales is not None:
+            flags |= _lib.FLAG_FP8_WEIGHTS
         args = _native_args(hidden, ids, weights, gate_up_local, down_local, shape, workspace,
                             partial, flags, expert_id_base=expert_id_base)
+        if fp8_scales is not None:
+            args.gate_up_scale = fp8_scales[0].data_ptr()
+            args.down_scale = fp8_scales[1].data_ptr()
         if ep_wait is not None:
             # (device address of this rank's dispatch flags, world size, epoch): the routing
             # kernel waits for every rank's pushed shard before it reads ids or rows

@@ -238,6 +238,26 @@ int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts
   return 0;
 }
 
+// Grid of the down projection.  The routing kernel picks the split-K factor from the number
+// of segments it finds, so the grid is sized for the worst case over every possible segment
+// count.  Remembered per thread: a decode loop asks for the same geometry every step.
+int down_grid(int bound, int tiles, int kblocks, int sm_count) {
+  if (g_down_splits > 0) return bound * tiles * g_down_splits;
+  struct Memo { int bound, tiles, kblocks, target, grid; };
+  static thread_local Memo memo = {0, 0, 0, 0, 0};
+  const int target = down_target(sm_count);
+  if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
+      memo.target != target) {
+    int worst = bound * tiles;
+    for (int segs = 1; segs <= bound; ++segs) {
+      const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
+      if (n > worst) worst = n;
+    }
+    memo = {bound, tiles, kblocks, target, worst};
+  }
+  return memo.grid;
+}
+
 int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                cudaStream_t stream) {
   const bool local = (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0;
@@ -307,30 +327,8 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   if (rc) return rc;
   rc = encode_bf16_map(&map_lo, s.act_lo, 2, dims, box);
   if (rc) return rc;
-  // Without split-K there are at most bound*tiles units.
-  int grid = segment_bound(assignments, experts) * tiles128(hidden);
-  // The routing kernel picks the split factor from the number of segments it finds; size
-  // the grid for the worst case over every possible segment count.
-  const int tiles = tiles128(hidden), kblocks = (inter + 63) / 64;
-  if (g_down_splits > 0) {
-    grid *= g_down_splits;
-  } else {
-    // remembered per thread: a decode loop asks for the same geometry every step
-    struct Memo { int bound, tiles, kblocks, target, grid; };
-    static thread_local Memo memo = {0, 0, 0, 0, 0};
-    const int bound = segment_bound(assignments, experts);
-    const int target = down_target(dev.sm_count);
-    if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
-        memo.target != target) {
-      int worst = grid;
-      for (int segs = 1; segs <= bound; ++segs) {
-        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
-        if (n > worst) worst = n;
-      }
-      memo = {bound, tiles, kblocks, target, worst};
-    }
-    grid = memo.grid;
-  }
+  const int grid = down_grid(segment_bound(assignments, experts), tiles128(hidden),
+                             (inter + 63) / 64, dev.sm_count);
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
                           rows_cap, grid, pdl, stream);
 }
@@ -372,26 +370,8 @@ int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int r
   }
   int rc = encode_plane_map(&map_act, s.q_planes, inter, rows_cap);
   if (rc) return rc;
-  const int bound = segment_bound(assignments, experts, g_fp8_seg_rows);
-  const int tiles = tiles128(hidden), kblocks = (inter + 127) / 128;
-  int grid = bound * tiles;
-  if (g_down_splits > 0) {
-    grid *= g_down_splits;
-  } else {
-    struct Memo { int bound, tiles, kblocks, target, grid; };
-    static thread_local Memo memo = {0, 0, 0, 0, 0};
-    const int target = down_target(dev.sm_count);
-    if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
-        memo.target != target) {
-      int worst = grid;
-      for (int segs = 1; segs <= bound; ++segs) {
-        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
-        if (n > worst) worst = n;
-      }
-      memo = {bound, tiles, kblocks, target, worst};
-    }
-    grid = memo.grid;
-  }
+  const int grid = down_grid(segment_bound(assignments, experts, g_fp8_seg_rows),
+                             tiles128(hidden), (inter + 127) / 128, dev.sm_count);
   // the activation rows become planes (in the bytes the gathered rows occupied), then the GEMM
   rc = (int)launch_act_planes_fp8(act_hi, s.act_lo, s.a_amax, s.q_planes, s.a_scale, assignments,
                                   inter, rows_cap, pdl, stream);

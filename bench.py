@@ -725,14 +725,26 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     base, count = expert_range(rank, world, EXPERTS)
     gate_up, down = workloads.make_expert_weights(count, HIDDEN, INTER, seed=1236 + rank,
                                                   std=0.02, device=device)
+    fp8_scales = None
+    if args.weights == "fp8":
+        # each rank quantises its own experts once, outside every timed region
+        from b200moe import quantize_expert_weights_fp8
+
+        global WEIGHT_ELEMENT_BYTES
+        WEIGHT_ELEMENT_BYTES = 1
+        fw = quantize_expert_weights_fp8(gate_up, down)
+        gate_up, down, fp8_scales = fw.gate_up_q, fw.down_q, (fw.gate_up_scale, fw.down_scale)
+        torch.cuda.synchronize(device)
     baseline = ExpertParallelMoE(gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                                 capacity_tokens=max(SWEEP), transport="nccl")
+                                 capacity_tokens=max(SWEEP), transport="nccl",
+                                 fp8_scales=fp8_scales)
     transport, transport_note = args.ep_transport, None
     layer = baseline
     if transport == "p2p":
         try:
             layer = ExpertParallelMoE(gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                                      capacity_tokens=max(SWEEP), transport="p2p")
+                                      capacity_tokens=max(SWEEP), transport="p2p",
+                                      fp8_scales=fp8_scales)
         except Exception as error:  # peer mapping unavailable on this box: say so, use NCCL
             transport, transport_note = "nccl", f"p2p setup failed: {type(error).__name__}: {error}"
         agree = torch.tensor([1 if transport == "p2p" else 0], device=device)
@@ -905,7 +917,7 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in SWEEP)
     d2h = sum(cases[T]["host_out"].numel() * 2 for T in SWEEP)
     return {
-        "metric": METRIC,
+        "metric": METRIC if fp8_scales is None else METRIC + "_fp8_weights",
         "value": round(sum(p50s) / len(p50s), 2),
         "unit": "us",
         "n_gpus": world,
@@ -916,10 +928,10 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         "higher_is_better": False,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "bf16",
+        "dtype": "bf16" if fp8_scales is None else "fp8_e4m3 weights x bf16 activations, fp32 accumulate",
         "data": "synthetic",
         "config": {
-            "workload": WORKLOAD,
+            "workload": WORKLOAD if fp8_scales is None else WORKLOAD.replace("_bf16_", "_fp8w_"),
             "tokens": list(SWEEP),
             "parallelism": f"expert-parallel ep{world}: {EXPERTS // world} experts per rank, "
                            "tokens replicated, FP32 partial outputs combined by "
@@ -934,7 +946,8 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "what": "ExpertParallelMoE.forward with pinned host activations/routes copied in "
                         "and the output copied out inside the timed region, per rank"},
-        "gpu_launches": (6 if transport == "p2p" else 5) * len(SWEEP) * args.steps * world,
+        "gpu_launches": ((6 if transport == "p2p" else 5) + (1 if fp8_scales is not None else 0))
+                        * len(SWEEP) * args.steps * world,
         "clocks": clocks,
         "roofline": {
             "kernel": f"grouped_gemm_kernel<gate_up> on the busiest rank, T={T_big}",
@@ -1056,8 +1069,8 @@ def main() -> int:
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
     parser.add_argument("--weights", choices=("bf16", "fp8"), default="bf16",
-                        help="N=1: bf16 (default, the configuration the metric is quoted on) or "
-                             "fp8: E4M3 expert weights through b300_moe_forward_fp8")
+                        help="bf16 (default, the configuration the metric is quoted on) or "
+                             "fp8: E4M3 expert weights (b300_moe_forward_fp8 / fp8_scales)")
     parser.add_argument("--csv", default=None,
                         help="N=1: also write per-stage rows in the reference's CSV schema")
     parser.add_argument("--library-gemm-baseline", action="store_true",

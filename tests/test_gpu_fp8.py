@@ -221,3 +221,31 @@ def test_mixtral_shaped_decode_step(cuda_device) -> None:
                                    check_status=True)
         ref, _ = _reference(fw, hidden, ids, weights, E, K)
         _check(out, ref, f"fp8 mixtral-shaped T={T}")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_shares_with_fp8_weights(world, cuda_device) -> None:
+    """Each rank's share of an expert-parallel forward with FP8 weights, run one after another
+    on one GPU: the FP32 partial outputs add up to the FP8 layer."""
+
+    from b200moe import B300MoEWorkspace, quantize_expert_weights_fp8
+    from b200moe.expert_parallel import expert_range, local_partial_forward
+
+    E, H, I, K, T = 8, 256, 384, 2, 16
+    gate_up, down, hidden, ids, weights = _case(E, H, I, K, T, "zipf", seed=7)
+    fw = quantize_expert_weights_fp8(gate_up.to(cuda_device), down.to(cuda_device))
+    dev = (hidden.to(cuda_device), ids.to(cuda_device), weights.to(cuda_device))
+    total = torch.zeros(T, H, dtype=torch.float32, device=cuda_device)
+    for rank in range(world):
+        base, count = expert_range(rank, world, E)
+        ws = B300MoEWorkspace(device=cuda_device)
+        partial, _ = local_partial_forward(
+            *dev, fw.gate_up_q[base:base + count].contiguous(),
+            fw.down_q[base:base + count].contiguous(), top_k=K, expert_id_base=base,
+            num_experts_global=E, workspace=ws,
+            fp8_scales=(fw.gate_up_scale[base:base + count].contiguous(),
+                        fw.down_scale[base:base + count].contiguous()))
+        total += partial
+        assert ws.status() == 0
+    ref, _ = _reference(fw, hidden, ids, weights, E, K)
+    _check(total.to(torch.bfloat16), ref, f"fp8 expert-parallel shares, world {world}")
