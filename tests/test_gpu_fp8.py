@@ -249,3 +249,48 @@ def test_expert_parallel_shares_with_fp8_weights(world, cuda_device) -> None:
         assert ws.status() == 0
     ref, _ = _reference(fw, hidden, ids, weights, E, K)
     _check(total.to(torch.bfloat16), ref, f"fp8 expert-parallel shares, world {world}")
+
+
+def test_full_size_deepseek_shaped_layer_spot_checked(cuda_device) -> None:
+    """E=256, K=8, H=7168, I=2048, T=64 with hot experts, all weights FP8 (10.5 GiB).  Three
+    tokens are checked against the token/slot loop oracle on the dequantised weights of the
+    experts they route to; routing tensors of the whole call bit-exact; two runs identical;
+    and the output is exactly linear in a power-of-two scale of the routing weights."""
+
+    from b200moe import B300MoEWorkspace, b300_moe_forward_fp8, quantize_expert_weights_fp8, workloads
+
+    T, H, I, E, K = 64, 7168, 2048, 256, 8
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing="hotspot", weight_kind="softmax", device=cuda_device)
+    fw = quantize_expert_weights_fp8(gate_up, down)
+    del gate_up, down
+    ws = B300MoEWorkspace(capacity_tokens=T, device=cuda_device)
+    out, meta = b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K,
+                                     workspace=ws, return_metadata=True, check_status=True)
+    again = b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K, workspace=ws)
+    assert torch.equal(out, again)
+    doubled = b300_moe_forward_fp8(hidden, ids, weights * 2, fw, num_experts=E, top_k=K,
+                                   workspace=ws)
+    assert torch.equal(doubled.float(), out.float() * 2)
+    want = moe_oracle.group_tokens(ids.cpu(), E)
+    for key in ("permutation", "reverse_mapping", "expert_counts", "expert_offsets"):
+        np.testing.assert_array_equal(meta[key].cpu().numpy(), getattr(want, key), err_msg=key)
+
+    tokens = [0, T // 2, T - 1]
+    picked = ids[tokens].cpu()
+    experts = sorted(set(picked.reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(experts)}
+    small_ids = torch.tensor([[remap[int(e)] for e in row] for row in picked])
+    index = torch.tensor(experts, device=cuda_device)
+    gate_up_ref = fp8_oracle.dequantize_rows(
+        fw.gate_up_q.index_select(0, index).cpu().numpy(),
+        fw.gate_up_scale.index_select(0, index).cpu().numpy())
+    down_ref = fp8_oracle.dequantize_rows(
+        fw.down_q.index_select(0, index).cpu().numpy(),
+        fw.down_scale.index_select(0, index).cpu().numpy())
+    ref = moe_oracle.routed_moe_naive(hidden[tokens].cpu(), small_ids, weights[tokens].cpu(),
+                                      gate_up_ref, down_ref)
+    got = out[tokens].float().cpu()
+    err = float((got - ref).abs().max()) / moe_oracle.rms(ref)
+    print(f"fp8 deepseek-shaped full size: err/rms={err:.5f} floor={moe_oracle.bf16_floor(ref):.5f}")
+    assert err <= TOLERANCE
