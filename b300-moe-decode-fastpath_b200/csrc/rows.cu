@@ -263,8 +263,11 @@ __global__ void __launch_bounds__(kRowThreads)
 act_planes_fp8_kernel(const uint4* __restrict__ act_hi, const uint4* __restrict__ act_lo,
                       const uint32_t* __restrict__ act_amax, uint8_t* __restrict__ planes,
                       float* __restrict__ row_scale, int inter, int rows_cap) {
-  pdl_wait();
+  // Let the down grid become resident and prefetch its weight tiles now; it waits for this
+  // grid's completion before it touches the planes, and the schedule it reads first has
+  // been final since the routing kernel completed, several grids ago.
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int vec_per_row = inter / 8;
   const float amax = __uint_as_float(act_amax[row]);
