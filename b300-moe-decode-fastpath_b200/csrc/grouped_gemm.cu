@@ -28,8 +28,9 @@
 // part plus a BF16 low-order remainder.
 //
 // down (stage 4): each stage holds one 128-row weight tile and the high and low
-// activation rows; two MMAs per K step accumulate W . hi + W . lo into one
-// accumulator.  The epilogue stores FP32 rows into this block's split-K slice.
+// activation rows, one after the other; one MMA per K step over both computes
+// W . hi and W . lo into two accumulators.  The epilogue adds them and stores FP32
+// rows into this block's split-K slice.
 #include "common.cuh"
 
 namespace b200moe {
@@ -263,7 +264,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   // ---- tensor memory ------------------------------------------------------------
-  const uint32_t cols_needed = (uint32_t)n_mma * (kGateUp ? 2u : 1u);
+  const uint32_t cols_needed = (uint32_t)n_mma * 2u;  // gate and up, or high and low halves
   uint32_t tmem_cols = 32;
   while (tmem_cols < cols_needed) tmem_cols <<= 1;
   if (warp == 1) {
@@ -300,6 +301,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     // ===== MMA issuer =====
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16_m128((uint32_t)n_mma);
+      const uint32_t idesc_down = umma_idesc_bf16_m128((uint32_t)(2 * n_mma));
       bool ok = true;
       for (int i = 0; i < num_kb; ++i) {
         const int s = i % num_stages;
@@ -325,12 +327,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
             umma_bf16(tmem + (uint32_t)n_mma, a1 + 2u * k, b0 + 2u * k, idesc, acc);
           }
         } else {
-          const uint64_t b1 = umma_smem_desc_sw128(b_addr + (uint32_t)n_mma * 128u);  // low halves
+          // The low halves follow the high halves in the stage: one K-major operand of
+          // 2 * n_mma rows, so a single MMA per K step fills both accumulators (columns
+          // [0, n_mma) from the high halves, [n_mma, 2 n_mma) from the low ones).
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k) {
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-            umma_bf16(tmem, a0 + 2u * k, b0 + 2u * k, idesc, acc);
-            umma_bf16(tmem, a0 + 2u * k, b1 + 2u * k, idesc, 1u);
+            umma_bf16(tmem, a0 + 2u * k, b0 + 2u * k, idesc_down, acc);
           }
         }
         umma_commit(smem_u32(&s_empty[s]));  // frees the stage once these MMAs have read it
@@ -358,7 +361,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         uint32_t g[16], u[16];
         if (num_kb > 0) {
           tmem_ld_16(lane_base + (uint32_t)c0, g);
-          if (kGateUp) tmem_ld_16(lane_base + (uint32_t)(n_mma + c0), u);
+          tmem_ld_16(lane_base + (uint32_t)(n_mma + c0), u);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -383,7 +386,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (m_ok && c0 + j < n_rows)
-              dst[(size_t)(row_start + c0 + j) * p.m_total + m] = __uint_as_float(g[j]);
+              dst[(size_t)(row_start + c0 + j) * p.m_total + m] =
+                  __uint_as_float(g[j]) + __uint_as_float(u[j]);  // W.hi + W.lo
           }
         }
       }
