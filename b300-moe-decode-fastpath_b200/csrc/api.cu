@@ -334,8 +334,9 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
 }
 
 // FP8 weights: one-byte tensor maps of the weights and of the token planes.
-int encode_plane_map(CUtensorMap* map, const uint8_t* planes, int cols, int rows_cap) {
-  const uint64_t dims[3] = {(uint64_t)cols, (uint64_t)rows_cap, (uint64_t)kFp8Planes};
+int encode_plane_map(CUtensorMap* map, const uint8_t* planes, int cols, int rows_cap,
+                     int num_planes) {
+  const uint64_t dims[3] = {(uint64_t)cols, (uint64_t)rows_cap, (uint64_t)num_planes};
   const uint32_t box[3] = {128, 16, 1};
   return encode_map(map, planes, 3, dims, box, true);
 }
@@ -346,13 +347,13 @@ int do_gate_up_fp8(const void* w, const float* row_scale, int rows_cap, int assi
   CUtensorMap map_w, map_x;
   {
     const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
-    const uint32_t box[4] = {128, 64, 2, 1};  // 64 gate rows + the 64 matching up rows
+    const uint32_t box[4] = {128, 128, 2, 1};  // 128 gate rows + the 128 matching up rows
     int rc = encode_map(&map_w, w, 4, dims, box, true);
     if (rc) return rc;
   }
-  int rc = encode_plane_map(&map_x, s.q_planes, hidden, rows_cap);
+  int rc = encode_plane_map(&map_x, s.q_planes, hidden, rows_cap, kFp8PlanesHidden);
   if (rc) return rc;
-  const int grid = segment_bound(assignments, experts, g_fp8_seg_rows) * ((inter + 63) / 64);
+  const int grid = segment_bound(assignments, experts, g_fp8_seg_rows) * tiles128(inter);
   return (int)launch_gate_up_fp8(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, s.a_amax,
                                  row_scale, s.x_scale, inter, hidden, rows_cap, grid, pdl,
                                  stream);
@@ -368,7 +369,7 @@ int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int r
     int rc = encode_map(&map_w, w, 3, dims, box, true);
     if (rc) return rc;
   }
-  int rc = encode_plane_map(&map_act, s.q_planes, inter, rows_cap);
+  int rc = encode_plane_map(&map_act, s.q_planes, inter, rows_cap, kFp8Planes);
   if (rc) return rc;
   const int grid = down_grid(segment_bound(assignments, experts, g_fp8_seg_rows),
                              tiles128(hidden), (inter + 127) / 128, dev.sm_count);

@@ -94,7 +94,8 @@ struct ScratchLayout {
   size_t total;
 };
 
-constexpr int kFp8Planes = 3;
+constexpr int kFp8Planes = 3;        // activation rows of the down projection
+constexpr int kFp8PlanesHidden = 2;  // BF16 hidden rows of gate+up: exact with a power-of-two scale
 
 __host__ __device__ inline ScratchLayout scratch_layout(int rows_cap, int experts, int hidden,
                                                         int inter) {

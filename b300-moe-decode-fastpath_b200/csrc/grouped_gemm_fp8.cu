@@ -9,21 +9,25 @@
 // memory costs more than the bytes it saves (measured: slower than the BF16 kernels).
 // So the weights go from TMA straight into the MMA, and the small operand -- the token
 // rows -- is what gets converted, once per row and not once per weight byte: every row r
-// is held as three E4M3 planes and a scale s_r with
-//     x[r, k] ~= s_r * (p0[r,k] + p1[r,k] / 16 + p2[r,k] / 256),
-// twelve significant bits relative to the row maximum (BF16 has eight).  Each plane is
-// multiplied with the weight tile into its own FP32 accumulator in tensor memory; the
-// epilogue adds the three with their weights and applies s_r and the weight row's scale.
+// is held as E4M3 planes and a scale s_r,
+//     x[r, k] ~= s_r * (p0[r,k] + p1[r,k] / 16 [+ p2[r,k] / 256]).
+// The hidden rows of gate+up are BF16 (eight significant bits): with a power-of-two scale
+// two planes hold them exactly.  The activation rows of the down projection carry sixteen
+// bits (high + low BF16 halves): three planes keep twelve relative to the row maximum.
+// The planes of a stage lie one after another in shared memory, i.e. they are one K-major
+// operand of planes x rows rows, so ONE MMA per K step fills one FP32 accumulator per plane
+// in tensor memory; the epilogue adds them with their weights and applies s_r and the
+// weight row's scale.
 //
-// Same structure as the BF16 kernels otherwise: one block = (segment of <= 64 rows,
-// 128-row weight tile[, K split]); warp 0 = TMA producer, warp 1 = TMEM allocation + MMA
-// issue, warps 2..5 = epilogue; two blocks per SM; every wait bounded.
+// Same structure as the BF16 kernels otherwise: one block = (segment of <= 64 rows, weight
+// tile[, K split]); warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue, warps 2..5
+// = epilogue; two blocks per SM; every wait bounded.
 //
-// gate+up: the 128 weight rows of a tile are 64 gate rows and the 64 matching up rows (one
-// 4-D TMA box over [E][2][I][H]), so accumulator lanes 0..63 hold gate and 64..127 hold up;
-// the up half crosses to the gate half's threads through shared memory.  Besides the
-// hi/lo BF16 activations it records each row's max |activation| (atomicMax on the bit
-// pattern), from which the rows are re-quantised into planes for the down projection.
+// gate+up: a stage holds 128 gate rows and the 128 matching up rows (one 4-D TMA box over
+// [E][2][I][H], 32 KB) and two MMAs per K step fill a gate and an up accumulator set, so
+// SwiGLU is thread-local as in the BF16 kernel.  Besides the hi/lo BF16 activations the
+// epilogue records each row's max |activation| (atomicMax on the bit pattern), from which
+// the rows are re-quantised into planes for the down projection.
 #include "common.cuh"
 
 namespace b200moe {
@@ -32,7 +36,7 @@ constexpr int kQThreads = 192;
 constexpr int kQStageK = 128;   // E4M3 elements (= bytes) per pipeline stage along K
 constexpr int kQTileM = 128;
 constexpr int kQMaxStages = 8;
-constexpr uint32_t kQABytes = kQTileM * kQStageK;  // 16 KB of weights per stage
+constexpr uint32_t kQTileBytes = kQTileM * kQStageK;  // one 128-row weight tile of a stage: 16 KB
 constexpr uint64_t kQAbortDrainNs = 1000000ull;
 
 struct QGemmParams {
@@ -46,7 +50,7 @@ struct QGemmParams {
   const float* token_scale;   // planes: [rows_cap]
   int m_total;                // I (gate+up) or H (down)
   int k_total;                // H (gate+up) or I (down)
-  int m_tiles;                // ceil(I / 64) (gate+up) or ceil(H / 128) (down)
+  int m_tiles;                // ceil(I / 128) (gate+up) or ceil(H / 128) (down)
   int rows_cap;
   unsigned long long* trace;
   uint32_t stage_budget;
@@ -105,8 +109,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   // ---- shared-memory pipeline geometry ----------------------------------------------
+  constexpr int kPlanes = kGateUp ? kFp8PlanesHidden : kFp8Planes;
+  constexpr uint32_t kABytes = kGateUp ? 2u * kQTileBytes : kQTileBytes;  // gate + up tiles
   const uint32_t plane_bytes = (uint32_t)n_mma * 128u;
-  const uint32_t stage_bytes = kQABytes + (uint32_t)kFp8Planes * plane_bytes;
+  const uint32_t stage_bytes = kABytes + (uint32_t)kPlanes * plane_bytes;
   const int num_stages = min((int)(p.stage_budget / stage_bytes), kQMaxStages);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   volatile int* abort_flag = &s_abort;
@@ -117,11 +123,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   auto load_weights = [&](uint32_t dst, uint32_t bar, int kc) {
-    if (kGateUp) tma_load_4d(dst, &map_w, bar, kc, tile * 64, 0, expert);
+    if (kGateUp) tma_load_4d(dst, &map_w, bar, kc, tile * kQTileM, 0, expert);
     else tma_load_3d(dst, &map_w, bar, kc, tile * kQTileM, expert);
   };
   auto load_tokens = [&](uint32_t b_dst, uint32_t bar, int kc) {
-    for (int pl = 0; pl < kFp8Planes; ++pl)
+    for (int pl = 0; pl < kPlanes; ++pl)
       for (int r = 0; r < n_mma; r += 16)
         tma_load_3d(b_dst + (uint32_t)pl * plane_bytes + (uint32_t)r * 128u, &map_b, bar, kc,
                     row_start + r, pl);
@@ -140,9 +146,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   pdl_wait();
   pdl_launch_dependents();
 
-  // ---- tensor memory: three accumulators of n_mma columns ---------------------------------
+  // ---- tensor memory: one accumulator of n_mma columns per plane (gate and up: each) -------
+  constexpr int kAccSets = kGateUp ? 2 : 1;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < (uint32_t)(kFp8Planes * n_mma)) tmem_cols <<= 1;
+  while (tmem_cols < (uint32_t)(kAccSets * kPlanes * n_mma)) tmem_cols <<= 1;
   if (warp == 1) {
     tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
     tmem_relinquish();
@@ -168,16 +175,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
           mbar_expect_tx(bar, stage_bytes);
           load_weights(a_dst, bar, kc);
         }
-        load_tokens(a_dst + kQABytes, bar, kc);
+        load_tokens(a_dst + kABytes, bar, kc);
       }
     }
   } else if (warp == 1) {
     // ===== MMA issuer =====
     if (lane == 0) {
-      // The three planes of a stage lie one after another in shared memory, n_mma rows
-      // each: one K-major operand of 3 * n_mma rows.  A single MMA per K step therefore
-      // fills all three accumulators (columns [pl * n_mma, (pl + 1) * n_mma) of plane pl).
-      const uint32_t idesc = umma_idesc_e4m3_m128((uint32_t)(kFp8Planes * n_mma));
+      // The planes of a stage are one K-major operand of kPlanes * n_mma rows: a single MMA
+      // per K step (and weight tile) fills all of a set's accumulators, plane pl in columns
+      // [pl * n_mma, (pl + 1) * n_mma) of the set.
+      const uint32_t idesc = umma_idesc_e4m3_m128((uint32_t)(kPlanes * n_mma));
       bool ok = true;
       for (int i = 0; i < num_kb; ++i) {
         const int s = i % num_stages;
@@ -191,11 +198,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
           p.trace[2 * (kGateUp ? kTraceGateUpFirstData : kTraceDownFirstData)] = global_timer_ns();
         const uint32_t a_addr = smem_base + (uint32_t)s * stage_bytes;
         const uint64_t a0 = umma_smem_desc_sw128(a_addr);
-        const uint64_t b0 = umma_smem_desc_sw128(a_addr + kQABytes);
+        const uint64_t a1 = umma_smem_desc_sw128(a_addr + kQTileBytes);  // up tile (gate+up only)
+        const uint64_t b0 = umma_smem_desc_sw128(a_addr + kABytes);
 #pragma unroll
         for (int k = 0; k < kQStageK / 32; ++k) {
           // 32 one-byte elements along K = 32 bytes = 2 descriptor units
-          umma_f8(tmem, a0 + 2u * k, b0 + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          umma_f8(tmem, a0 + 2u * k, b0 + 2u * k, idesc, acc);
+          if (kGateUp)
+            umma_f8(tmem + (uint32_t)(kPlanes * n_mma), a1 + 2u * k, b0 + 2u * k, idesc, acc);
         }
         umma_commit(smem_u32(&s_empty[s]));
       }
@@ -205,37 +216,28 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
     // ===== epilogue: TMEM -> registers -> scales -> global =====
     const int quarter = warp & 3;
     const int trow = quarter * 32 + lane;  // accumulator lane = weight row of the tile
+    const int m = tile * kQTileM + trow;
+    const bool m_ok = m < p.m_total;
     bool have_acc = true;
     if (num_kb > 0) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
-    // all four epilogue warps must agree (they meet at a named barrier below)
-    {
-      uint32_t all_ok;
-      asm volatile(
-          "{\n\t.reg .pred p, q;\n\t"
-          "setp.ne.b32 p, %1, 0;\n\t"
-          "barrier.red.and.pred q, 1, 128, p;\n\t"
-          "selp.u32 %0, 1, 0, q;\n\t}"
-          : "=r"(all_ok)
-          : "r"((uint32_t)have_acc)
-          : "memory");
-      have_acc = all_ok != 0;
-    }
+    have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld needs the whole warp
+    // A block that gave up writes nothing; the status word reports it.
     if (have_acc) {
       tc_fence_after_sync();
       const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-      // sum of the three plane accumulators for 16 columns starting at c0, times the
-      // token rows' scales
-      auto load_columns = [&](int c0, float (&out)[16]) {
+      // weighted sum of one set's plane accumulators for 16 columns starting at c0, times
+      // the token rows' scales
+      auto load_columns = [&](int set, int c0, float (&out)[16]) {
         if (num_kb > 0) {
-          uint32_t a0[16], a1[16], a2[16];
-          tmem_ld_16(lane_base + (uint32_t)c0, a0);
-          tmem_ld_16(lane_base + (uint32_t)(n_mma + c0), a1);
-          tmem_ld_16(lane_base + (uint32_t)(2 * n_mma + c0), a2);
+          uint32_t a[kPlanes][16];
+#pragma unroll
+          for (int pl = 0; pl < kPlanes; ++pl)
+            tmem_ld_16(lane_base + (uint32_t)((set * kPlanes + pl) * n_mma + c0), a[pl]);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = __uint_as_float(a0[j]) + __uint_as_float(a1[j]) * 0.0625f +
-                            __uint_as_float(a2[j]) * 0.00390625f;
+            float v = __uint_as_float(a[0][j]) + __uint_as_float(a[1][j]) * 0.0625f;
+            if (kPlanes > 2) v += __uint_as_float(a[kPlanes - 1][j]) * 0.00390625f;
             const float ts = (c0 + j < n_rows) ? p.token_scale[row_start + c0 + j] : 0.0f;
             out[j] = v * ts;
           }
@@ -245,58 +247,42 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
         }
       };
       if (kGateUp) {
-        // lanes 0..63: gate rows, lanes 64..127: the matching up rows.  The up half goes
-        // through shared memory (the stage ring is idle now) as xchg[column][row], FP32.
-        const int idx = trow & 63;
-        const int m = tile * 64 + idx;
-        const bool m_ok = m < p.m_total;
-        const bool is_up = trow >= 64;
-        float scale = 0.0f;
-        if (m_ok)
-          scale = p.row_scale[(size_t)expert * 2 * p.m_total + (is_up ? p.m_total : 0) + m];
-        float* xchg = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
-        float v[16];
-        if (is_up) {
-          for (int c0 = 0; c0 < n_mma; c0 += 16) {
-            load_columns(c0, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) xchg[(c0 + j) * 64 + idx] = v[j] * scale;
-          }
+        float gate_scale = 0.0f, up_scale = 0.0f;
+        if (m_ok) {
+          gate_scale = p.row_scale[(size_t)expert * 2 * p.m_total + m];
+          up_scale = p.row_scale[(size_t)expert * 2 * p.m_total + p.m_total + m];
         }
-        asm volatile("barrier.sync 1, 128;" ::: "memory");
-        if (!is_up) {
-          for (int c0 = 0; c0 < n_mma; c0 += 16) {
-            load_columns(c0, v);
+        float g[16], u[16];
+        for (int c0 = 0; c0 < n_mma; c0 += 16) {
+          load_columns(0, c0, g);
+          load_columns(1, c0, u);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float mag = 0.0f;
-              if (m_ok && c0 + j < n_rows) {
-                const float gate = v[j] * scale;
-                const float up = xchg[(c0 + j) * 64 + idx];
-                const float act = gate / (1.0f + __expf(-gate)) * up;
-                const __nv_bfloat16 hi = __float2bfloat16_rn(act);
-                const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
-                const size_t o = (size_t)(row_start + c0 + j) * p.m_total + m;
-                p.act_hi[o] = hi;
-                p.act_lo[o] = lo;
-                // what the next kernel reads back is hi + lo
-                mag = fabsf(__bfloat162float(hi) + __bfloat162float(lo));
-              }
-              // non-negative floats order like their bit patterns
-              const uint32_t warp_max = __reduce_max_sync(0xffffffffu, __float_as_uint(mag));
-              if (lane == 0 && c0 + j < n_rows && warp_max != 0u)
-                atomicMax(p.act_amax + row_start + c0 + j, warp_max);
+          for (int j = 0; j < 16; ++j) {
+            float mag = 0.0f;
+            if (m_ok && c0 + j < n_rows) {
+              const float gate = g[j] * gate_scale;
+              const float up = u[j] * up_scale;
+              const float act = gate / (1.0f + __expf(-gate)) * up;
+              const __nv_bfloat16 hi = __float2bfloat16_rn(act);
+              const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
+              const size_t o = (size_t)(row_start + c0 + j) * p.m_total + m;
+              p.act_hi[o] = hi;
+              p.act_lo[o] = lo;
+              // what the next kernel reads back is hi + lo
+              mag = fabsf(__bfloat162float(hi) + __bfloat162float(lo));
             }
+            // non-negative floats order like their bit patterns
+            const uint32_t warp_max = __reduce_max_sync(0xffffffffu, __float_as_uint(mag));
+            if (lane == 0 && c0 + j < n_rows && warp_max != 0u)
+              atomicMax(p.act_amax + row_start + c0 + j, warp_max);
           }
         }
       } else {
-        const int m = tile * kQTileM + trow;
-        const bool m_ok = m < p.m_total;
         const float scale = m_ok ? p.row_scale[(size_t)expert * p.m_total + m] : 0.0f;
         float* dst = p.partials + (size_t)split * p.rows_cap * p.m_total;
         float v[16];
         for (int c0 = 0; c0 < n_mma; c0 += 16) {
-          load_columns(c0, v);
+          load_columns(0, c0, v);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (m_ok && c0 + j < n_rows)
@@ -324,7 +310,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 }
 
-constexpr uint32_t kQStageBudget = 111u * 1024u;  // five 22 KB stages at 16 rows; two blocks per SM
+constexpr uint32_t kQStageBudget = 111u * 1024u;  // 16 rows: three 36 KB (gate+up) or five 22 KB (down) stages; two blocks per SM
 
 template <bool kGateUp>
 static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b,
@@ -378,7 +364,7 @@ cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_
                                const float* token_scale, int inter, int hidden, int rows_cap,
                                int grid, bool pdl, cudaStream_t stream) {
   QGemmParams p = fp8_params(sched, status, row_scale, token_scale, inter, hidden,
-                             (inter + 63) / 64, rows_cap);
+                             (inter + 127) / 128, rows_cap);
   p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
   p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
   p.act_amax = act_amax;

@@ -151,11 +151,13 @@ combine_bf16_rows_kernel(const uint4* __restrict__ expert_rows,
 }
 
 // ---------------------------------------------------------------------------
-// FP8-weight path: token rows as three E4M3 planes plus a scale per row.
+// FP8-weight path: token rows as E4M3 planes plus a scale per row.
 //
-// r = x / s with s = max|row| / 448 (1 for an all-zero row), then
+// r = x / s, then
 //   p0 = e4m3(r), p1 = e4m3((r - p0) * 16), p2 = e4m3(((r - p0) * 16 - p1) * 16),
 // every rounding to nearest-even, saturating; x ~= s * (p0 + p1/16 + p2/256).
+// Hidden rows (BF16): s = the power of two that puts max|row| / s into [128, 256), two
+// planes, exact.  Activation rows: s = max|row| / 448 (1 for an all-zero row), three planes.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float e4m3_to_float(uint32_t code) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
@@ -182,7 +184,8 @@ __device__ __forceinline__ float block_max(float v, float* tmp) {
   return m;
 }
 
-// Eight consecutive values of one row -> eight bytes in each of the three planes.
+// Eight consecutive values of one row -> eight bytes in each of the kPlanes planes.
+template <int kPlanes>
 __device__ __forceinline__ void store_planes8(const float (&r)[8], uint8_t* plane0,
                                               size_t plane_stride, size_t offset) {
   uint32_t lo[3] = {0u, 0u, 0u}, hi[3] = {0u, 0u, 0u};
@@ -191,19 +194,22 @@ __device__ __forceinline__ void store_planes8(const float (&r)[8], uint8_t* plan
     uint32_t c[3];
     split_e4m3x3(r[i], c[0], c[1], c[2]);
 #pragma unroll
-    for (int pl = 0; pl < 3; ++pl) {
+    for (int pl = 0; pl < kPlanes; ++pl) {
       if (i < 4) lo[pl] |= c[pl] << (8 * i);
       else hi[pl] |= c[pl] << (8 * (i - 4));
     }
   }
 #pragma unroll
-  for (int pl = 0; pl < 3; ++pl)
+  for (int pl = 0; pl < kPlanes; ++pl)
     *reinterpret_cast<uint2*>(plane0 + pl * plane_stride + offset) = make_uint2(lo[pl], hi[pl]);
 }
 
 // Gather for the FP8-weight path: the BF16 row goes to permuted_hidden as in
-// gather_rows_kernel, and its three planes and scale go to scratch.  Also clears the row's
-// activation maximum, which the gate+up kernel accumulates next.
+// gather_rows_kernel, and its planes and scale go to scratch.  The row is BF16 (eight
+// significant bits), so with a power-of-two scale -- the division is then exact -- two
+// planes of four bits each hold it exactly (values below 2^-12 of the row maximum run into
+// the second plane's subnormal step: their error stays under 2^-21 of that maximum).  Also clears the row's activation
+// maximum, which the gate+up kernel accumulates next.
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_fp8_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
                        uint4* __restrict__ out, uint8_t* __restrict__ planes,
@@ -233,7 +239,13 @@ gather_rows_fp8_kernel(const uint4* __restrict__ hidden, const int64_t* __restri
     }
   }
   amax = block_max(amax, s_tmp);
-  const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  // power of two with max|x| / scale in [128, 256): frexp gives amax = f * 2^e, f in [0.5, 1)
+  float scale = 1.0f;
+  if (amax > 0.0f) {
+    int e;
+    frexpf(amax, &e);
+    scale = ldexpf(1.0f, e - 8);
+  }
   if (threadIdx.x == 0) {
     row_scale[row] = scale;
     act_amax[row] = 0u;
@@ -250,7 +262,8 @@ gather_rows_fp8_kernel(const uint4* __restrict__ hidden, const int64_t* __restri
       r[2 * i] = __fdiv_rn(f.x, scale);
       r[2 * i + 1] = __fdiv_rn(f.y, scale);
     }
-    store_planes8(r, planes, plane_stride, (size_t)row * hidden_size + (size_t)v * 8);
+    store_planes8<kFp8PlanesHidden>(r, planes, plane_stride,
+                                    (size_t)row * hidden_size + (size_t)v * 8);
   }
   trace_end(trace, kTraceGather);
 }
@@ -287,7 +300,7 @@ act_planes_fp8_kernel(const uint4* __restrict__ act_hi, const uint4* __restrict_
     r[2 * i] = __fdiv_rn(fh.x + fl.x, scale);
     r[2 * i + 1] = __fdiv_rn(fh.y + fl.y, scale);
   }
-  store_planes8(r, planes, plane_stride, (size_t)row * inter + (size_t)v * 8);
+  store_planes8<kFp8Planes>(r, planes, plane_stride, (size_t)row * inter + (size_t)v * 8);
 }
 
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,

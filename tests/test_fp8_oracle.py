@@ -89,3 +89,28 @@ def test_three_plane_split_reconstructs_to_twelve_bits() -> None:
     assert (err <= bound).all(), float((err / np.maximum(bound, 1e-30)).max())
     # no plane ever needs the NaN code or saturation after the first
     assert not ((codes & 0x7F) == 0x7F).any()
+
+
+def test_two_plane_split_of_bf16_rows_is_exact() -> None:
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(16, 1024, generator=g).to(torch.bfloat16)
+    x[2] = 0.0
+    x[4, 9] = 300.0
+    x[5] *= 1e-3
+    x[6, :8] = torch.tensor([1.0, -1.0, 0.5, 255.0, 1.0078125, 3.984375, 2.0 ** -7, -(2.0 ** -9)])
+    codes, scale = fp8_oracle.split_planes_pow2(x.float().numpy())
+    assert codes.shape == (2, 16, 1024)
+    mantissa, _ = np.frexp(scale)
+    assert (mantissa == 0.5).all()                      # powers of two
+    amax = x.float().abs().amax(dim=-1).numpy()
+    ratio = amax[amax > 0] / scale[amax > 0]
+    assert (ratio >= 128).all() and (ratio < 256).all()
+    planes = fp8_oracle.dequantize_e4m3(codes).astype(np.float64)
+    back = (planes[0] + planes[1] / 16.0) * scale.astype(np.float64)[:, None]
+    want = x.float().numpy().astype(np.float64)
+    err = np.abs(back - want)
+    # exact wherever the value is not vanishingly small against its row's maximum
+    big = np.abs(want) >= amax[:, None] * 2.0 ** -12
+    assert (err[big] == 0).all()
+    # below that the second plane runs into its subnormal step: 2^-14 of a scaled maximum >= 2^7
+    assert (err <= amax[:, None] * 2.0 ** -21 + 1e-30).all()
