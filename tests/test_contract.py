@@ -171,3 +171,59 @@ def test_validate_returns_shape() -> None:
     shape = validate_routed_moe_inputs(*_case(), num_experts=8, top_k=2)
     assert (shape.num_tokens, shape.num_experts, shape.top_k) == (4, 8, 2)
     assert (shape.hidden_size, shape.intermediate_size, shape.num_assignments) == (16, 24, 8)
+
+
+# ---------------------------------------------------------------------------
+# FP8-weight entry point: host-side contract (no GPU needed to be rejected)
+# ---------------------------------------------------------------------------
+def _fp8_inputs(E=4, H=32, I=48, K=2, T=3):
+    from b200moe import Fp8ExpertWeights
+
+    hidden = torch.zeros(T, H, dtype=torch.bfloat16)
+    ids = torch.zeros(T, K, dtype=torch.int64)
+    ids[:, 1] = 1
+    weights = torch.ones(T, K, dtype=torch.bfloat16)
+    fw = Fp8ExpertWeights(
+        torch.zeros(E, 2 * I, H, dtype=torch.uint8), torch.ones(E, 2 * I, dtype=torch.float32),
+        torch.zeros(E, H, I, dtype=torch.uint8), torch.ones(E, H, dtype=torch.float32))
+    return hidden, ids, weights, fw
+
+
+def test_fp8_forward_rejects_bad_arguments_on_the_host() -> None:
+    from b200moe import Fp8ExpertWeights, b300_moe_forward_fp8
+
+    hidden, ids, weights, fw = _fp8_inputs()
+    E, K = 4, 2
+    with pytest.raises(TypeError, match="Fp8ExpertWeights"):
+        b300_moe_forward_fp8(hidden, ids, weights, (fw.gate_up_q, fw.down_q), num_experts=E, top_k=K)
+    with pytest.raises(TypeError, match="return_metadata"):
+        b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K, return_metadata=1)
+    with pytest.raises(TypeError, match="int64"):
+        b300_moe_forward_fp8(hidden, ids.int(), weights, fw, num_experts=E, top_k=K)
+    with pytest.raises(ValueError, match="num_experts"):
+        b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E + 1, top_k=K)
+    with pytest.raises(ValueError, match="hidden dimension"):
+        b300_moe_forward_fp8(hidden[:, :16].contiguous(), ids, weights, fw, num_experts=E, top_k=K)
+    with pytest.raises(TypeError, match="uint8"):
+        bad = Fp8ExpertWeights(fw.gate_up_q.to(torch.int8), fw.gate_up_scale, fw.down_q, fw.down_scale)
+        b300_moe_forward_fp8(hidden, ids, weights, bad, num_experts=E, top_k=K)
+    with pytest.raises(TypeError, match="float32"):
+        bad = Fp8ExpertWeights(fw.gate_up_q, fw.gate_up_scale.double(), fw.down_q, fw.down_scale)
+        b300_moe_forward_fp8(hidden, ids, weights, bad, num_experts=E, top_k=K)
+    with pytest.raises(TypeError, match="bfloat16"):
+        b300_moe_forward_fp8(hidden.float(), ids, weights.float(), fw, num_experts=E, top_k=K)
+    with pytest.raises(ValueError, match="out-of-range"):
+        b300_moe_forward_fp8(hidden, ids + 7, weights, fw, num_experts=E, top_k=K)
+    # H = 40 is a multiple of 8 (enough for BF16 weights) but not of 16
+    h40, i40, w40, fw40 = _fp8_inputs(H=40)
+    with pytest.raises(ValueError, match="divisible by 16"):
+        b300_moe_forward_fp8(h40, i40, w40, fw40, num_experts=E, top_k=K)
+    # a valid call still needs a CUDA device: there is no CPU path
+    with pytest.raises(ValueError, match="requires CUDA tensors"):
+        b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K)
+
+
+def test_fp8_weight_container_reports_its_geometry() -> None:
+    _, _, _, fw = _fp8_inputs(E=4, H=32, I=48)
+    assert (fw.num_experts, fw.hidden_size, fw.intermediate_size) == (4, 32, 48)
+    assert fw.nbytes == 4 * (2 * 48 * 32 + 32 * 48) + 4 * 4 * (2 * 48 + 32)
