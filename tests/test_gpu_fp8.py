@@ -294,3 +294,28 @@ def test_full_size_deepseek_shaped_layer_spot_checked(cuda_device) -> None:
     err = float((got - ref).abs().max()) / moe_oracle.rms(ref)
     print(f"fp8 deepseek-shaped full size: err/rms={err:.5f} floor={moe_oracle.bf16_floor(ref):.5f}")
     assert err <= TOLERANCE
+
+
+def test_one_workspace_serves_bf16_and_fp8_calls_alternately(cuda_device) -> None:
+    """The two weight formats share a workspace layout; switching between them per call must
+    neither reallocate nor leak state from one call into the next, with and without PDL."""
+
+    from b200moe import (B300MoEWorkspace, b300_moe_forward, b300_moe_forward_fp8,
+                         quantize_expert_weights_fp8)
+
+    E, H, I, K, T = 8, 256, 384, 2, 10
+    gate_up, down, hidden, ids, weights = _case(E, H, I, K, T, seed=9)
+    gate_up, down = gate_up.to(cuda_device), down.to(cuda_device)
+    fw = quantize_expert_weights_fp8(gate_up, down)
+    dev = (hidden.to(cuda_device), ids.to(cuda_device), weights.to(cuda_device))
+    want_bf16 = b300_moe_forward(*dev, gate_up, down, num_experts=E, top_k=K)
+    want_fp8 = b300_moe_forward_fp8(*dev, fw, num_experts=E, top_k=K)
+    ws = B300MoEWorkspace(device=cuda_device)
+    for use_pdl in (True, False, True):
+        got_fp8 = b300_moe_forward_fp8(*dev, fw, num_experts=E, top_k=K, workspace=ws,
+                                       use_pdl=use_pdl, check_status=True)
+        got_bf16 = b300_moe_forward(*dev, gate_up, down, num_experts=E, top_k=K, workspace=ws,
+                                    use_pdl=use_pdl, check_status=True)
+        assert torch.equal(got_fp8, want_fp8)
+        assert torch.equal(got_bf16, want_bf16)
+    assert ws.allocation_count == 1
