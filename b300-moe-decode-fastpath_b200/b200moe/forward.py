@@ -352,9 +352,13 @@ def b300_moe_forward_pinned(
     workspace: B300MoEWorkspace,
     out: torch.Tensor | None = None,
     use_pdl: bool = True,
+    fp8_weights=None,
 ) -> torch.Tensor:
     """The layer with its per-step tensors in pinned host memory (no counterpart in the
     reference, whose compiled path takes device tensors only).
+
+    With ``fp8_weights`` (an ``Fp8ExpertWeights``) the FP8-weight kernels run; the two BF16
+    weight arguments are then ignored and may be ``None``.
 
     A decode step's activations ``[T,H]``, routes and routing weights are a few KB to a few
     hundred KB.  Copying them with four separate DMA transfers costs more in launch latency
@@ -367,6 +371,9 @@ def b300_moe_forward_pinned(
     checks as :func:`b300_moe_forward`.
     """
 
+    if fp8_weights is not None:
+        return _forward_pinned_fp8(hidden_states, expert_indices, expert_weights, fp8_weights,
+                                   num_experts, top_k, workspace, out, use_pdl)
     device = gate_up_weight.device
     if device.type != "cuda":
         raise ValueError("expert weights must be CUDA tensors")
@@ -404,3 +411,51 @@ def b300_moe_forward_pinned(
         workspace._record_use()
     return out
 
+
+
+def _forward_pinned_fp8(hidden_states, expert_indices, expert_weights, fw, num_experts, top_k,
+                        workspace, out, use_pdl):
+    """:func:`b300_moe_forward_pinned` for FP8 expert weights."""
+
+    from .fp8 import Fp8ExpertWeights, _validate
+
+    if not isinstance(fw, Fp8ExpertWeights):
+        raise TypeError("fp8_weights must be an Fp8ExpertWeights")
+    device = fw.gate_up_q.device
+    if device.type != "cuda":
+        raise ValueError("expert weights must be CUDA tensors")
+    per_step = (hidden_states, expert_indices, expert_weights) + ((out,) if out is not None else ())
+    for tensor in per_step:
+        if not isinstance(tensor, torch.Tensor) or tensor.device.type != "cpu" or \
+                not tensor.is_pinned():
+            raise ValueError("per-step tensors must be pinned host tensors")
+    if not isinstance(workspace, B300MoEWorkspace):
+        raise TypeError("workspace must be a B300MoEWorkspace")
+    shape = _validate(hidden_states, expert_indices, expert_weights, fw, num_experts, top_k,
+                      weights_on_other_device=True)
+    # device, capability and build gates are those of the GPU that holds the weights (an empty
+    # BF16 tensor there stands in for the host-resident activations)
+    _resolve_native_backend("b200_fp8", fw.gate_up_scale.new_empty(0, dtype=torch.bfloat16),
+                            fw.gate_up_scale, fw.gate_up_scale, fw.down_scale, shape)
+    if out is None:
+        out = torch.empty(shape.num_tokens, shape.hidden_size, dtype=hidden_states.dtype,
+                          pin_memory=True)
+    elif tuple(out.shape) != (shape.num_tokens, shape.hidden_size) or \
+            out.dtype != hidden_states.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [T, H] tensor of the input dtype")
+    with workspace._lock:
+        workspace.reserve(
+            num_tokens=shape.num_tokens, num_experts=shape.num_experts, top_k=shape.top_k,
+            hidden_size=shape.hidden_size, intermediate_size=shape.intermediate_size,
+            device=device, dtype=hidden_states.dtype, backend="b200_bf16", quant_mode="bf16",
+        )
+        flags = _lib.FLAG_FP8_WEIGHTS | (_lib.FLAG_PDL if use_pdl else 0)
+        args = _native_args(hidden_states, expert_indices, expert_weights, fw.gate_up_q,
+                            fw.down_q, shape, workspace, out, flags)
+        args.gate_up_scale = fw.gate_up_scale.data_ptr()
+        args.down_scale = fw.down_scale.data_ptr()
+        code = _enqueue(_lib.load().b200moe_forward, args, device)
+        if code:
+            _lib.check(code, "b200moe_forward")
+        workspace._record_use()
+    return out

@@ -7,11 +7,12 @@ raising here too; this module is a separate, explicitly named entry point and ne
 in for another backend.
 
 Format: one E4M3 byte per weight plus one FP32 scale per weight row
-(``scale = max|row| / 448``).  Activations, routing weights, accumulation (FP32) and the
-output stay as in the BF16 path; the kernels expand each E4M3 byte to the BF16 of the same
-value in shared memory (exact) and apply the row scale to the FP32 accumulator, so the
-layer equals the FP32 reference evaluated on the dequantised weights within the usual
-2e-2 x RMS bar.
+(``scale = max|row| / 448``).  Routing, routing weights, accumulation (FP32) and the output
+stay as in the BF16 path.  The weights feed ``tcgen05.mma kind::f8f6f4`` as they are; the
+token rows are split into E4M3 planes (two exact planes for the BF16 hidden rows, three for
+the activation rows: twelve significant bits, BF16 has eight) and the scales are applied to
+the FP32 accumulators, so the layer equals the FP32 reference evaluated on the dequantised
+weights within the usual 2e-2 x RMS bar.
 """
 
 from __future__ import annotations
@@ -124,7 +125,12 @@ def dequantize_expert_weights_fp8(weights: Fp8ExpertWeights) -> tuple[torch.Tens
 
 
 def _validate(hidden_states, expert_indices, expert_weights, weights: Fp8ExpertWeights,
-              num_experts: int, top_k: int) -> RoutedMoEShape:
+              num_experts: int, top_k: int, *, weights_on_other_device: bool = False
+              ) -> RoutedMoEShape:
+    """Contract of the FP8-weight entry points.  ``weights_on_other_device`` relaxes the
+    one-device rule for the pinned-host variant: the three per-step tensors share a device
+    and the four weight tensors share a device."""
+
     if not isinstance(weights, Fp8ExpertWeights):
         raise TypeError("weights must be an Fp8ExpertWeights")
     tokens, slots = validate_routing(expert_indices, expert_weights, num_experts, top_k)
@@ -150,9 +156,12 @@ def _validate(hidden_states, expert_indices, expert_weights, weights: Fp8ExpertW
         raise TypeError("scales must have dtype torch.float32")
     if hidden_states.dtype != torch.bfloat16 or expert_weights.dtype != torch.bfloat16:
         raise TypeError("the FP8-weight path requires bfloat16 activations and routing weights")
-    tensors = (hidden_states, expert_indices, expert_weights, weights.gate_up_q,
-               weights.gate_up_scale, weights.down_q, weights.down_scale)
-    if any(t.device != hidden_states.device for t in tensors):
+    per_step = (hidden_states, expert_indices, expert_weights)
+    resident = (weights.gate_up_q, weights.gate_up_scale, weights.down_q, weights.down_scale)
+    tensors = per_step + resident
+    anchor = weights.gate_up_q.device if weights_on_other_device else hidden_states.device
+    if any(t.device != hidden_states.device for t in per_step) or \
+            any(t.device != anchor for t in resident):
         raise ValueError("all inputs must be on the same device")
     if not all(t.is_contiguous() for t in tensors):
         raise ValueError("all inputs must be contiguous")

@@ -319,3 +319,25 @@ def test_one_workspace_serves_bf16_and_fp8_calls_alternately(cuda_device) -> Non
         assert torch.equal(got_fp8, want_fp8)
         assert torch.equal(got_bf16, want_bf16)
     assert ws.allocation_count == 1
+
+
+def test_pinned_host_io_with_fp8_weights(cuda_device) -> None:
+    """Per-step tensors in pinned host memory, read and written by the kernels directly,
+    with FP8 expert weights: same bits as the device-resident call."""
+
+    from b200moe import (B300MoEWorkspace, b300_moe_forward_fp8, b300_moe_forward_pinned,
+                         quantize_expert_weights_fp8)
+
+    E, H, I, K, T = 8, 256, 384, 2, 7
+    gate_up, down, hidden, ids, weights = _case(E, H, I, K, T, seed=11)
+    fw = quantize_expert_weights_fp8(gate_up.to(cuda_device), down.to(cuda_device))
+    want = b300_moe_forward_fp8(hidden.to(cuda_device), ids.to(cuda_device),
+                                weights.to(cuda_device), fw, num_experts=E, top_k=K)
+    host = tuple(t.pin_memory() for t in (hidden, ids, weights))
+    ws = B300MoEWorkspace(device=cuda_device)
+    got = b300_moe_forward_pinned(*host, None, None, num_experts=E, top_k=K, workspace=ws,
+                                  fp8_weights=fw)
+    torch.cuda.synchronize(cuda_device)
+    assert got.is_pinned() and got.device.type == "cpu"
+    assert torch.equal(got, want.cpu())
+    assert ws.status() == 0
