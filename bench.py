@@ -83,6 +83,7 @@ STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch at T=1 from
 # the committed ncu capture (profiles/); None until a capture exists.
 GATE_UP_T1_DRAM_TRAFFIC_BYTES = 473_528_320  # 469.84 MB read + 3.69 MB written
+GATE_UP_T1_DRAM_TRAFFIC_BYTES_FP8 = 239_050_752  # FP8 weights: 235.18 MB read + 3.87 MB written
 
 
 def percentile(sorted_values: list[float], q: float) -> float:
@@ -655,7 +656,10 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "unit": "GB/s",
         "frac": round(achieved / peak, 3),
         "algorithmic_bytes": gu_bytes,
-        "traffic": GATE_UP_T1_DRAM_TRAFFIC_BYTES if fp8 is None else None,
+        # the captures are of the Mixtral-shaped layer at T=1 (two active experts)
+        "traffic": (None if (args.config != "mixtral" or sweep[0] != 1)
+                    else GATE_UP_T1_DRAM_TRAFFIC_BYTES if fp8 is None
+                    else GATE_UP_T1_DRAM_TRAFFIC_BYTES_FP8),
         "frac_of_8000": round(achieved / 8000.0, 3),
     }
 
