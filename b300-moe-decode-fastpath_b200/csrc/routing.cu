@@ -114,6 +114,11 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
   }
   __syncthreads();
 
+  // The routing weight of this thread's first assignment is only copied (pass 2); asking
+  // for it now lets its memory latency overlap the histogram and the scans.
+  __nv_bfloat16 first_weight = __float2bfloat16(0.0f);
+  if (perm_weights && weights && tid < num_assign) first_weight = weights[tid];
+
   // Pass 1: histogram.  Ids outside [0, E) are not counted (the reference
   // ignores them the same way, csrc/routing_kernels.cu:33) and are reported.
   for (int a = tid; a < num_assign; a += threads) {
@@ -206,7 +211,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
       permutation[p] = a;
       if (perm_tokens) perm_tokens[p] = a / top_k;
       if (perm_experts) perm_experts[p] = e;
-      if (perm_weights && weights) perm_weights[p] = weights[a];
+      if (perm_weights && weights) perm_weights[p] = base == 0 ? first_weight : weights[a];
     } else if (a < num_assign) {
       reverse_mapping[a] = -1;
     }
