@@ -45,21 +45,23 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
                            int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
                            int num_assign, int num_experts, int id_base, int top_k,
-                           const CUtensorMap* map_hidden, bool pdl, cudaStream_t stream);
+                           const CUtensorMap* map_hidden, int sm_count, bool pdl,
+                           cudaStream_t stream);
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
-                        float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
-                        cudaStream_t stream);
+                        float* partials, int hidden, int inter, int rows_cap, int grid,
+                        int sm_count, bool pdl, cudaStream_t stream);
 
 cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
                                const int32_t* sched, uint32_t* status, void* act_hi,
                                void* act_lo, uint32_t* act_amax, const float* row_scale,
                                const float* token_scale, int inter, int hidden, int rows_cap,
-                               int grid, bool pdl, cudaStream_t stream);
+                               int grid, int sm_count, bool pdl, cudaStream_t stream);
 cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
                             const int32_t* sched, uint32_t* status, float* partials,
                             const float* row_scale, const float* token_scale, int hidden,
-                            int inter, int rows_cap, int grid, bool pdl, cudaStream_t stream);
+                            int inter, int rows_cap, int grid, int sm_count, bool pdl,
+                            cudaStream_t stream);
 cudaError_t launch_gather_fp8(const void* hidden, const int64_t* permutation, void* out,
                               uint8_t* planes, float* row_scale, uint32_t* act_amax,
                               int num_assign, int num_tokens, int top_k, int hidden_size,
@@ -280,7 +282,7 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
                int hidden, int inter, void* act_hi, const Scratch& s, const int64_t* ids,
-               int id_base, int top_k, const void* hidden_states, bool pdl,
+               int id_base, int top_k, const void* hidden_states, const DeviceInfo& dev, bool pdl,
                cudaStream_t stream) {
   CUtensorMap map_w, map_x;
   {
@@ -308,7 +310,7 @@ int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int 
   }
   return (int)launch_gate_up(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, inter, hidden,
                              rows_cap, grid, ids, assignments, experts, id_base, top_k,
-                             have_hidden ? &map_hidden : nullptr, pdl, stream);
+                             have_hidden ? &map_hidden : nullptr, dev.sm_count, pdl, stream);
 }
 
 int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, int experts,
@@ -330,7 +332,7 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   const int grid = down_grid(segment_bound(assignments, experts), tiles128(hidden),
                              (inter + 63) / 64, dev.sm_count);
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
-                          rows_cap, grid, pdl, stream);
+                          rows_cap, grid, dev.sm_count, pdl, stream);
 }
 
 // FP8 weights: one-byte tensor maps of the weights and of the token planes.
@@ -342,8 +344,8 @@ int encode_plane_map(CUtensorMap* map, const uint8_t* planes, int cols, int rows
 }
 
 int do_gate_up_fp8(const void* w, const float* row_scale, int rows_cap, int assignments,
-                   int experts, int hidden, int inter, void* act_hi, const Scratch& s, bool pdl,
-                   cudaStream_t stream) {
+                   int experts, int hidden, int inter, void* act_hi, const Scratch& s,
+                   const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
   CUtensorMap map_w, map_x;
   {
     const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
@@ -355,8 +357,8 @@ int do_gate_up_fp8(const void* w, const float* row_scale, int rows_cap, int assi
   if (rc) return rc;
   const int grid = segment_bound(assignments, experts, g_fp8_seg_rows) * tiles128(inter);
   return (int)launch_gate_up_fp8(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, s.a_amax,
-                                 row_scale, s.x_scale, inter, hidden, rows_cap, grid, pdl,
-                                 stream);
+                                 row_scale, s.x_scale, inter, hidden, rows_cap, grid,
+                                 dev.sm_count, pdl, stream);
 }
 
 int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int rows_cap,
@@ -378,7 +380,8 @@ int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int r
                                   inter, rows_cap, pdl, stream);
   if (rc) return rc;
   return (int)launch_down_fp8(map_w, map_act, s.sched, s.status, s.partials, row_scale,
-                              s.a_scale, hidden, inter, rows_cap, grid, pdl, stream);
+                              s.a_scale, hidden, inter, rows_cap, grid, dev.sm_count, pdl,
+                              stream);
 }
 
 unsigned long long* trace_of(const Scratch& s) {
@@ -445,13 +448,13 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
     if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
     return do_gate_up_fp8(a->gate_up_weight, a->gate_up_scale, a->rows_cap, c.assignments,
                           a->num_experts, a->hidden_size, a->intermediate_size,
-                          a->swiglu_output, c.s, pdl, c.stream);
+                          a->swiglu_output, c.s, c.dev, pdl, c.stream);
   }
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
                     a->ep_wait_flags ? nullptr : a->expert_indices,
                     (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) ? a->expert_id_base : 0, a->top_k,
-                    a->hidden_states, pdl, c.stream);
+                    a->hidden_states, c.dev, pdl, c.stream);
 }
 
 int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {

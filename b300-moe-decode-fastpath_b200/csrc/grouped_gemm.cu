@@ -417,8 +417,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
 int g_gemm_stage_kb = 108;
 int g_gemm_evict_first = 0;
 int g_early_mode = 0;
-static uint32_t gemm_stage_budget() {
+// Shared memory of one block's stage ring.  Normally two blocks share an SM.  A grid that
+// cannot put more than one block on an SM anyway (`grid <= sm_count`, known on the host from
+// the worst-case unit count) gets the whole SM per block: with so few blocks the bytes in
+// flight, not HBM, bound the stream, and a ring twice as deep doubles them.
+constexpr uint32_t kLoneBlockStageBudget = 216u * 1024u;
+static uint32_t gemm_stage_budget(int grid, int sm_count) {
   uint32_t b = (uint32_t)g_gemm_stage_kb * 1024u;
+  if (g_gemm_stage_kb == 108 && sm_count > 0 && grid <= sm_count) b = kLoneBlockStageBudget;
   if (b < 48u * 1024u) b = 48u * 1024u;
   if (b > kMaxStageBudget) b = kMaxStageBudget;
   return b;
@@ -456,7 +462,8 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
                            int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
                            int num_assign, int num_experts, int id_base, int top_k,
-                           const CUtensorMap* map_hidden, bool pdl, cudaStream_t stream) {
+                           const CUtensorMap* map_hidden, int sm_count, bool pdl,
+                           cudaStream_t stream) {
   GemmParams p = {};
   p.ids = ids;
   p.num_assign = num_assign;
@@ -467,7 +474,7 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
   p.early_mode = g_early_mode;
   p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
                                                   kTraceOffsetBytes);
-  p.stage_budget = gemm_stage_budget();
+  p.stage_budget = gemm_stage_budget(grid, sm_count);
   p.evict_first = g_gemm_evict_first;
   p.sched = sched;
   p.status = status;
@@ -483,10 +490,10 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
 
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
-                        float* partials, int hidden, int inter, int rows_cap, int grid, bool pdl,
-                        cudaStream_t stream) {
+                        float* partials, int hidden, int inter, int rows_cap, int grid,
+                        int sm_count, bool pdl, cudaStream_t stream) {
   GemmParams p = {};
-  p.stage_budget = gemm_stage_budget();
+  p.stage_budget = gemm_stage_budget(grid, sm_count);
   p.evict_first = g_gemm_evict_first;
   p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
                                                   kTraceOffsetBytes);

@@ -311,6 +311,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
 }
 
 constexpr uint32_t kQStageBudget = 111u * 1024u;  // 16 rows: three 36 KB (gate+up) or five 22 KB (down) stages; two blocks per SM
+// a grid of at most one block per SM gets the whole SM's shared memory per block (deeper
+// ring: more bytes in flight when few blocks stream)
+constexpr uint32_t kQLoneBlockStageBudget = 216u * 1024u;
 
 template <bool kGateUp>
 static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b,
@@ -323,14 +326,14 @@ static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     err = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kGateUp>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)(kQStageBudget + 1024u));
+                               (int)(kQLoneBlockStageBudget + 1024u));
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kQThreads);
-  cfg.dynamicSmemBytes = kQStageBudget + 1024u;
+  cfg.dynamicSmemBytes = params.stage_budget + 1024u;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -342,7 +345,7 @@ static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b
 
 static QGemmParams fp8_params(const int32_t* sched, uint32_t* status, const float* row_scale,
                               const float* token_scale, int m_total, int k_total, int m_tiles,
-                              int rows_cap) {
+                              int rows_cap, int grid, int sm_count) {
   QGemmParams p = {};
   p.sched = sched;
   p.status = status;
@@ -354,7 +357,7 @@ static QGemmParams fp8_params(const int32_t* sched, uint32_t* status, const floa
   p.rows_cap = rows_cap;
   p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
                                                   kTraceOffsetBytes);
-  p.stage_budget = kQStageBudget;
+  p.stage_budget = (sm_count > 0 && grid <= sm_count) ? kQLoneBlockStageBudget : kQStageBudget;
   return p;
 }
 
@@ -362,9 +365,9 @@ cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_
                                const int32_t* sched, uint32_t* status, void* act_hi,
                                void* act_lo, uint32_t* act_amax, const float* row_scale,
                                const float* token_scale, int inter, int hidden, int rows_cap,
-                               int grid, bool pdl, cudaStream_t stream) {
+                               int grid, int sm_count, bool pdl, cudaStream_t stream) {
   QGemmParams p = fp8_params(sched, status, row_scale, token_scale, inter, hidden,
-                             (inter + 127) / 128, rows_cap);
+                             (inter + 127) / 128, rows_cap, grid, sm_count);
   p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
   p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
   p.act_amax = act_amax;
@@ -374,9 +377,10 @@ cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_
 cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
                             const int32_t* sched, uint32_t* status, float* partials,
                             const float* row_scale, const float* token_scale, int hidden,
-                            int inter, int rows_cap, int grid, bool pdl, cudaStream_t stream) {
+                            int inter, int rows_cap, int grid, int sm_count, bool pdl,
+                            cudaStream_t stream) {
   QGemmParams p = fp8_params(sched, status, row_scale, token_scale, hidden, inter,
-                             (hidden + 127) / 128, rows_cap);
+                             (hidden + 127) / 128, rows_cap, grid, sm_count);
   p.partials = partials;
   return launch_fp8<false>(map_w, map_act, p, grid, pdl, stream);
 }
