@@ -104,3 +104,43 @@ def test_scratch_bytes_and_host_side_errors(lib) -> None:
     assert "top" in _lib.error_string(-2).lower() or "shape" in _lib.error_string(-2).lower()
     with pytest.raises(ValueError):
         _lib.check(-3, "probe")
+
+
+def test_header_is_plain_c_and_links_from_c(lib, tmp_path) -> None:
+    """The boundary is a C ABI: the header must compile as C99 (and as C++), and a C
+    program must link against the library and call it with nothing but the header."""
+
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    from b200moe import _lib
+
+    source = tmp_path / "abi_check.c"
+    source.write_text(
+        '#include <stddef.h>\n#include <string.h>\n#include "b200moe.h"\n'
+        "int main(void) {\n"
+        "  B200MoeArgs args; size_t bytes = 0; char info[1024];\n"
+        "  memset(&args, 0, sizeof args);\n"
+        "  if (b200moe_abi_version() != B200MOE_ABI_VERSION) return 1;\n"
+        "  if (b200moe_scratch_bytes(64, 2, 8, 4096, 14336, &bytes) != 0 || bytes == 0) return 2;\n"
+        "  if (b200moe_scratch_bytes(64, 3, 8, 4096, 14336, &bytes) != B200MOE_E_SHAPE) return 3;\n"
+        "  if (b200moe_forward(NULL, NULL) != B200MOE_E_NULL) return 4;\n"
+        "  if (b200moe_build_info(info, sizeof info) <= 0 || !strstr(info, \"sm_100a\")) return 5;\n"
+        "  if (b200moe_nvfp4_available() != 0) return 6;\n"
+        "  return 0;\n}\n"
+    )
+    include = str(HEADER.parent)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                    "-I", include, str(source)], check=True)
+    if shutil.which("g++"):
+        subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++",
+                        "-I", include, str(source)], check=True)
+    library = _lib.library_path()
+    binary = tmp_path / "abi_check"
+    subprocess.run(["gcc", "-std=c99", "-I", include, str(source), "-o", str(binary),
+                    f"-L{library.parent}", "-l:" + library.name,
+                    f"-Wl,-rpath,{library.parent}"], check=True)
+    result = subprocess.run([str(binary)], capture_output=True, text=True)
+    assert result.returncode == 0, (result.returncode, result.stderr)
