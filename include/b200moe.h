@@ -69,6 +69,11 @@ extern "C" {
  * which names quantised expert weights as future work (docs/goal_1b_report.md:313-314);
  * the "cutlass_nvfp4" name keeps failing loudly (b200moe_nvfp4_available() == 0). */
 #define B200MOE_FLAG_FP8_WEIGHTS   0x8u
+/* With B200MOE_FLAG_FP8_WEIGHTS the staged entry points keep their meaning, with two
+ * details: b200moe_gather also writes the gathered rows as E4M3 planes into scratch, which
+ * b200moe_gate_up_swiglu consumes; b200moe_down first turns the activation rows into planes
+ * in the same scratch bytes (one extra launch inside the call), so after it the planes of
+ * stage 2 are gone and stage 3 cannot be repeated without repeating stage 2. */
 
 /* ABI version of the loaded library (== B200MOE_ABI_VERSION it was built with). */
 int b200moe_abi_version(void);
