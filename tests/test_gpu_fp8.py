@@ -341,3 +341,48 @@ def test_pinned_host_io_with_fp8_weights(cuda_device) -> None:
     assert got.is_pinned() and got.device.type == "cpu"
     assert torch.equal(got, want.cpu())
     assert ws.status() == 0
+
+
+def test_seeded_random_shapes_both_weight_formats(cuda_device) -> None:
+    """Twenty-four seeded random geometries (ragged H and I, every top_k, all routing patterns,
+    token counts up to 150 so that experts exceed one segment) through both weight formats:
+    routing bit-exact, outputs within the bar of their FP32 oracles."""
+
+    import random
+
+    from b200moe import (B300MoEWorkspace, b300_moe_forward, b300_moe_forward_fp8,
+                         quantize_expert_weights_fp8)
+
+    rng = random.Random(20240607)
+    patterns = ("uniform", "zipf", "concentrated", "empty_half", "duplicates")
+    for trial in range(24):
+        E = rng.choice((1, 2, 3, 8, 17, 64))
+        K = rng.choice([k for k in (1, 2, 4, 8) if k <= E])
+        H = 16 * rng.randint(1, 24)
+        I = 16 * rng.randint(1, 24)
+        T = rng.choice((1, 2, 3, 7, 16, 33, 64, 150))
+        routing = rng.choice(patterns)
+        if routing == "empty_half" and E < 2 * K:
+            routing = "uniform"
+        gate_up, down, hidden, ids, weights = _case(E, H, I, K, T, routing, seed=100 + trial)
+        dev = (hidden.to(cuda_device), ids.to(cuda_device), weights.to(cuda_device))
+        gate_up_d, down_d = gate_up.to(cuda_device), down.to(cuda_device)
+        label = f"trial {trial}: E{E} K{K} H{H} I{I} T{T} {routing}"
+
+        ws = B300MoEWorkspace(device=cuda_device)
+        out, meta = b300_moe_forward(*dev, gate_up_d, down_d, num_experts=E, top_k=K,
+                                     workspace=ws, return_metadata=True, check_status=True)
+        ref, routing_ref = moe_oracle.routed_moe(hidden, ids, weights, gate_up, down,
+                                                 num_experts=E, top_k=K)
+        for key in ("permutation", "reverse_mapping", "expert_counts", "expert_offsets"):
+            np.testing.assert_array_equal(meta[key].cpu().numpy(), getattr(routing_ref, key),
+                                          err_msg=f"{label} {key}")
+        _check(out, ref, label + " bf16")
+
+        fw = quantize_expert_weights_fp8(gate_up_d, down_d)
+        out8, meta8 = b300_moe_forward_fp8(*dev, fw, num_experts=E, top_k=K, workspace=ws,
+                                           return_metadata=True, check_status=True)
+        ref8, _ = _reference(fw, hidden, ids, weights, E, K)
+        np.testing.assert_array_equal(meta8["permutation"].cpu().numpy(), routing_ref.permutation,
+                                      err_msg=label)
+        _check(out8, ref8, label + " fp8")
