@@ -10,6 +10,7 @@ from ._lib import build_info
 from .forward import ARCHITECTURE, b300_moe_forward, b300_moe_forward_pinned
 from .fp8 import (Fp8ExpertWeights, b300_moe_forward_fp8, dequantize_expert_weights_fp8,
                   dequantize_rows_fp8, quantize_expert_weights_fp8, quantize_rows_fp8)
+from .graphed import GraphedMoEDecodeLayer
 from .ops import DispatchResult, combine_tokens, dispatch_tokens
 from .router import topk_routing
 from .stages import StagedLayer
@@ -21,6 +22,7 @@ __all__ = [
     "B300MoEWorkspace",
     "DispatchResult",
     "Fp8ExpertWeights",
+    "GraphedMoEDecodeLayer",
     "RoutedMoEShape",
     "StagedLayer",
     "b300_moe_forward",

@@ -566,3 +566,58 @@ def test_bench_writes_reference_csv_schema(tmp_path):
     assert float(by_stage["total_us"]["p50_us"]) > 50.0
     assert all(r["used_fallback"] == "false" and r["architecture"] == "sm_100a" for r in rows)
     assert {r["num_tokens"] for r in rows} == {"1", "4"}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True], ids=["bf16", "fp8"])
+def test_graphed_layer_replays_equal_eager_calls(fp8, cuda_device) -> None:
+    """GraphedMoEDecodeLayer: one captured graph per token count, bit-identical to the eager
+    call for changing inputs; other token counts fall back to an eager call on a separate
+    workspace and leave the captured graphs intact."""
+
+    from b200moe import (GraphedMoEDecodeLayer, b300_moe_forward, b300_moe_forward_fp8,
+                         quantize_expert_weights_fp8, workloads)
+
+    H, I, E, K = 256, 384, 8, 2
+    _, _, _, gate_up, down = workloads.make_case(1, H, I, E, K, std=None, device=cuda_device)
+    fw = quantize_expert_weights_fp8(gate_up, down) if fp8 else None
+    layer = GraphedMoEDecodeLayer(None if fp8 else gate_up, None if fp8 else down, num_experts=E,
+                                  top_k=K, token_counts=(1, 4, 16), fp8_weights=fw)
+    assert layer.token_counts == (1, 4, 16)
+
+    def eager(hidden, ids, weights):
+        if fp8:
+            return b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K)
+        return b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K)
+
+    for seed, T in enumerate((4, 1, 16, 4, 5, 16, 1)):
+        hidden, ids, weights, _, _ = workloads.make_case(T, H, I, E, K, seed=300 + 3 * seed,
+                                                         routing="zipf", device="cpu")
+        hidden, ids, weights = (t.to(cuda_device) for t in (hidden, ids, weights))
+        got = layer(hidden, ids, weights, copy=True)
+        assert torch.equal(got, eager(hidden, ids, weights)), (seed, T)
+    assert layer.replays == 6 and layer.eager_calls == 1
+    assert layer.workspace.allocation_count == 1
+
+
+@pytest.mark.gpu
+def test_graphed_layer_with_the_router_inside(cuda_device) -> None:
+    """Router logits -> top-k + softmax -> layer in one graph replay."""
+
+    from b200moe import GraphedMoEDecodeLayer, b300_moe_forward, topk_routing, workloads
+
+    H, I, E, K = 256, 384, 16, 4
+    _, _, _, gate_up, down = workloads.make_case(1, H, I, E, K, std=None, device=cuda_device)
+    layer = GraphedMoEDecodeLayer(gate_up, down, num_experts=E, top_k=K, token_counts=(2, 8),
+                                  route_logits=True)
+    g = torch.Generator().manual_seed(17)
+    for T in (8, 2, 8):
+        hidden = workloads.make_hidden(T, H, seed=int(torch.randint(0, 1000, (1,), generator=g)))
+        logits = torch.randn(T, E, generator=g).to(torch.bfloat16)
+        hidden, logits = hidden.to(cuda_device), logits.to(cuda_device)
+        got = layer.forward_logits(hidden, logits, copy=True)
+        ids, weights = topk_routing(logits, K)
+        want = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K)
+        assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="router inside"):
+        layer(hidden, ids, weights)
