@@ -19,8 +19,9 @@ namespace b200moe {
 // one tcgen05 accumulator tile.
 // ---------------------------------------------------------------------------
 constexpr int kSegRows = 128;        // max token rows per segment (MMA N <= 128)
-constexpr int kSegRowsFp8 = 64;      // ... when the weights are FP8: the converted-tile buffers
-                                     // take the shared memory the longer token tiles would need
+constexpr int kSegRowsFp8 = 64;      // ... when the weights are FP8: the token operand is held as
+                                     // two to three planes per row, so 64 rows already make
+                                     // an MMA of N = 192 and a 24 KB share of every stage
 constexpr int kDownSplitMax = 8;     // max split-K factor of the down projection
 constexpr int kSchedHeaderWords = 8;
 constexpr int kSchedSegWords = 4;    // {expert, row_start, n_rows, reserved}
