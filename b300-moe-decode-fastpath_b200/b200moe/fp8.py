@@ -81,8 +81,8 @@ def quantize_rows_fp8(weights: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor
 
 
 def dequantize_rows_fp8(q: torch.Tensor, scale: torch.Tensor | None) -> torch.Tensor:
-    """E4M3 codes (+ per-row scales, or ``None`` for the bare E4M3 values) -> BF16, with the
-    byte-to-BF16 conversion the GEMM kernels use."""
+    """E4M3 codes (+ per-row scales, or ``None`` for the bare E4M3 values) -> BF16.  For
+    inspection and tests; the GEMM kernels consume the E4M3 bytes as they are."""
 
     if q.device.type != "cuda" or q.dtype != torch.uint8 or not q.is_contiguous():
         raise TypeError("dequantize_rows_fp8 needs a contiguous CUDA uint8 tensor")

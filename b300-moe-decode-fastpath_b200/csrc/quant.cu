@@ -78,8 +78,9 @@ fp8_quantize_rows_kernel(const uint4* __restrict__ w, uint4* __restrict__ q,
   }
 }
 
-// Uses the conversion of the GEMM kernels (e4m3x4_to_bf16x4), so a test over all 256 byte
-// values of this kernel checks what the GEMMs compute with.
+// Dequantisation for inspection and tests (the GEMM kernels feed the E4M3 bytes to the tensor
+// core as they are): byte -> BF16 of the same value by a bit placement and one packed multiply
+// (e4m3x4_to_bf16x4), exact for every byte value, then the row scale in FP32.
 __device__ __forceinline__ uint32_t scale_pair(uint32_t pair, float scale) {
   const float lo = bf16_bits_to_float(pair & 0xFFFFu) * scale;
   const float hi = bf16_bits_to_float(pair >> 16) * scale;

@@ -344,7 +344,8 @@ int b200moe_nvfp4_available(void);
  * scale[r] = max|w[r,:]| / 448 (1 when the row is all zero) and
  * q[r,c] = E4M3(round-to-nearest-even, saturating)(float(w[r,c]) / scale[r]).
  * b200moe_fp8_dequantize_rows writes bf16(E4M3 value * scale[r]) (scale == NULL: the bare
- * E4M3 values, which BF16 holds exactly) using the conversion the GEMM kernels use.
+ * E4M3 values, which BF16 holds exactly); it is for inspection and tests, the GEMM kernels
+ * feed the E4M3 bytes to the tensor core as they are.
  * cols must be a multiple of 16; pointers 16-byte aligned.
  */
 int b200moe_fp8_quantize_rows(const void* weights_bf16, long long rows, int cols,
