@@ -241,8 +241,8 @@ int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts
 }
 
 // Grid of the down projection.  The routing kernel picks the split-K factor from the number
-// of segments it finds, so the grid is sized for the worst case over every possible segment
-// count.  Remembered per thread: a decode loop asks for the same geometry every step.
+// of segments and rows it finds, so the grid is sized for the worst case over every possible
+// segment count and row average.  Remembered per thread: a decode loop asks for the same geometry every step.
 int down_grid(int bound, int tiles, int kblocks, int sm_count) {
   if (g_down_splits > 0) return bound * tiles * g_down_splits;
   struct Memo { int bound, tiles, kblocks, target, grid; };
@@ -252,8 +252,10 @@ int down_grid(int bound, int tiles, int kblocks, int sm_count) {
       memo.target != target) {
     int worst = bound * tiles;
     for (int segs = 1; segs <= bound; ++segs) {
-      const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks);
-      if (n > worst) worst = n;
+      for (int rows16 = 16; rows16 <= kSegRows; rows16 += 16) {
+        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks, rows16);
+        if (n > worst) worst = n;
+      }
     }
     memo = {bound, tiles, kblocks, target, worst};
   }

@@ -34,19 +34,24 @@ enum SchedWord {
 };
 
 // Split-K factor of the down projection for `units` (segment, tile) work units, each of
-// `kblocks` K blocks, when `resident` blocks fit on the GPU at once.  Cost model fitted to
-// measurements, in units of one full wave of unsplit blocks: full waves each take 1/s; the
-// last, partial wave of r blocks cannot go faster than ~0.67 of a full wave however few
-// blocks it has (a block alone on its SM streams ~33 GB/s against a fair share of ~22),
-// nor than ~0.75 once some SMs hold two blocks and others one; every extra split adds a
-// little fixed work per block.
+// `kblocks` K blocks and on average `rows16` token rows (rounded up to a multiple of 16),
+// when `resident` blocks fit on the GPU at once.  Cost model fitted to measurements, in
+// units of one full wave of unsplit blocks: full waves each take 1/s; the last, partial
+// wave of r blocks cannot go faster than ~0.67 of a full wave however few blocks it has (a
+// block alone on its SM streams ~33 GB/s against a fair share of ~22), nor than ~0.75 once
+// some SMs hold two blocks and others one; every extra split adds fixed work per block
+// (start-up, and an epilogue and token tiles that grow with the rows).
 // Above four waves of units the tail no longer matters and nothing is split.  Shared by
 // the routing kernel (which decides) and the host (which sizes the grid for the worst case).
-__host__ __device__ inline int choose_down_splits(int units, int resident, int kblocks) {
+__host__ __device__ inline int choose_down_splits(int units, int resident, int kblocks,
+                                                  int rows16) {
   if (units <= 0 || units >= 4 * resident) return 1;
   int max_splits = kblocks / 4;
   if (max_splits > kDownSplitMax) max_splits = kDownSplitMax;
   if (max_splits < 1) max_splits = 1;
+  // start-up and drain of a block cost about as much as streaming 4.7 K blocks; the
+  // epilogue and the token tiles add about one more per 16 rows
+  const float fixed = 4.7f + (float)(rows16 - 16) * (1.0f / 16.0f);
   int splits = 1;
   float best = 3.0e38f;
   for (int s = 1; s <= max_splits; ++s) {
@@ -60,13 +65,22 @@ __host__ __device__ inline int choose_down_splits(int units, int resident, int k
       if (tail < floor_) tail = floor_;
     }
     float cost = ((float)full + tail) / (float)s;
-    cost *= 1.0f + 1.5f * (float)s / (float)kblocks;
+    cost *= 1.0f + fixed * (float)s / (float)kblocks;
     if (cost < best * 0.995f) {
       best = cost;
       splits = s;
     }
   }
   return splits;
+}
+
+// Average rows per segment, rounded up to a multiple of 16 and capped at 128: the argument
+// of the cost model above.
+__host__ __device__ inline int rows16_of(int rows, int segments) {
+  if (segments <= 0) return 16;
+  int avg = (rows + segments - 1) / segments;
+  avg = (avg + 15) / 16 * 16;
+  return avg < 16 ? 16 : (avg > 128 ? 128 : avg);
 }
 
 constexpr size_t kScratchAlign = 256;

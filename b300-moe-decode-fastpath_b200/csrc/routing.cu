@@ -163,7 +163,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     if (target_ctas < 0) {
       splits = -target_ctas;  // forced by the caller (tuning)
     } else {
-      splits = choose_down_splits(units, target_ctas, down_kblocks);
+      splits = choose_down_splits(units, target_ctas, down_kblocks, rows16_of(n_valid, n_seg));
     }
     splits = max(1, min(splits, kDownSplitMax));
     splits = min(splits, max(1, down_kblocks));
