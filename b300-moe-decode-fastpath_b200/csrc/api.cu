@@ -2,6 +2,7 @@
 // argument checks, TMA tensor-map encoding, grid sizing and kernel launches.
 // Host code here never allocates device memory, never synchronises and never
 // reads device memory.
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -246,20 +247,29 @@ int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts
 int down_grid(int bound, int tiles, int kblocks, int sm_count) {
   if (g_down_splits > 0) return bound * tiles * g_down_splits;
   struct Memo { int bound, tiles, kblocks, target, grid; };
-  static thread_local Memo memo = {0, 0, 0, 0, 0};
+  constexpr int kMemo = 16;  // a decode loop cycles through a handful of token counts
+  static thread_local Memo memo[kMemo] = {};
+  static thread_local int next = 0;
   const int target = down_target(sm_count);
-  if (memo.bound != bound || memo.tiles != tiles || memo.kblocks != kblocks ||
-      memo.target != target) {
-    int worst = bound * tiles;
-    for (int segs = 1; segs <= bound; ++segs) {
-      for (int rows16 = 16; rows16 <= kSegRows; rows16 += 16) {
-        const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks, rows16);
-        if (n > worst) worst = n;
-      }
-    }
-    memo = {bound, tiles, kblocks, target, worst};
+  for (int i = 0; i < kMemo; ++i) {
+    const Memo& m = memo[i];
+    if (m.grid > 0 && m.bound == bound && m.tiles == tiles && m.kblocks == kblocks &&
+        m.target == target)
+      return m.grid;
   }
-  return memo.grid;
+  int worst = bound * tiles;
+  // the model never splits at or above four waves of units: segment counts beyond that
+  // cannot raise the bound above bound * tiles
+  const int last = std::min(bound, 4 * target / (tiles > 0 ? tiles : 1) + 1);
+  for (int segs = 1; segs <= last; ++segs) {
+    for (int rows16 = 16; rows16 <= kSegRows; rows16 += 16) {
+      const int n = segs * tiles * choose_down_splits(segs * tiles, target, kblocks, rows16);
+      if (n > worst) worst = n;
+    }
+  }
+  memo[next] = {bound, tiles, kblocks, target, worst};
+  next = (next + 1) % kMemo;
+  return worst;
 }
 
 int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
