@@ -344,8 +344,8 @@ def b300_moe_forward_pinned(
     hidden_states: torch.Tensor,
     expert_indices: torch.Tensor,
     expert_weights: torch.Tensor,
-    gate_up_weight: torch.Tensor,
-    down_weight: torch.Tensor,
+    gate_up_weight: torch.Tensor | None,
+    down_weight: torch.Tensor | None,
     *,
     num_experts: int,
     top_k: int,
