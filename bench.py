@@ -1043,6 +1043,12 @@ def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
         return None
     from b200moe import workloads
 
+    # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm runs on rank 0 alone and is
+    # meant to use all the host cores the process may run on
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     gate_up, down = workloads.make_expert_weights(EXPERTS, HIDDEN, INTER, seed=1236, std=0.02,
                                                   device="cpu")
     cases = {}
