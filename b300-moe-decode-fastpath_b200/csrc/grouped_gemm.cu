@@ -152,18 +152,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       pdl_wait();  // this grid was started early: the schedule may still be in the making
       waited = true;
     }
-    const int n_seg = p.sched[kSchedNumSegments];
+    // header {segments, active, valid rows, splits} and the segment entry are 16 bytes each;
+    // gate+up knows its segment index without the header, so both loads go out together
+    // (the schedule array is sized for every segment index a block of this grid can have)
+    const int4 header = *reinterpret_cast<const int4*>(p.sched);
+    const int n_seg = header.x;
     if (!kGateUp) {
-      n_split = p.sched[kSchedDownSplits];
+      n_split = header.w;
       split = unit % n_split;
       unit /= n_split;
     }
     const int seg = unit / p.m_tiles;
+    const int4 entry = *reinterpret_cast<const int4*>(p.sched + kSchedHeaderWords +
+                                                       kSchedSegWords * seg);
     if (seg >= n_seg) return;
-    const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
-    expert = seg_words[0];
-    row_start = seg_words[1];
-    n_rows = seg_words[2];
+    expert = entry.x;
+    row_start = entry.y;
+    n_rows = entry.z;
   }
   const int tile = unit % p.m_tiles;
   const int n_mma = (n_rows + 15) & ~15;  // accumulator columns: 16..128

@@ -84,18 +84,22 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   // ---- this block's unit (the schedule is final before this grid can start) ----------
   int unit = blockIdx.x;
   int split = 0, n_split = 1;
-  const int n_seg = p.sched[kSchedNumSegments];
+  // header {segments, active, valid rows, splits} and the segment entry are 16 bytes each;
+  // gate+up knows its segment index without the header, so both loads go out together
+  const int4 header = *reinterpret_cast<const int4*>(p.sched);
+  const int n_seg = header.x;
   if (!kGateUp) {
-    n_split = p.sched[kSchedDownSplits];
+    n_split = header.w;
     split = unit % n_split;
     unit /= n_split;
   }
   const int seg = unit / p.m_tiles;
+  const int4 entry = *reinterpret_cast<const int4*>(p.sched + kSchedHeaderWords +
+                                                     kSchedSegWords * seg);
   if (seg >= n_seg) return;
-  const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * seg;
-  const int expert = seg_words[0];
-  const int row_start = seg_words[1];
-  const int n_rows = seg_words[2];
+  const int expert = entry.x;
+  const int row_start = entry.y;
+  const int n_rows = entry.z;
   const int tile = unit % p.m_tiles;
   const int n_mma = (n_rows + 15) & ~15;  // accumulator columns per plane: 16..64
   trace_start(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
