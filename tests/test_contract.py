@@ -227,3 +227,16 @@ def test_fp8_weight_container_reports_its_geometry() -> None:
     _, _, _, fw = _fp8_inputs(E=4, H=32, I=48)
     assert (fw.num_experts, fw.hidden_size, fw.intermediate_size) == (4, 32, 48)
     assert fw.nbytes == 4 * (2 * 48 * 32 + 32 * 48) + 4 * 4 * (2 * 48 + 32)
+
+
+def test_graphed_layer_rejects_bad_construction_on_the_host() -> None:
+    from b200moe import GraphedMoEDecodeLayer
+
+    gate_up = torch.zeros(4, 96, 32, dtype=torch.bfloat16)
+    down = torch.zeros(4, 32, 48, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="requires CUDA weights"):
+        GraphedMoEDecodeLayer(gate_up, down, num_experts=4, top_k=2)
+    with pytest.raises(ValueError, match="pass gate_up_weight and down_weight"):
+        GraphedMoEDecodeLayer(None, None, num_experts=4, top_k=2)
+    with pytest.raises(TypeError, match="Fp8ExpertWeights"):
+        GraphedMoEDecodeLayer(None, None, num_experts=4, top_k=2, fp8_weights=(gate_up, down))
