@@ -16,7 +16,7 @@ from pathlib import Path
 from typing import Mapping
 
 LIBRARY_NAME = "libb200moe.so"
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 STATUS_BAD_EXPERT_ID = 0x1
 STATUS_PIPE_TIMEOUT = 0x2
@@ -26,13 +26,15 @@ FLAG_PDL = 0x1
 FLAG_LOCAL_EXPERTS = 0x2
 FLAG_F32_OUTPUT = 0x4
 FLAG_FP8_WEIGHTS = 0x8
+FLAG_HOST_IO = 0x10
+FLAG_SKIP_COMBINE = 0x20
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
 TUNE_STAGE_KB = 1
 TUNE_L2_PROMOTION = 2
 TUNE_EVICT_FIRST = 3
-TUNE_EARLY_START = 4
+TUNE_SMALL_CALL_MAX = 4
 TUNE_DOWN_TARGET = 5
 TUNE_DOWN_SPLITS = 6
 TUNE_FP8_SEG_ROWS = 7
@@ -53,6 +55,7 @@ EXPORTS = (
     "b200moe_dispatch_scratch_bytes",
     "b200moe_combine_bf16",
     "b200moe_ep_reduce",
+    "b200moe_ep_combine_reduce",
     "b200moe_ep_push",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
@@ -118,6 +121,8 @@ class B200MoeEpReduceArgs(ctypes.Structure):
         ("output", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
+        ("first_token", ctypes.c_int32),
+        ("block_counter", ctypes.c_void_p),
     ]
 
 
@@ -183,6 +188,9 @@ def _declare(lib: ctypes.CDLL) -> None:
                                                    ctypes.POINTER(ctypes.c_size_t)]
     lib.b200moe_ep_reduce.restype = ctypes.c_int
     lib.b200moe_ep_reduce.argtypes = [ctypes.POINTER(B200MoeEpReduceArgs), ctypes.c_void_p]
+    lib.b200moe_ep_combine_reduce.restype = ctypes.c_int
+    lib.b200moe_ep_combine_reduce.argtypes = [args_p, ctypes.POINTER(B200MoeEpReduceArgs),
+                                              ctypes.c_void_p]
     lib.b200moe_combine_bf16.restype = ctypes.c_int
     lib.b200moe_combine_bf16.argtypes = [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,

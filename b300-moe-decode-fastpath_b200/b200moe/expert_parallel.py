@@ -18,11 +18,13 @@ One forward:
    stream only the local active experts' weights; the combine kernel stores
    unrounded FP32 sums of the local assignments (``B200MOE_FLAG_F32_OUTPUT``).
 3. *Combine.*  The FP32 partial outputs are summed across ranks and rounded to
-   BF16 once.  ``transport="p2p"`` does this in one kernel of this library over
-   NVLink peer memory (``b200moe_ep_reduce``: publish a flag, bounded wait for the
-   peers' flags, plain peer loads of every rank's partial rows, fixed rank-order
-   sum); ``transport="nccl"`` is the unfused baseline (all-reduce, then a cast).
-   ``sharded`` callers keep their own rows.
+   BF16 once.  ``transport="p2p"`` does the local combine and the cross-rank sum
+   in one kernel of this library over NVLink peer memory
+   (``b200moe_ep_combine_reduce``: weighted sum of the rank's rows, store to the
+   rank's peer-mapped buffer, publish a flag, bounded wait for the peers' flags,
+   plain peer loads of the partial rows of the ranks that own an expert of the
+   token, fixed rank-order sum); ``transport="nccl"`` is the unfused baseline
+   (combine kernel, all-reduce, cast).  ``sharded`` callers keep their own rows.
 
 Global routing metadata (bit-exact against a single-GPU run) is assembled from
 the ranks' local tensors by :meth:`ExpertParallelMoE.global_routing`.
@@ -73,9 +75,13 @@ class ExpertParallelMoE:
         use_pdl: bool = True,
         transport: str = "nccl",
         fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
+        wait_limit_us: int = 0,
     ) -> None:
         """``fp8_scales = (gate_up_scale [E_local, 2I], down_scale [E_local, H])`` marks the two
-        weight tensors as E4M3 codes (uint8) of the FP8-weight path (``b200moe.fp8``)."""
+        weight tensors as E4M3 codes (uint8) of the FP8-weight path (``b200moe.fp8``).
+        ``wait_limit_us`` bounds every device-side wait for a peer (0: one second)."""
+
+        self.wait_limit_us = int(wait_limit_us)
 
         self.fp8_scales = fp8_scales
         self.group = group
@@ -147,6 +153,8 @@ class ExpertParallelMoE:
         self._g_flags = symm_mem.empty((_lib.EP_MAX_WORLD,), dtype=torch.int32, device=device)
         self._g_flags.zero_()
         self._push_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._reduce_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._reduce_args = None
         handles = [symm_mem.rendezvous(t, group)
                    for t in (self._g_hidden, self._g_ids, self._g_weights, self._g_flags)]
         torch.cuda.synchronize(device)
@@ -194,29 +202,42 @@ class ExpertParallelMoE:
 
     def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype,
                      first_token: int = 0) -> torch.Tensor:
-        """One launch: publish, wait for the peers (bounded), add the ranks' partial outputs
-        in rank order over NVLink, round to BF16."""
+        """One launch after the down projection: this rank's combine, publish, wait for the
+        peers (bounded), add the owning ranks' partial rows in rank order over NVLink, round
+        to BF16.  ``tokens`` rows starting at ``first_token`` are returned."""
 
         assert self.workspace is not None and self.workspace.scratch is not None
         device = self.gate_up.device
         output = torch.empty(tokens, self.hidden_size, dtype=dtype, device=device)
-        args = _lib.B200MoeEpReduceArgs()
-        partial_ptrs = self._partial_ptrs[parity]
-        if first_token:
-            skip = first_token * self.hidden_size * 4
-            partial_ptrs = (ctypes.c_void_p * self.world)(*[int(p) + skip for p in partial_ptrs])
-        args.partial_ptrs = ctypes.cast(partial_ptrs, ctypes.POINTER(ctypes.c_void_p))
-        args.flag_ptrs = ctypes.cast(self._flag_ptrs, ctypes.POINTER(ctypes.c_void_p))
-        args.world, args.rank = self.world, self.rank
-        args.num_tokens, args.hidden_size = tokens, self.hidden_size
+        args = self._reduce_args
+        if args is None:
+            # everything that does not change between forwards is filled in once
+            args = _lib.B200MoeEpReduceArgs()
+            args.flag_ptrs = ctypes.cast(self._flag_ptrs, ctypes.POINTER(ctypes.c_void_p))
+            args.world, args.rank = self.world, self.rank
+            args.hidden_size = self.hidden_size
+            args.wait_limit_us = self.wait_limit_us
+            args.block_counter = self._reduce_counter.data_ptr()
+            args.flags = _lib.FLAG_PDL if self.use_pdl else 0
+            self._reduce_args = args
+        args.partial_ptrs = ctypes.cast(self._partial_ptrs[parity],
+                                        ctypes.POINTER(ctypes.c_void_p))
+        args.num_tokens, args.first_token = tokens, first_token
         args.epoch = self._epoch & 0xFFFFFFFF
-        args.wait_limit_us = 0
         args.output = output.data_ptr()
         args.status = self.workspace.scratch.data_ptr()
-        args.flags = _lib.FLAG_PDL if self.use_pdl else 0
-        code = _enqueue(_lib.load().b200moe_ep_reduce, args, device)
+        layer_args = self._last_call[0]
+        lib = _lib.load()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        if torch.cuda.current_device() == device.index:
+            code = lib.b200moe_ep_combine_reduce(ctypes.byref(layer_args), ctypes.byref(args),
+                                                 stream)
+        else:
+            with torch.cuda.device(device):
+                code = lib.b200moe_ep_combine_reduce(ctypes.byref(layer_args),
+                                                     ctypes.byref(args), stream)
         if code:
-            _lib.check(code, "b200moe_ep_reduce")
+            _lib.check(code, "b200moe_ep_combine_reduce")
         return output
 
     # ------------------------------------------------------------------ local compute
@@ -230,18 +251,19 @@ class ExpertParallelMoE:
             self._check_native_inputs(hidden, ids, weights)
             self._checked = True
         assert self.workspace is not None
-        out = None
-        if self.transport == "p2p":
-            if hidden.shape[0] > self.capacity_tokens:
-                raise ValueError(
-                    f"{hidden.shape[0]} tokens exceed the peer buffers' capacity "
-                    f"({self.capacity_tokens}); construct the layer with a larger capacity_tokens")
-            out = self._partials[self._epoch & 1][: hidden.shape[0]]
+        p2p = self.transport == "p2p"
+        if p2p and hidden.shape[0] > self.capacity_tokens:
+            raise ValueError(
+                f"{hidden.shape[0]} tokens exceed the peer buffers' capacity "
+                f"({self.capacity_tokens}); construct the layer with a larger capacity_tokens")
+        # p2p: the forward stops after the down projection; the combine happens inside the
+        # cross-rank kernel (_peer_reduce), which writes the peer-mapped partial buffer
         partial, call = local_partial_forward(
             hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
             expert_id_base=self.base, num_experts_global=self.num_experts,
-            workspace=self.workspace, use_pdl=self.use_pdl, out=out, ep_wait=ep_wait,
-            fp8_scales=self.fp8_scales,
+            workspace=self.workspace, use_pdl=self.use_pdl, ep_wait=ep_wait,
+            fp8_scales=self.fp8_scales, skip_combine=p2p,
+            ep_wait_limit_us=self.wait_limit_us,
         )
         self._last_call = call
         return partial
@@ -299,8 +321,16 @@ class ExpertParallelMoE:
         expert_weights: torch.Tensor,
         *,
         tokens: str = "replicated",
+        check_status: bool = False,
     ) -> torch.Tensor:
-        """Run the layer; returns BF16 ``[T,H]`` for the tokens this rank was given."""
+        """Run the layer; returns BF16 ``[T,H]`` for the tokens this rank was given.
+
+        A peer that does not arrive within the wait limit does not hang the call: the rows
+        that needed it come back as zeros and ``B200MOE_STATUS_PEER_TIMEOUT`` is set in the
+        workspace status word.  ``check_status=True`` reads that word after the call (one
+        synchronisation) and raises ``RuntimeError``; without it, call
+        ``self.workspace.raise_for_status()`` before the next forward, whose first kernel
+        clears the word."""
 
         if tokens not in ("replicated", "sharded"):
             raise ValueError("tokens must be 'replicated' or 'sharded'")
@@ -330,12 +360,17 @@ class ExpertParallelMoE:
             # a sharded caller only needs its own rows: reduce that slice of every partial
             first = self.rank * local_tokens if sharded else 0
             rows = local_tokens if sharded else hidden_all.shape[0]
-            return self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first)
+            output = self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first)
+            if check_status:
+                self.workspace.raise_for_status()
+            return output
         if self.world > 1:
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         output = partial.to(hidden_states.dtype)
         if sharded:
             output = output[self.rank * local_tokens:(self.rank + 1) * local_tokens]
+        if check_status and self.workspace is not None:
+            self.workspace.raise_for_status()
         return output
 
     def _all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
@@ -386,6 +421,8 @@ def local_partial_forward(
     out: torch.Tensor | None = None,
     ep_wait: tuple[int, int, int] | None = None,
     fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
+    skip_combine: bool = False,
+    ep_wait_limit_us: int = 0,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -393,6 +430,8 @@ def local_partial_forward(
     ``ids`` are GLOBAL expert ids; other ranks' assignments are dropped by the routing
     kernel (``reverse_mapping == -1``).  Returns the partial output and the bound native
     call (argument struct plus the tensors it points to) for per-stage re-runs.
+    ``skip_combine`` stops after the down projection (no partial output is produced; the
+    caller runs ``b200moe_ep_combine_reduce`` on the returned call).
     """
 
     tokens, hidden_size = hidden.shape
@@ -406,7 +445,9 @@ def local_partial_forward(
             hidden_size=hidden_size, intermediate_size=inter, device=hidden.device,
             dtype=hidden.dtype, backend="b200_bf16", quant_mode="bf16",
         )
-        if out is None:
+        if skip_combine:
+            partial = None
+        elif out is None:
             partial = torch.empty(tokens, hidden_size, dtype=torch.float32, device=hidden.device)
         else:
             if out.dtype != torch.float32 or tuple(out.shape) != (tokens, hidden_size) or \
@@ -414,6 +455,8 @@ def local_partial_forward(
                 raise ValueError("out must be a contiguous float32 [T, H] tensor")
             partial = out
         flags = _lib.FLAG_LOCAL_EXPERTS | _lib.FLAG_F32_OUTPUT
+        if skip_combine:
+            flags |= _lib.FLAG_SKIP_COMBINE
         if use_pdl:
             flags |= _lib.FLAG_PDL
         if fp8_scales is not None:
@@ -427,6 +470,7 @@ def local_partial_forward(
             # (device address of this rank's dispatch flags, world size, epoch): the routing
             # kernel waits for every rank's pushed shard before it reads ids or rows
             args.ep_wait_flags, args.ep_world, args.ep_epoch = ep_wait
+            args.ep_wait_limit_us = ep_wait_limit_us
         code = _enqueue(_lib.load().b200moe_forward, args, hidden.device)
         if code:
             _lib.check(code, "b200moe_forward (expert-parallel rank)")

@@ -93,7 +93,7 @@ def _native_args(
     down_weight: torch.Tensor,
     shape: RoutedMoEShape,
     workspace: B300MoEWorkspace,
-    output: torch.Tensor,
+    output: torch.Tensor | None,
     flags: int,
     expert_id_base: int = 0,
 ) -> _lib.B200MoeArgs:
@@ -150,7 +150,7 @@ def _native_args(
     args.expert_indices = expert_indices.data_ptr()
     args.expert_weights = expert_weights.data_ptr()
     args.num_tokens = shape.num_tokens
-    args.output = output.data_ptr()
+    args.output = output.data_ptr() if output is not None else None
     args.flags = flags
     args.expert_id_base = expert_id_base
     args.ep_wait_flags = None  # expert-parallel callers set these after this call
@@ -267,9 +267,8 @@ def b300_moe_forward(
         )
     if backend == "torch":
         raise RuntimeError(
-            "backend='torch' is the reference oracle (oracle/moe_oracle.py in this "
-            "repository) and is not an execution path of this library; there is no "
-            "CPU or PyTorch fallback"
+            "backend='torch' is not an execution path of this library: it runs the sm_100a "
+            "kernels only and has no CPU or PyTorch fallback; use 'cutlass_bf16' or 'b200_bf16'"
         )
 
     build_info = _resolve_native_backend(
@@ -322,12 +321,19 @@ def b300_moe_forward(
                 "shape_signature": active.shape_signature,
             }
             metadata["build"] = dict(build_info)
+            # The count of experts with rows is an int, as the reference reports it
+            # (b300_moe.py:753-759); reading it waits for the routing kernel, which only a
+            # caller that asked for metadata pays.  Inside a graph capture nothing can be
+            # read back, so it stays None there.
+            active_experts = None
+            if not torch.cuda.is_current_stream_capturing():
+                active_experts = int((metadata["expert_counts"] > 0).sum())
             metadata["gemm_dispatch"] = {
                 "policy": gemm_policy,
                 "gate_up_strategy": GEMM_STRATEGY,
                 "down_strategy": GEMM_STRATEGY,
                 "total_rows": shape.num_assignments,
-                "active_experts": None,
+                "active_experts": active_experts,
             }
         active._record_use()
         if check_status:
@@ -404,7 +410,8 @@ def b300_moe_forward_pinned(
             device=device, dtype=hidden_states.dtype, backend="b200_bf16", quant_mode="bf16",
         )
         args = _native_args(hidden_states, expert_indices, expert_weights, gate_up_weight,
-                            down_weight, shape, workspace, out, _lib.FLAG_PDL if use_pdl else 0)
+                            down_weight, shape, workspace, out,
+                            _lib.FLAG_HOST_IO | (_lib.FLAG_PDL if use_pdl else 0))
         code = _enqueue(_lib.load().b200moe_forward, args, device)
         if code:
             _lib.check(code, "b200moe_forward")
@@ -449,7 +456,7 @@ def _forward_pinned_fp8(hidden_states, expert_indices, expert_weights, fw, num_e
             hidden_size=shape.hidden_size, intermediate_size=shape.intermediate_size,
             device=device, dtype=hidden_states.dtype, backend="b200_bf16", quant_mode="bf16",
         )
-        flags = _lib.FLAG_FP8_WEIGHTS | (_lib.FLAG_PDL if use_pdl else 0)
+        flags = _lib.FLAG_FP8_WEIGHTS | _lib.FLAG_HOST_IO | (_lib.FLAG_PDL if use_pdl else 0)
         args = _native_args(hidden_states, expert_indices, expert_weights, fw.gate_up_q,
                             fw.down_q, shape, workspace, out, flags)
         args.gate_up_scale = fw.gate_up_scale.data_ptr()

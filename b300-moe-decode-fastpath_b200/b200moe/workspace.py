@@ -154,7 +154,9 @@ class B300MoEWorkspace:
         """Device timeline of the last forward (synchronises): for each kernel the time its
         first block started and its last block finished, in microseconds after the start of
         the routing kernel, from ``%globaltimer`` stamps the kernels leave in the scratch
-        region.  ``*_first_data`` is when block 0 of a GEMM saw its first operands arrive."""
+        region.  ``*_first_data`` is when block 0 of a GEMM saw its first operands arrive.
+        A forward in small-call order starts with the gate+up kernel, whose times are then
+        negative or near zero, and has no ``gather`` entry."""
 
         if self._scratch is None:
             return {}

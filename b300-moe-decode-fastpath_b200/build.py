@@ -2,7 +2,7 @@
 
     python b300-moe-decode-fastpath_b200/build.py [--force] [--verbose]
 
-The library has no Python, PyTorch, CUTLASS or pybind dependency: four `.cu`
+The library has no Python, PyTorch, CUTLASS or pybind dependency: eight `.cu`
 files, the CUDA runtime (static) and nothing else.  Exactly one `-gencode` is
 passed, like the reference's single-architecture build
 (fastpath/build.py:52-57, setup.py:49-54), but for `sm_100a`.

@@ -21,7 +21,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
-                           unsigned long long wait_limit_ns, cudaStream_t stream);
+                           unsigned long long wait_limit_ns, bool after_gate_up, bool pdl,
+                           void* zero_rows, int zero_row_vecs, cudaStream_t stream);
 cudaError_t launch_ep_push(const void* hidden, const int64_t* ids, const void* weights,
                            void* const* hidden_dst, void* const* ids_dst,
                            void* const* weights_dst, void* const* flag_ptrs,
@@ -35,31 +36,32 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
                                   int down_kblocks, int target_ctas, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
                           int num_assign, int num_tokens, int top_k, int hidden_size,
-                          bool early_trigger, unsigned long long* trace, bool pdl,
-                          cudaStream_t stream);
+                          unsigned long long* trace, bool pdl, cudaStream_t stream);
 cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
                            const float* partials, const int32_t* sched, void* out,
                            void* expert_out, int num_tokens, int top_k, int hidden_size,
                            size_t slice_elems, bool f32_out, unsigned long long* trace, bool pdl,
                            cudaStream_t stream);
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
-                           const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
-                           int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
-                           int num_assign, int num_experts, int id_base, int top_k,
-                           const CUtensorMap* map_hidden, int sm_count, bool pdl,
-                           cudaStream_t stream);
+                           const CUtensorMap* map_hidden, const int32_t* sched, int sched_cap,
+                           uint32_t* status, void* act_hi, void* act_lo, int inter, int hidden,
+                           int rows_cap, int grid, const SmallCall* small, int sm_count,
+                           bool pdl, cudaStream_t stream);
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
-                        const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
-                        float* partials, int hidden, int inter, int rows_cap, int grid,
-                        int sm_count, bool pdl, cudaStream_t stream);
+                        const CUtensorMap& map_lo, const int32_t* sched, int sched_cap,
+                        uint32_t* status, float* partials, int hidden, int inter, int rows_cap,
+                        int grid, const SmallCall* small, int sm_count, bool pdl,
+                        cudaStream_t stream);
 
 cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
-                               const int32_t* sched, uint32_t* status, void* act_hi,
-                               void* act_lo, uint32_t* act_amax, const float* row_scale,
+                               const int32_t* sched, int sched_cap, uint32_t* status,
+                               void* act_hi, void* act_lo, uint32_t* act_amax,
+                               const float* row_scale,
                                const float* token_scale, int inter, int hidden, int rows_cap,
                                int grid, int sm_count, bool pdl, cudaStream_t stream);
 cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
-                            const int32_t* sched, uint32_t* status, float* partials,
+                            const int32_t* sched, int sched_cap, uint32_t* status,
+                            float* partials,
                             const float* row_scale, const float* token_scale, int hidden,
                             int inter, int rows_cap, int grid, int sm_count, bool pdl,
                             cudaStream_t stream);
@@ -85,13 +87,23 @@ cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_
                              unsigned long long wait_limit_ns, void* output, uint32_t* status,
                              bool pdl, cudaStream_t stream);
 
+cudaError_t launch_ep_combine_reduce(const int64_t* reverse_mapping, const void* weights,
+                                     const float* slices, const int32_t* sched,
+                                     void* expert_out, const int64_t* ids,
+                                     const void* const* partial_ptrs, void* const* flag_ptrs,
+                                     unsigned int* block_counter, void* output,
+                                     uint32_t* status, size_t slice_elems, int num_tokens,
+                                     int top_k, int hidden, int experts_per_rank, int world,
+                                     int rank, int first_token, int out_tokens, uint32_t epoch,
+                                     unsigned long long wait_limit_ns, unsigned long long* trace,
+                                     bool pdl, cudaStream_t stream);
+
 cudaError_t launch_router_topk(const void* logits, bool logits_f32, int num_tokens,
                                int num_experts, int top_k, int64_t* ids, void* weights_bf16,
                                float* weights_f32, cudaStream_t stream);
 
 extern int g_gemm_stage_kb;
 extern int g_gemm_evict_first;
-extern int g_early_mode;
 
 namespace {
 
@@ -100,6 +112,7 @@ int g_down_target = 0;   // blocks the down projection's split-K aims at (0: 2 p
 
 int g_fp8_seg_rows = kSegRowsFp8;  // segment length of the FP8-weight path (16, 32, 48 or 64)
 int g_down_splits = 0;   // forced split-K factor of the down projection (0: chosen on the device)
+int g_small_call_max = kSmallCallMaxAssign;  // most assignments that run in small-call order (0: never)
 
 int down_target(int sm_count) { return g_down_target > 0 ? g_down_target : 2 * sm_count; }
 // what the routing kernel receives: the target, or minus the forced split factor
@@ -272,8 +285,9 @@ int down_grid(int bound, int tiles, int kblocks, int sm_count) {
   return worst;
 }
 
+// `after_gate_up`: the forward runs in small-call order (see b200moe_forward).
 int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
-               cudaStream_t stream) {
+               cudaStream_t stream, bool after_gate_up = false, bool pdl = false) {
   const bool local = (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) != 0;
   return (int)launch_routing(a->expert_indices, a->expert_weights, a->num_tokens * a->top_k,
                              a->top_k, a->num_experts, a->expert_counts, a->expert_offsets,
@@ -289,45 +303,43 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              a->ep_epoch,
                              (a->ep_wait_limit_us ? (unsigned long long)a->ep_wait_limit_us
                                                   : 1000000ull) * 1000ull,
+                             after_gate_up, pdl,
+                             after_gate_up ? a->permuted_hidden : nullptr, a->hidden_size / 8,
                              stream);
 }
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
-               int hidden, int inter, void* act_hi, const Scratch& s, const int64_t* ids,
-               int id_base, int top_k, const void* hidden_states, const DeviceInfo& dev, bool pdl,
-               cudaStream_t stream) {
-  CUtensorMap map_w, map_x;
+               int hidden, int inter, void* act_hi, const Scratch& s, const SmallCall* small,
+               const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
+  CUtensorMap map_w, map_x, map_hidden;
   {
     const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
-    const uint32_t box[4] = {64, 128, 2, 1};
+    const uint32_t box[4] = {64, 128, 2, 1};  // 128 gate rows + the 128 matching up rows
     int rc = encode_bf16_map(&map_w, w, 4, dims, box);
     if (rc) return rc;
   }
+  const int grid = segment_bound(assignments, experts) * tiles128(inter);
   {
     const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)rows_cap};
     const uint32_t box[2] = {64, 16};
     int rc = encode_bf16_map(&map_x, x, 2, dims, box);
     if (rc) return rc;
   }
-  const int grid = segment_bound(assignments, experts) * tiles128(inter);
-  // hidden_states [T,H] with one-row boxes: blocks with few rows fetch them from here
-  CUtensorMap map_hidden;
-  const bool have_hidden = g_early_mode >= 2 && ids != nullptr && hidden_states != nullptr &&
-                           aligned16(hidden_states);
-  if (have_hidden) {
-    const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)(assignments / top_k)};
+  if (small) {
+    // hidden_states [T,H] with one-row boxes: the blocks fetch their token rows from here
+    const uint64_t dims[2] = {(uint64_t)hidden, (uint64_t)(assignments / small->top_k)};
     const uint32_t box[2] = {64, 1};
-    int rc = encode_bf16_map(&map_hidden, hidden_states, 2, dims, box);
+    int rc = encode_bf16_map(&map_hidden, small->hidden, 2, dims, box);
     if (rc) return rc;
   }
-  return (int)launch_gate_up(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, inter, hidden,
-                             rows_cap, grid, ids, assignments, experts, id_base, top_k,
-                             have_hidden ? &map_hidden : nullptr, dev.sm_count, pdl, stream);
+  return (int)launch_gate_up(map_w, map_x, small ? &map_hidden : nullptr, s.sched,
+                             max_segments(rows_cap, experts), s.status, act_hi, s.act_lo, inter,
+                             hidden, rows_cap, grid, small, dev.sm_count, pdl, stream);
 }
 
 int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, int experts,
-            int hidden, int inter, const Scratch& s, const DeviceInfo& dev, bool pdl,
-            cudaStream_t stream) {
+            int hidden, int inter, const Scratch& s, const SmallCall* small,
+            const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
   CUtensorMap map_w, map_hi, map_lo;
   {
     const uint64_t dims[3] = {(uint64_t)inter, (uint64_t)hidden, (uint64_t)experts};
@@ -343,8 +355,9 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
   if (rc) return rc;
   const int grid = down_grid(segment_bound(assignments, experts), tiles128(hidden),
                              (inter + 63) / 64, dev.sm_count);
-  return (int)launch_down(map_w, map_hi, map_lo, s.sched, s.status, s.partials, hidden, inter,
-                          rows_cap, grid, dev.sm_count, pdl, stream);
+  return (int)launch_down(map_w, map_hi, map_lo, s.sched, max_segments(rows_cap, experts),
+                          s.status, s.partials, hidden, inter, rows_cap, grid, small,
+                          dev.sm_count, pdl, stream);
 }
 
 // FP8 weights: one-byte tensor maps of the weights and of the token planes.
@@ -368,7 +381,8 @@ int do_gate_up_fp8(const void* w, const float* row_scale, int rows_cap, int assi
   int rc = encode_plane_map(&map_x, s.q_planes, hidden, rows_cap, kFp8PlanesHidden);
   if (rc) return rc;
   const int grid = segment_bound(assignments, experts, g_fp8_seg_rows) * tiles128(inter);
-  return (int)launch_gate_up_fp8(map_w, map_x, s.sched, s.status, act_hi, s.act_lo, s.a_amax,
+  return (int)launch_gate_up_fp8(map_w, map_x, s.sched, max_segments(rows_cap, experts),
+                                 s.status, act_hi, s.act_lo, s.a_amax,
                                  row_scale, s.x_scale, inter, hidden, rows_cap, grid,
                                  dev.sm_count, pdl, stream);
 }
@@ -391,7 +405,8 @@ int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int r
   rc = (int)launch_act_planes_fp8(act_hi, s.act_lo, s.a_amax, s.q_planes, s.a_scale, assignments,
                                   inter, rows_cap, pdl, stream);
   if (rc) return rc;
-  return (int)launch_down_fp8(map_w, map_act, s.sched, s.status, s.partials, row_scale,
+  return (int)launch_down_fp8(map_w, map_act, s.sched, max_segments(rows_cap, experts),
+                              s.status, s.partials, row_scale,
                               s.a_scale, hidden, inter, rows_cap, grid, dev.sm_count, pdl,
                               stream);
 }
@@ -430,11 +445,33 @@ int prepare(const B200MoeArgs* a, void* stream, Ctx* c) {
   return 0;
 }
 
-int stage_routing(const B200MoeArgs* a, const Ctx& c) {
+int stage_routing(const B200MoeArgs* a, const Ctx& c, bool after_gate_up = false,
+                  bool pdl = false) {
   if (!a->expert_indices || !a->expert_counts || !a->expert_offsets || !a->expert_offsets_i32 ||
       !a->permutation || !a->reverse_mapping)
     return B200MOE_E_NULL;
-  return do_routing(a, c.s, c.dev, c.stream);
+  return do_routing(a, c.s, c.dev, c.stream, after_gate_up, pdl);
+}
+
+// Small-call order applies to BF16 weights, device-resident per-step tensors and ids that
+// are in place when the forward is enqueued (not pushed by peers during it).
+bool small_call(const B200MoeArgs* a, int assignments) {
+  int most = g_small_call_max < kSmallCallMaxAssign ? g_small_call_max : kSmallCallMaxAssign;
+  return assignments <= most && !fp8_weights(a) && a->ep_wait_flags == nullptr &&
+         (a->flags & B200MOE_FLAG_HOST_IO) == 0;
+}
+
+SmallCall small_call_of(const B200MoeArgs* a, const Ctx& c) {
+  SmallCall sc;
+  sc.ids = a->expert_indices;
+  sc.num_assign = c.assignments;
+  sc.num_experts = a->num_experts;
+  sc.id_base = (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) ? a->expert_id_base : 0;
+  sc.top_k = a->top_k;
+  sc.hidden = a->hidden_states;
+  sc.permuted_hidden = a->permuted_hidden;
+  sc.split_request = down_split_request(c.dev.sm_count);
+  return sc;
 }
 
 int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
@@ -446,11 +483,10 @@ int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
                                   a->num_tokens, a->top_k, a->hidden_size, a->rows_cap,
                                   trace_of(c.s), pdl, c.stream);
   return (int)launch_gather(a->hidden_states, a->permutation, a->permuted_hidden, c.assignments,
-                            a->num_tokens, a->top_k, a->hidden_size, g_early_mode >= 1,
-                            trace_of(c.s), pdl, c.stream);
+                            a->num_tokens, a->top_k, a->hidden_size, trace_of(c.s), pdl, c.stream);
 }
 
-int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr) {
   if (!a->permuted_hidden || !a->gate_up_weight || !a->swiglu_output) return B200MOE_E_NULL;
   if (!aligned16(a->permuted_hidden) || !aligned16(a->gate_up_weight) ||
       !aligned16(a->swiglu_output))
@@ -464,12 +500,10 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   }
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
-                    a->ep_wait_flags ? nullptr : a->expert_indices,
-                    (a->flags & B200MOE_FLAG_LOCAL_EXPERTS) ? a->expert_id_base : 0, a->top_k,
-                    a->hidden_states, c.dev, pdl, c.stream);
+                    small, c.dev, pdl, c.stream);
 }
 
-int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {
+int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr) {
   if (!a->swiglu_output || !a->down_weight) return B200MOE_E_NULL;
   if (!aligned16(a->swiglu_output) || !aligned16(a->down_weight)) return B200MOE_E_ALIGN;
   if (fp8_weights(a)) {
@@ -480,7 +514,7 @@ int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl) {
                        c.dev, pdl, c.stream);
   }
   return do_down(a->swiglu_output, a->down_weight, a->rows_cap, c.assignments, a->num_experts,
-                 a->hidden_size, a->intermediate_size, c.s, c.dev, pdl, c.stream);
+                 a->hidden_size, a->intermediate_size, c.s, small, c.dev, pdl, c.stream);
 }
 
 int stage_combine(const B200MoeArgs* a, const Ctx& c, bool pdl) {
@@ -623,9 +657,9 @@ int b200moe_tune(int knob, int value) {
       if (value < 16 || value > kSegRowsFp8 || value % 16) return B200MOE_E_SHAPE;
       g_fp8_seg_rows = value;
       return 0;
-    case B200MOE_TUNE_EARLY_START:
-      if (value < 0 || value > 2) return B200MOE_E_SHAPE;
-      g_early_mode = value;
+    case B200MOE_TUNE_SMALL_CALL_MAX:
+      if (value < 0 || value > kSmallCallMaxAssign) return B200MOE_E_SHAPE;
+      g_small_call_max = value;
       return 0;
     default:
       return B200MOE_E_SHAPE;
@@ -702,6 +736,54 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
                                a->hidden_size, a->epoch, limit_ns, a->output, a->status,
                                (a->flags & B200MOE_FLAG_PDL) != 0,
                                static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_combine_reduce(const B200MoeArgs* a, const B200MoeEpReduceArgs* e, void* stream) {
+  if (!e || !e->partial_ptrs || !e->flag_ptrs || !e->output || !e->block_counter)
+    return B200MOE_E_NULL;
+  Ctx c;
+  int rc = prepare(a, stream, &c);
+  if (rc) return rc;
+  if (!a->reverse_mapping || !a->expert_weights || !a->expert_indices) return B200MOE_E_NULL;
+  if (e->world < 1 || e->world > B200MOE_EP_MAX_WORLD || e->rank < 0 || e->rank >= e->world ||
+      e->num_tokens < 1 || e->first_token < 0 ||
+      e->first_token + e->num_tokens > a->num_tokens || e->hidden_size != a->hidden_size)
+    return B200MOE_E_SHAPE;
+  if (!aligned16(e->output) || (a->expert_output && !aligned16(a->expert_output)))
+    return B200MOE_E_ALIGN;
+  for (int r = 0; r < e->world; ++r) {
+    if (!e->partial_ptrs[r] || !e->flag_ptrs[r]) return B200MOE_E_NULL;
+    if (!aligned16(e->partial_ptrs[r])) return B200MOE_E_ALIGN;
+  }
+  const unsigned long long limit_ns =
+      (e->wait_limit_us ? (unsigned long long)e->wait_limit_us : 1000000ull) * 1000ull;
+  const bool pdl = (e->flags & B200MOE_FLAG_PDL) != 0;
+  const int chunks = (a->hidden_size / 8 + 127) / 128;
+  const size_t slice_elems = (size_t)a->rows_cap * a->hidden_size;
+  // The fused kernel's blocks wait for other GPUs while the publishing block of their own
+  // grid may not have run yet, so it is used only while the whole grid is resident at once
+  // (eight 128-thread blocks per SM is well inside what an SM holds).
+  if ((long long)a->num_tokens * chunks <= 8ll * c.dev.sm_count)
+    return (int)launch_ep_combine_reduce(
+        a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched, a->expert_output,
+        a->expert_indices, e->partial_ptrs, e->flag_ptrs, e->block_counter, e->output,
+        e->status, slice_elems, a->num_tokens, a->top_k, a->hidden_size, a->num_experts,
+        e->world, e->rank, e->first_token, e->num_tokens, e->epoch, limit_ns, trace_of(c.s),
+        pdl, c.stream);
+  // Larger calls: the combine kernel writes this rank's FP32 partial output, then the
+  // reduce kernel (whose blocks never depend on blocks of their own grid) adds the ranks'.
+  rc = (int)launch_combine(a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched,
+                           const_cast<void*>(e->partial_ptrs[e->rank]), a->expert_output,
+                           a->num_tokens, a->top_k, a->hidden_size, slice_elems, true,
+                           trace_of(c.s), pdl, c.stream);
+  if (rc) return rc;
+  const void* shifted[B200MOE_EP_MAX_WORLD];
+  for (int r = 0; r < e->world; ++r)
+    shifted[r] = static_cast<const char*>(e->partial_ptrs[r]) +
+                 (size_t)e->first_token * a->hidden_size * sizeof(float);
+  return (int)launch_ep_reduce(shifted, e->flag_ptrs, e->world, e->rank, e->num_tokens,
+                               a->hidden_size, e->epoch, limit_ns, e->output, e->status, pdl,
+                               c.stream);
 }
 
 static size_t dispatch_scratch_need(int rows_cap, int experts) {
@@ -790,25 +872,35 @@ int b200moe_forward(const B200MoeArgs* a, void* stream) {
   int rc = prepare(a, stream, &c);
   if (rc) return rc;
   // All pointer checks first, so a contract error launches nothing at all.
+  const bool skip_combine = (a->flags & B200MOE_FLAG_SKIP_COMBINE) != 0;
   if (!a->hidden_states || !a->expert_indices || !a->expert_weights || !a->gate_up_weight ||
       !a->down_weight || !a->expert_counts || !a->expert_offsets || !a->expert_offsets_i32 ||
       !a->permutation || !a->reverse_mapping || !a->permuted_hidden || !a->swiglu_output ||
-      !a->output)
+      (!a->output && !skip_combine))
     return B200MOE_E_NULL;
   if (!aligned16(a->hidden_states) || !aligned16(a->gate_up_weight) ||
       !aligned16(a->down_weight) || !aligned16(a->permuted_hidden) ||
-      !aligned16(a->swiglu_output) || !aligned16(a->output) ||
+      !aligned16(a->swiglu_output) || (!skip_combine && !aligned16(a->output)) ||
       (a->expert_output && !aligned16(a->expert_output)))
     return B200MOE_E_ALIGN;
   if (fp8_weights(a)) {
     if (!a->gate_up_scale || !a->down_scale) return B200MOE_E_NULL;
     if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
   }
+  if (small_call(a, c.assignments)) {
+    // Small-call order: the gate+up GEMM first (its blocks need nothing from the routing
+    // kernel and also do the gather), the routing kernel beside it, then down and combine.
+    const SmallCall sc = small_call_of(a, c);
+    if ((rc = stage_gate_up(a, c, c.pdl, &sc))) return rc;
+    if ((rc = stage_routing(a, c, true, c.pdl))) return rc;
+    if ((rc = stage_down(a, c, c.pdl, &sc))) return rc;
+    return skip_combine ? 0 : stage_combine(a, c, c.pdl);
+  }
   if ((rc = stage_routing(a, c))) return rc;
   if ((rc = stage_gather(a, c, c.pdl))) return rc;
   if ((rc = stage_gate_up(a, c, c.pdl))) return rc;
   if ((rc = stage_down(a, c, c.pdl))) return rc;
-  return stage_combine(a, c, c.pdl);
+  return skip_combine ? 0 : stage_combine(a, c, c.pdl);
 }
 
 }  // extern "C"

@@ -83,6 +83,34 @@ __host__ __device__ inline int rows16_of(int rows, int segments) {
   return avg < 16 ? 16 : (avg > 128 ? 128 : avg);
 }
 
+// The factor the routing kernel publishes for a call with `n_seg` segments and `n_valid`
+// rows.  `request` is the number of resident blocks to aim at, or minus a forced factor.
+// One function for every place that must arrive at the same number: the routing kernel,
+// down-projection blocks that derive their unit from the expert ids, and the host.
+__host__ __device__ inline int down_splits_for(int n_seg, int n_valid, int down_tiles,
+                                               int down_kblocks, int request) {
+  int splits = request < 0 ? -request
+                           : choose_down_splits(n_seg * down_tiles, request, down_kblocks,
+                                                rows16_of(n_valid, n_seg));
+  if (splits > kDownSplitMax) splits = kDownSplitMax;
+  if (splits > down_kblocks) splits = down_kblocks;
+  return splits < 1 ? 1 : splits;
+}
+
+// Calls with at most this many assignments (T * top_k) can run in "small-call" order: one
+// warp holds every expert id of the call in its lanes, so a GEMM block finds its work unit
+// with a few warp votes instead of waiting for the routing kernel.
+constexpr int kSmallCallMaxAssign = 32;
+
+// What a GEMM launch needs to run in small-call order (host side).
+struct SmallCall {
+  const int64_t* ids;         // [num_assign] expert ids of the call
+  int num_assign, num_experts, id_base, top_k;
+  const void* hidden;         // gate+up: [T, H] rows to fetch and to copy to permuted_hidden
+  void* permuted_hidden;
+  int split_request;          // down: what the routing kernel is given
+};
+
 constexpr size_t kScratchAlign = 256;
 constexpr size_t kStatusBytes = 256;  // status word lives in the first 256 bytes
 
@@ -160,6 +188,62 @@ __device__ __forceinline__ void trace_start(unsigned long long* t, int k) {
 }
 __device__ __forceinline__ void trace_end(unsigned long long* t, int k) {
   if (t && threadIdx.x == 0) atomicMax(&t[2 * k + 1], (unsigned long long)global_timer_ns());
+}
+
+// Routing of a small call (num_assign <= 32) held in the lanes of one warp: lane a owns
+// assignment a.  Restates the routing kernel's rules for this size -- ids outside
+// [id_base, id_base + num_experts) are dropped, every expert with rows is exactly one
+// segment, segments are ordered by expert id, rows of an expert keep increasing assignment
+// ids -- so a block that uses it agrees with the schedule the routing kernel writes.
+struct SmallRouteLane {
+  int expert;         // this lane's expert (local id), -1 when the lane has no valid assignment
+  unsigned members;   // lanes that hold the same expert
+  int rows_before;    // valid assignments whose expert id is lower = first row of this expert
+  int segs_before;    // active experts with a lower id = this expert's segment index
+  int n_seg, n_valid; // of the whole call
+};
+__device__ __forceinline__ SmallRouteLane small_route_scan(const int64_t* __restrict__ ids,
+                                                           int num_assign, int num_experts,
+                                                           int id_base) {
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  long long e64 = -1;
+  if (lane < num_assign) e64 = (long long)ids[lane] - (long long)id_base;
+  const bool valid = lane < num_assign && e64 >= 0 && e64 < (long long)num_experts;
+  SmallRouteLane r;
+  r.expert = valid ? (int)e64 : -1;
+  r.members = __match_any_sync(full, r.expert);
+  const bool first = valid && (r.members & ((1u << lane) - 1u)) == 0u;
+  const unsigned firsts = __ballot_sync(full, first);
+  r.n_valid = __popc(__ballot_sync(full, valid));
+  r.n_seg = __popc(firsts);
+  r.rows_before = 0;
+  r.segs_before = 0;
+  for (int j = 0; j < num_assign; ++j) {
+    const int ej = __shfl_sync(full, r.expert, j);
+    if (ej >= 0 && ej < r.expert) {
+      r.rows_before += 1;
+      r.segs_before += (int)((firsts >> j) & 1u);
+    }
+  }
+  return r;
+}
+// The segment with index `seg`: {expert, first row, rows, member lanes}; false when the call
+// has fewer segments.  Every lane of the warp gets the same answer.
+__device__ __forceinline__ bool small_route_pick(const SmallRouteLane& r, int seg, int& expert,
+                                                 int& row_start, int& n_rows,
+                                                 unsigned& members) {
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const bool first = r.expert >= 0 && (r.members & ((1u << lane) - 1u)) == 0u;
+  const unsigned who = __ballot_sync(full, first && r.segs_before == seg);
+  if (who == 0u) return false;
+  const int src = __ffs(who) - 1;
+  expert = __shfl_sync(full, r.expert, src);
+  row_start = __shfl_sync(full, r.rows_before, src);
+  members = __shfl_sync(full, r.members, src);
+  n_rows = __popc(members);
+  return true;
 }
 
 // Programmatic dependent launch: wait until the grids this one depends on have

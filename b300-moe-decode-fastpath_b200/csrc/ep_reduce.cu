@@ -65,14 +65,15 @@ ep_reduce_kernel(const EpReduceParams p) {
     }
   }
   __syncthreads();
-  if (!s_ready) {
-    // A peer never arrived: report it and leave the output untouched.
-    if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200MOE_STATUS_PEER_TIMEOUT);
-    return;
-  }
-
   const int token = blockIdx.x;
   const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (!s_ready) {
+    // A peer never arrived: report it; the rows read as zeros, never as stale memory.
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200MOE_STATUS_PEER_TIMEOUT);
+    if (col < p.hidden)
+      p.output[((size_t)token * p.hidden + col) >> 3] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
   if (col >= p.hidden) return;
   const size_t at = (size_t)token * p.hidden + col;
   float acc[8];
@@ -120,6 +121,222 @@ cudaError_t launch_ep_reduce(const void* const* partial_ptrs, void* const* flag_
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, ep_reduce_kernel, p);
+}
+
+// ---------------------------------------------------------------------------
+// Combine and cross-rank reduce in one kernel.  Replaces the pair "combine kernel
+// (FP32 partial output) + ep_reduce_kernel" of an expert-parallel forward:
+//
+//  1. every block computes this rank's weighted sum for its (token, 1024 columns) from the
+//     split-K slices of the down projection, exactly as the combine kernel does, keeps it
+//     in registers and -- only if this rank owns an expert of the token -- stores it to
+//     this rank's peer-mapped partial buffer;
+//  2. the block that finishes last publishes the epoch into flags[rank] of every rank;
+//  3. blocks of the tokens this rank must output wait (bounded) until every rank has
+//     published, then add the partial rows of the ranks that own an expert of the token,
+//     in rank order (their own from registers, the others with plain peer loads), and
+//     round once to BF16.  Which ranks those are follows from the token's expert ids,
+//     which every rank holds: a token routed to K experts reads at most K rows instead of
+//     `world`.
+//
+// Waiting for every rank (not only the owners) costs nothing -- a rank without work
+// publishes early -- and keeps the ranks within one forward of each other, which is what
+// makes two alternating partial buffers enough.  Blocks of one grid wait for other GPUs,
+// never for each other; the host uses this kernel only while the whole grid is resident at
+// once, so the publishing block of every rank always gets to run.
+// ---------------------------------------------------------------------------
+struct EpCombineParams {
+  const int64_t* reverse_mapping;   // [T*K] local rows, -1 for other ranks' assignments
+  const __nv_bfloat16* weights;     // [T,K]
+  const float* slices;              // [splits][rows_cap][H] of the down projection
+  const int32_t* sched;
+  uint4* expert_out;                // [rows_cap,H] bf16 or null
+  const int64_t* ids;               // [T,K] global expert ids
+  float* partial[kMaxEpWorld];      // every rank's FP32 [T,H] partial buffer
+  uint32_t* flags[kMaxEpWorld];
+  unsigned int* block_counter;      // local, zero between launches
+  uint4* output;                    // BF16 [out_tokens, H]
+  uint32_t* status;
+  size_t slice_elems;
+  int num_assign, top_k, hidden, experts_per_rank;
+  int world, rank, first_token, out_tokens;
+  uint32_t epoch;
+  unsigned long long wait_limit_ns;
+  unsigned long long* trace;
+};
+
+__global__ void __launch_bounds__(128)
+ep_combine_reduce_kernel(const EpCombineParams p) {
+  __shared__ int s_flag;
+  pdl_wait();  // the down projection of this rank has completed
+  pdl_launch_dependents();
+  trace_start(p.trace, kTraceCombine);
+  const int token = blockIdx.x;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const bool active = col < p.hidden;
+  const int splits = p.sched[kSchedDownSplits];
+
+  // ---- 1. this rank's share of the token --------------------------------------------
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  bool contributes = false;
+  unsigned owners = 0u;  // ranks that own an expert of this token
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (k >= p.top_k) break;
+    const int a = token * p.top_k + k;
+    const int64_t id = p.ids[a];
+    if (id >= 0 && id < (int64_t)p.world * p.experts_per_rank)
+      owners |= 1u << (int)(id / p.experts_per_rank);
+    const int64_t row = p.reverse_mapping[a];
+    if (row < 0 || row >= (int64_t)p.num_assign) continue;
+    contributes = true;
+    if (!active) continue;
+    const float w = __bfloat162float(p.weights[a]);
+    const float* src = p.slices + (size_t)row * p.hidden + col;
+    float v[8];
+    {
+      const float4 lo = *reinterpret_cast<const float4*>(src);
+      const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+      v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    }
+    for (int s = 1; s < splits; ++s) {
+      const float4 lo = *reinterpret_cast<const float4*>(src + (size_t)s * p.slice_elems);
+      const float4 hi = *reinterpret_cast<const float4*>(src + (size_t)s * p.slice_elems + 4);
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+    if (p.expert_out) {
+      uint4 packed;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      p.expert_out[((size_t)row * p.hidden + col) >> 3] = packed;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[i], w, acc[i]);
+  }
+  const size_t at = (size_t)token * p.hidden + col;
+  if (active && contributes) {
+    float4* o = reinterpret_cast<float4*>(p.partial[p.rank] + at);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+
+  // ---- 2. the last block of the grid publishes the epoch -----------------------------
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    s_flag = (atomicAdd(p.block_counter, 1u) == total - 1u) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_flag) {
+    if (threadIdx.x == 0) *p.block_counter = 0u;
+    if (threadIdx.x < p.world) {
+      __threadfence_system();
+      st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
+    }
+  }
+
+  // ---- 3. tokens this rank outputs ---------------------------------------------------
+  if (token < p.first_token || token >= p.first_token + p.out_tokens) return;
+  __syncthreads();
+  if (threadIdx.x == 0) s_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    const uint32_t* flag = p.flags[p.rank] + threadIdx.x;
+    const uint64_t t0 = global_timer_ns();
+    while ((int32_t)(ld_acquire_sys(flag) - p.epoch) < 0) {
+      if (global_timer_ns() - t0 > p.wait_limit_ns) {
+        s_flag = 0;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  const size_t out_at = ((size_t)(token - p.first_token) * p.hidden + col) >> 3;
+  if (!s_flag) {
+    // A peer never arrived: report it; the rows read as zeros, never as stale memory.
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200MOE_STATUS_PEER_TIMEOUT);
+    if (active) p.output[out_at] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  if (!active) return;
+  float sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kMaxEpWorld; ++r) {
+    if (r < p.world && ((owners >> r) & 1u)) {
+      if (r == p.rank) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] += acc[i];
+      } else {
+        const float4 lo = *reinterpret_cast<const float4*>(p.partial[r] + at);
+        const float4 hi = *reinterpret_cast<const float4*>(p.partial[r] + at + 4);
+        sum[0] += lo.x; sum[1] += lo.y; sum[2] += lo.z; sum[3] += lo.w;
+        sum[4] += hi.x; sum[5] += hi.y; sum[6] += hi.z; sum[7] += hi.w;
+      }
+    }
+  }
+  uint4 packed;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(sum[2 * i], sum[2 * i + 1]);
+  p.output[out_at] = packed;
+  trace_end(p.trace, kTraceCombine);
+}
+
+cudaError_t launch_ep_combine_reduce(const int64_t* reverse_mapping, const void* weights,
+                                     const float* slices, const int32_t* sched,
+                                     void* expert_out, const int64_t* ids,
+                                     const void* const* partial_ptrs, void* const* flag_ptrs,
+                                     unsigned int* block_counter, void* output,
+                                     uint32_t* status, size_t slice_elems, int num_tokens,
+                                     int top_k, int hidden, int experts_per_rank, int world,
+                                     int rank, int first_token, int out_tokens, uint32_t epoch,
+                                     unsigned long long wait_limit_ns, unsigned long long* trace,
+                                     bool pdl, cudaStream_t stream) {
+  EpCombineParams p = {};
+  p.reverse_mapping = reverse_mapping;
+  p.weights = static_cast<const __nv_bfloat16*>(weights);
+  p.slices = slices;
+  p.sched = sched;
+  p.expert_out = static_cast<uint4*>(expert_out);
+  p.ids = ids;
+  for (int r = 0; r < world; ++r) {
+    p.partial[r] = static_cast<float*>(const_cast<void*>(partial_ptrs[r]));
+    p.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  p.block_counter = block_counter;
+  p.output = static_cast<uint4*>(output);
+  p.status = status;
+  p.slice_elems = slice_elems;
+  p.num_assign = num_tokens * top_k;
+  p.top_k = top_k;
+  p.hidden = hidden;
+  p.experts_per_rank = experts_per_rank;
+  p.world = world;
+  p.rank = rank;
+  p.first_token = first_token;
+  p.out_tokens = out_tokens;
+  p.epoch = epoch;
+  p.wait_limit_ns = wait_limit_ns;
+  p.trace = trace;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_tokens, (hidden / 8 + 127) / 128);
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, ep_combine_reduce_kernel, p);
 }
 
 // ---------------------------------------------------------------------------

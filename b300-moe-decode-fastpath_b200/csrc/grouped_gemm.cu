@@ -31,6 +31,11 @@
 // activation rows, one after the other; one MMA per K step over both computes
 // W . hi and W . lo into two accumulators.  The epilogue adds them and stores FP32
 // rows into this block's split-K slice.
+//
+// A call with at most 32 assignments runs in "small-call" order: gate+up is the
+// first kernel of the forward, its blocks derive their unit from the expert ids
+// and fetch their token rows from hidden_states themselves, and the routing
+// kernel runs beside it.
 #include "common.cuh"
 
 namespace b200moe {
@@ -41,8 +46,6 @@ constexpr uint32_t kMaxStageBudget = 220u * 1024u;        // one block per SM
 constexpr int kTileM = 128;   // weight rows per unit
 constexpr int kTileK = 64;    // elements per pipeline stage along K (128 bytes)
 constexpr uint64_t kAbortDrainNs = 1000000ull;
-constexpr int kOwnRoutingMaxAssign = 2048;  // gate+up blocks derive their unit themselves up to here
-constexpr int kDirectRowsMax = 32;  // ... and fetch the token rows themselves up to this many
 
 struct GemmParams {
   const int32_t* sched;
@@ -54,10 +57,18 @@ struct GemmParams {
   int k_total;             // reduction length: H (gate+up) or I (down)
   int m_tiles;             // ceil(m_total / 128)
   int rows_cap;
-  const int64_t* ids;      // gate+up: the call's expert ids [num_assign] (or null)
+  int sched_cap;           // segment entries the schedule array holds
+  // small calls (<= kSmallCallMaxAssign assignments): every block derives its unit from
+  // the call's expert ids and does not read the schedule before its dependency wait
+  int small;
+  const int64_t* ids;      // [num_assign]
   int num_assign, num_experts, id_base, top_k;
-  int hidden_map_valid;    // gate+up: the third tensor map describes hidden_states [T,H]
-  int early_mode;          // gate+up: 0 wait for routing, 1 own routing, 2 own routing + own rows
+  int split_request;       // down: what the routing kernel is given to choose the split-K factor
+  // small gate+up: blocks load their token rows from hidden_states themselves, and the
+  // blocks of tile 0 also write them to permuted_hidden (the gather of this call)
+  const uint4* hidden;
+  uint4* permuted_hidden;
+  int hidden_vecs;         // H / 8
   unsigned long long* trace;
   uint32_t stage_budget;   // bytes of shared memory the stage ring may use
   int evict_first;         // stream the weight tiles with an L2 evict-first hint
@@ -74,9 +85,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   __shared__ __align__(8) uint64_t s_acc;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ int s_hist[B200MOE_MAX_EXPERTS];
-  __shared__ int s_unit[5];
-  __shared__ int s_tokens[kDirectRowsMax];
+  __shared__ int s_tokens[kSmallCallMaxAssign];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -93,68 +102,53 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     prefetch_tensormap(&map_b0);
     prefetch_tensormap(&map_b1);
   }
+  __syncthreads();  // s_abort and the barriers are initialised before any thread uses them
 
   // ---- find this block's unit --------------------------------------------------
-  // down: the schedule is final before this grid can start (a dependent grid starts
-  // only after every block of gate+up has passed its own dependency wait, hence after
-  // the routing kernel completed), so it is read before this grid's own wait.
-  // gate+up: routing and gather let their dependents start at once, so this grid can
-  // be running while the routing kernel still is.  For decode-sized calls each block
-  // therefore derives its unit from the expert ids itself (a histogram and a scan over
-  // <= 256 experts: the routing kernel's segment rule, restated), starts streaming its
-  // weight tiles, and only then waits for routing and gather to complete.
+  // Regular order (routing, gather, gate+up, down, combine): the schedule is final before
+  // either GEMM grid can start -- gather lets gate+up start only after its own wait for
+  // the routing kernel, and down starts after every gate+up block has passed its wait --
+  // so blocks read it first and prefetch weight tiles before their own dependency wait.
+  //
+  // Small-call order (gate+up, routing, down, combine): gate+up is the first kernel of the
+  // forward and needs nothing from the routing kernel, which runs beside it.  Its blocks
+  // wait for whatever preceded the forward (the inputs are then final and the previous
+  // forward has released the activation buffers), derive their unit from the expert ids
+  // held in one warp, and fetch their token rows from hidden_states themselves.  The
+  // routing kernel leaves only after gate+up has completed, so that the completion of
+  // routing, which is what down waits for, implies both.  Down blocks derive their unit
+  // the same way (the ids are inputs of the call, nothing an earlier kernel of this
+  // forward writes), prefetch weights, wait, and then compare with the schedule.
   int unit = blockIdx.x;
   int split = 0, n_split = 1;
   int expert = 0, row_start = 0, n_rows = 0;
-  bool waited = false;
-  const bool own_routing = kGateUp && p.early_mode >= 1 && p.ids != nullptr &&
-                           p.num_assign <= kOwnRoutingMaxAssign;
-  if (own_routing) {
-    for (int e = threadIdx.x; e < p.num_experts; e += kGemmThreads) s_hist[e] = 0;
-    __syncthreads();
-    for (int a = threadIdx.x; a < p.num_assign; a += kGemmThreads) {
-      const long long e = p.ids[a] - p.id_base;
-      if (e >= 0 && e < (long long)p.num_experts) atomicAdd(&s_hist[(int)e], 1);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int seg = unit / p.m_tiles;
-      int segs = 0, rows = 0, found = 0;
-      for (int e = 0; e < p.num_experts; ++e) {
-        const int cnt = s_hist[e];
-        const int chunks = (cnt + kSegRows - 1) / kSegRows;
-        if (!found && seg < segs + chunks) {
-          const int done = (seg - segs) * kSegRows;
-          s_unit[0] = e;
-          s_unit[1] = rows + done;
-          s_unit[2] = min(kSegRows, cnt - done);
-          s_unit[4] = done;  // rows of this expert that belong to earlier segments
-          found = 1;
-        }
-        segs += chunks;
-        rows += cnt;
-      }
-      s_unit[3] = found;
-    }
-    __syncthreads();
-    if (!s_unit[3]) {
-      // No such unit in this call.  Leave only after the dependency is resolved: the down
-      // grid may start once every block here has triggered or exited, and it reads the
-      // schedule straight away, so no block may exit while routing could still be running.
+  const int tiles = p.m_tiles;
+  unsigned members = 0u;
+  const int kblocks = (p.k_total + kTileK - 1) / kTileK;
+  if (p.small) {
+    if (kGateUp) {
       pdl_wait();
+      pdl_launch_dependents();  // the routing kernel may start now
+    }
+    const SmallRouteLane route = small_route_scan(p.ids, p.num_assign, p.num_experts, p.id_base);
+    if (!kGateUp) {
+      n_split = down_splits_for(route.n_seg, route.n_valid, p.m_tiles, kblocks, p.split_request);
+      split = unit % n_split;
+      unit /= n_split;
+    }
+    if (!small_route_pick(route, unit / tiles, expert, row_start, n_rows, members)) {
+      // No such unit in this call.  A down block still leaves only after its dependency
+      // is resolved: the combine kernel waits for this grid alone and reads what the
+      // routing kernel wrote.
+      if (!kGateUp) pdl_wait();
       return;
     }
-    expert = s_unit[0];
-    row_start = s_unit[1];
-    n_rows = s_unit[2];
+    if (kGateUp && warp == 0 && ((members >> lane) & 1u))
+      s_tokens[__popc(members & ((1u << lane) - 1u))] = lane / p.top_k;
   } else {
-    if (kGateUp && p.early_mode >= 1) {
-      pdl_wait();  // this grid was started early: the schedule may still be in the making
-      waited = true;
-    }
-    // header {segments, active, valid rows, splits} and the segment entry are 16 bytes each;
-    // gate+up knows its segment index without the header, so both loads go out together
-    // (the schedule array is sized for every segment index a block of this grid can have)
+    // header {segments, active, valid rows, splits} and the segment entry are 16 bytes
+    // each; gate+up knows its segment index without the header, so both loads go out
+    // together (the index is clamped to the array and checked against the count after).
     const int4 header = *reinterpret_cast<const int4*>(p.sched);
     const int n_seg = header.x;
     if (!kGateUp) {
@@ -162,42 +156,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       split = unit % n_split;
       unit /= n_split;
     }
-    const int seg = unit / p.m_tiles;
-    const int4 entry = *reinterpret_cast<const int4*>(p.sched + kSchedHeaderWords +
-                                                       kSchedSegWords * seg);
+    const int seg = unit / tiles;
+    const int4 entry = *reinterpret_cast<const int4*>(
+        p.sched + kSchedHeaderWords + kSchedSegWords * min(seg, p.sched_cap - 1));
     if (seg >= n_seg) return;
     expert = entry.x;
     row_start = entry.y;
     n_rows = entry.z;
   }
-  const int tile = unit % p.m_tiles;
+  const int tile = unit % tiles;
   const int n_mma = (n_rows + 15) & ~15;  // accumulator columns: 16..128
   trace_start(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
+  const bool direct = kGateUp && p.small != 0;  // token rows come straight from hidden_states
 
-  // Few rows: the block also finds the tokens of its rows (the stable order of the
-  // expert's assignments) and loads their activations straight from hidden_states, row
-  // by row, so nothing it needs comes from the routing or gather kernels.
-  const bool direct = own_routing && p.early_mode >= 2 && p.hidden_map_valid &&
-                      n_rows <= kDirectRowsMax;
-  if (direct) {
-    if (warp == 0) {
-      const int skip = s_unit[4];
-      int found = 0;
-      for (int base = 0; base < p.num_assign && found < skip + n_rows; base += 32) {
-        const int a = base + lane;
-        const bool mine = a < p.num_assign && (p.ids[a] - p.id_base) == (long long)expert;
-        const unsigned votes = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-          const int pos = found + __popc(votes & ((1u << lane) - 1u)) - skip;
-          if (pos >= 0 && pos < n_rows) s_tokens[pos] = a / p.top_k;
-        }
-        found += __popc(votes);
-      }
-    }
-    __syncthreads();
-  }
-
-  const int kblocks = (p.k_total + kTileK - 1) / kTileK;
   int kb0 = 0, num_kb = kblocks;
   if (!kGateUp) {
     const int per = kblocks / n_split, rem = kblocks % n_split;
@@ -206,17 +177,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   // ---- shared-memory pipeline geometry ---------------------------------------
-  constexpr uint32_t kABytes = kGateUp ? 2u * kTileM * 128u : kTileM * 128u;
+  constexpr uint32_t a_bytes = kGateUp ? 2u * kTileM * 128u : kTileM * 128u;
   const uint32_t b_bytes = (uint32_t)n_mma * 128u * (kGateUp ? 1u : 2u);
-  const uint32_t stage_bytes = kABytes + b_bytes;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
   // bytes one stage receives: row-by-row loads bring only the real rows
-  const uint32_t stage_tx = direct ? kABytes + (uint32_t)n_rows * 128u : stage_bytes;
+  const uint32_t stage_tx = direct ? a_bytes + (uint32_t)n_rows * 128u : stage_bytes;
   const int num_stages = min((int)(p.stage_budget / stage_bytes), kMaxStages);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   const uint64_t weight_policy = p.evict_first ? l2_policy_evict_first() : 0ull;
   auto load_weights = [&](uint32_t dst, uint32_t bar, int kc) {
     if (kGateUp) {
+      // one box over [E][2][I][H]: the gate rows of the tile, then the matching up rows
       if (p.evict_first) tma_load_4d_hint(dst, &map_w, bar, kc, tile * kTileM, 0, expert, weight_policy);
       else tma_load_4d(dst, &map_w, bar, kc, tile * kTileM, 0, expert);
     } else {
@@ -227,6 +199,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
 
   auto load_tokens = [&](uint32_t b_dst, uint32_t bar, int kc) {
     if (direct) {
+      // map_b1 describes hidden_states [T, H] with one-row boxes
       for (int r = 0; r < n_rows; ++r)
         tma_load_2d(b_dst + (uint32_t)r * 128u, &map_b1, bar, kc, s_tokens[r]);
     } else {
@@ -239,33 +212,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   };
 
   // ---- weight prefetch: fill the first stages' weight tiles while the previous
-  // kernel is still finishing; the token rows of those stages follow after the wait.
+  // kernel is still finishing; the token rows of those stages follow after the wait
+  // (a small-call gate+up block has waited already and loads both at once).
   const int prefetched = min(num_stages, num_kb);
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < prefetched; ++i) {
-      const uint32_t bar = smem_u32(&s_full[i]);
-      const uint32_t a_dst = smem_base + (uint32_t)i * stage_bytes;
-      const int kc = (kb0 + i) * kTileK;
-      mbar_expect_tx(bar, stage_tx);
-      load_weights(a_dst, bar, kc);
-      if (direct) load_tokens(a_dst + kABytes, bar, kc);
+  if (warp == 0) {
+    __syncwarp();  // s_tokens, written by this warp
+    if (lane == 0) {
+      for (int i = 0; i < prefetched; ++i) {
+        const uint32_t bar = smem_u32(&s_full[i]);
+        const uint32_t a_dst = smem_base + (uint32_t)i * stage_bytes;
+        const int kc = (kb0 + i) * kTileK;
+        mbar_expect_tx(bar, stage_tx);
+        load_weights(a_dst, bar, kc);
+        if (direct) load_tokens(a_dst + a_bytes, bar, kc);
+      }
     }
   }
 
-  // The dependency wait.  A block in direct mode has nothing to wait for before its
-  // main loop; its epilogue warps, idle until the accumulators are complete, do the wait
-  // (and only then let the down grid start, which reads the schedule at once).
-  auto check_own_routing = [&]() {
-    // The routing kernel's schedule is authoritative; a block whose own derivation
-    // disagreed with it would have used the wrong tiles.  Never observed; reported.
-    const int32_t* seg_words = p.sched + kSchedHeaderWords + kSchedSegWords * (unit / p.m_tiles);
-    if (seg_words[0] != expert || seg_words[1] != row_start || seg_words[2] != n_rows)
-      s_abort = 1;
-  };
-  if (!direct) {
-    if (!waited) pdl_wait();
+  // ---- the dependency wait ------------------------------------------------------
+  if (!(kGateUp && p.small)) {
+    pdl_wait();
     pdl_launch_dependents();
-    if (own_routing) check_own_routing();
+  }
+  if (!kGateUp && p.small) {
+    // The routing kernel's schedule is authoritative; a block whose own derivation
+    // disagreed with it would have streamed the wrong tiles.  Never observed; reported.
+    const int4 header = *reinterpret_cast<const int4*>(p.sched);
+    const int4 entry = *reinterpret_cast<const int4*>(
+        p.sched + kSchedHeaderWords + kSchedSegWords * min(unit / tiles, p.sched_cap - 1));
+    if (header.w != n_split || entry.x != expert || entry.y != row_start || entry.z != n_rows)
+      s_abort = 1;
   }
 
   // ---- tensor memory ------------------------------------------------------------
@@ -293,7 +269,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
           break;
         const uint32_t bar = smem_u32(&s_full[s]);
         const uint32_t a_dst = smem_base + (uint32_t)s * stage_bytes;
-        const uint32_t b_dst = a_dst + kABytes;
+        const uint32_t b_dst = a_dst + a_bytes;
         const int kc = (kb0 + i) * kTileK;
         if (i >= prefetched) {
           mbar_expect_tx(bar, stage_tx);
@@ -319,7 +295,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         if (i == 0 && p.trace && blockIdx.x == 0)
           p.trace[2 * (kGateUp ? kTraceGateUpFirstData : kTraceDownFirstData)] = global_timer_ns();
         const uint32_t a_addr = smem_base + (uint32_t)s * stage_bytes;
-        const uint32_t b_addr = a_addr + kABytes;
+        const uint32_t b_addr = a_addr + a_bytes;
         const uint64_t a0 = umma_smem_desc_sw128(a_addr);
         const uint64_t b0 = umma_smem_desc_sw128(b_addr);
         if (kGateUp) {
@@ -346,20 +322,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       if (ok && num_kb > 0) umma_commit(smem_u32(&s_acc));  // accumulators complete
     }
   } else {
-    // ===== epilogue: TMEM -> registers -> global =====
-    if (direct) {
-      pdl_wait();
-      pdl_launch_dependents();
-      check_own_routing();
-    }
+    // ===== epilogue warps =====
     const int quarter = warp & 3;
-    const int m = tile * kTileM + quarter * 32 + lane;  // weight row of this thread
-    const bool m_ok = m < p.m_total;
+    // Small call: this forward has no gather kernel; the blocks of tile 0 copy their rows
+    // to permuted_hidden while the main loop runs (16-byte loads and stores).
+    if (direct && tile == 0 && p.permuted_hidden != nullptr) {
+      const int t = (int)threadIdx.x - 64;
+      for (int r = 0; r < n_rows; ++r) {
+        const uint4* src = p.hidden + (size_t)s_tokens[r] * p.hidden_vecs;
+        uint4* dst = p.permuted_hidden + (size_t)(row_start + r) * p.hidden_vecs;
+        for (int v = t; v < p.hidden_vecs; v += 128) dst[v] = __ldg(src + v);
+      }
+    }
+    // ----- TMEM -> registers -> global -----
     bool have_acc = num_kb > 0;
     if (have_acc) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
     have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld needs the whole warp
-    // A block that gave up writes nothing; the status word reports it.
     if (have_acc || num_kb == 0) {
+      // A block that gave up writes nothing; the status word reports it.
+      const int m = tile * kTileM + quarter * 32 + lane;  // weight row of this thread
+      const bool m_ok = m < p.m_total;
       tc_fence_after_sync();
       const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
       for (int c0 = 0; c0 < n_mma; c0 += 16) {
@@ -421,7 +403,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
 // Tuning knobs (b200moe_tune): process-wide, meant for benchmarking sweeps.
 int g_gemm_stage_kb = 108;
 int g_gemm_evict_first = 0;
-int g_early_mode = 0;
 // Shared memory of one block's stage ring.  Normally two blocks share an SM.  A grid that
 // cannot put more than one block on an SM anyway (`grid <= sm_count`, known on the host from
 // the worst-case unit count) gets the whole SM per block: with so few blocks the bytes in
@@ -464,24 +445,28 @@ static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_
 }
 
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
-                           const int32_t* sched, uint32_t* status, void* act_hi, void* act_lo,
-                           int inter, int hidden, int rows_cap, int grid, const int64_t* ids,
-                           int num_assign, int num_experts, int id_base, int top_k,
-                           const CUtensorMap* map_hidden, int sm_count, bool pdl,
-                           cudaStream_t stream) {
+                           const CUtensorMap* map_hidden, const int32_t* sched, int sched_cap,
+                           uint32_t* status, void* act_hi, void* act_lo, int inter, int hidden,
+                           int rows_cap, int grid, const SmallCall* small, int sm_count,
+                           bool pdl, cudaStream_t stream) {
   GemmParams p = {};
-  p.ids = ids;
-  p.num_assign = num_assign;
-  p.num_experts = num_experts;
-  p.id_base = id_base;
-  p.top_k = top_k;
-  p.hidden_map_valid = map_hidden != nullptr ? 1 : 0;
-  p.early_mode = g_early_mode;
+  if (small != nullptr && map_hidden != nullptr) {
+    p.small = 1;
+    p.ids = small->ids;
+    p.num_assign = small->num_assign;
+    p.num_experts = small->num_experts;
+    p.id_base = small->id_base;
+    p.top_k = small->top_k;
+    p.hidden = static_cast<const uint4*>(small->hidden);
+    p.permuted_hidden = static_cast<uint4*>(small->permuted_hidden);
+    p.hidden_vecs = hidden / 8;
+  }
   p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
                                                   kTraceOffsetBytes);
   p.stage_budget = gemm_stage_budget(grid, sm_count);
   p.evict_first = g_gemm_evict_first;
   p.sched = sched;
+  p.sched_cap = sched_cap;
   p.status = status;
   p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
   p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
@@ -490,19 +475,30 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
   p.k_total = hidden;
   p.m_tiles = (inter + kTileM - 1) / kTileM;
   p.rows_cap = rows_cap;
-  return launch_gemm<true>(map_w, map_x, map_hidden ? *map_hidden : map_x, p, grid, pdl, stream);
+  return launch_gemm<true>(map_w, map_x, p.small ? *map_hidden : map_x, p, grid, pdl, stream);
 }
 
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
-                        const CUtensorMap& map_lo, const int32_t* sched, uint32_t* status,
-                        float* partials, int hidden, int inter, int rows_cap, int grid,
-                        int sm_count, bool pdl, cudaStream_t stream) {
+                        const CUtensorMap& map_lo, const int32_t* sched, int sched_cap,
+                        uint32_t* status, float* partials, int hidden, int inter, int rows_cap,
+                        int grid, const SmallCall* small, int sm_count, bool pdl,
+                        cudaStream_t stream) {
   GemmParams p = {};
+  if (small != nullptr) {
+    p.small = 1;
+    p.ids = small->ids;
+    p.num_assign = small->num_assign;
+    p.num_experts = small->num_experts;
+    p.id_base = small->id_base;
+    p.top_k = small->top_k;
+    p.split_request = small->split_request;
+  }
   p.stage_budget = gemm_stage_budget(grid, sm_count);
   p.evict_first = g_gemm_evict_first;
   p.trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) +
                                                   kTraceOffsetBytes);
   p.sched = sched;
+  p.sched_cap = sched_cap;
   p.status = status;
   p.act_hi = nullptr;
   p.act_lo = nullptr;

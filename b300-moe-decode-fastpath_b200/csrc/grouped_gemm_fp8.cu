@@ -52,6 +52,7 @@ struct QGemmParams {
   int k_total;                // H (gate+up) or I (down)
   int m_tiles;                // ceil(I / 128) (gate+up) or ceil(H / 128) (down)
   int rows_cap;
+  int sched_cap;              // segment entries the schedule array holds
   unsigned long long* trace;
   uint32_t stage_budget;
 };
@@ -85,7 +86,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   int unit = blockIdx.x;
   int split = 0, n_split = 1;
   // header {segments, active, valid rows, splits} and the segment entry are 16 bytes each;
-  // gate+up knows its segment index without the header, so both loads go out together
+  // gate+up knows its segment index without the header, so both loads go out together (the
+  // index is clamped to the array; blocks past the last segment leave right after)
   const int4 header = *reinterpret_cast<const int4*>(p.sched);
   const int n_seg = header.x;
   if (!kGateUp) {
@@ -94,8 +96,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
     unit /= n_split;
   }
   const int seg = unit / p.m_tiles;
-  const int4 entry = *reinterpret_cast<const int4*>(p.sched + kSchedHeaderWords +
-                                                     kSchedSegWords * seg);
+  const int4 entry = *reinterpret_cast<const int4*>(
+      p.sched + kSchedHeaderWords + kSchedSegWords * min(seg, p.sched_cap - 1));
   if (seg >= n_seg) return;
   const int expert = entry.x;
   const int row_start = entry.y;
@@ -347,11 +349,12 @@ static cudaError_t launch_fp8(const CUtensorMap& map_w, const CUtensorMap& map_b
   return cudaLaunchKernelEx(&cfg, grouped_gemm_fp8_kernel<kGateUp>, map_w, map_b, params);
 }
 
-static QGemmParams fp8_params(const int32_t* sched, uint32_t* status, const float* row_scale,
+static QGemmParams fp8_params(const int32_t* sched, int sched_cap, uint32_t* status, const float* row_scale,
                               const float* token_scale, int m_total, int k_total, int m_tiles,
                               int rows_cap, int grid, int sm_count) {
   QGemmParams p = {};
   p.sched = sched;
+  p.sched_cap = sched_cap;
   p.status = status;
   p.row_scale = row_scale;
   p.token_scale = token_scale;
@@ -366,11 +369,11 @@ static QGemmParams fp8_params(const int32_t* sched, uint32_t* status, const floa
 }
 
 cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
-                               const int32_t* sched, uint32_t* status, void* act_hi,
-                               void* act_lo, uint32_t* act_amax, const float* row_scale,
+                               const int32_t* sched, int sched_cap, uint32_t* status,
+                               void* act_hi, void* act_lo, uint32_t* act_amax, const float* row_scale,
                                const float* token_scale, int inter, int hidden, int rows_cap,
                                int grid, int sm_count, bool pdl, cudaStream_t stream) {
-  QGemmParams p = fp8_params(sched, status, row_scale, token_scale, inter, hidden,
+  QGemmParams p = fp8_params(sched, sched_cap, status, row_scale, token_scale, inter, hidden,
                              (inter + 127) / 128, rows_cap, grid, sm_count);
   p.act_hi = static_cast<__nv_bfloat16*>(act_hi);
   p.act_lo = static_cast<__nv_bfloat16*>(act_lo);
@@ -379,11 +382,11 @@ cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_
 }
 
 cudaError_t launch_down_fp8(const CUtensorMap& map_w, const CUtensorMap& map_act,
-                            const int32_t* sched, uint32_t* status, float* partials,
+                            const int32_t* sched, int sched_cap, uint32_t* status, float* partials,
                             const float* row_scale, const float* token_scale, int hidden,
                             int inter, int rows_cap, int grid, int sm_count, bool pdl,
                             cudaStream_t stream) {
-  QGemmParams p = fp8_params(sched, status, row_scale, token_scale, hidden, inter,
+  QGemmParams p = fp8_params(sched, sched_cap, status, row_scale, token_scale, hidden, inter,
                              (hidden + 127) / 128, rows_cap, grid, sm_count);
   p.partials = partials;
   return launch_fp8<false>(map_w, map_act, p, grid, pdl, stream);

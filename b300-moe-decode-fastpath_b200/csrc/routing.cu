@@ -57,10 +57,11 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
                uint32_t* __restrict__ status, int down_tiles, int down_kblocks, int target_ctas,
                int seg_rows, int id_base, int foreign_ids_allowed, unsigned long long* __restrict__ trace,
                const uint32_t* __restrict__ wait_flags, int wait_world, uint32_t wait_epoch,
-               unsigned long long wait_limit_ns) {
+               unsigned long long wait_limit_ns, int wait_at_end,
+               uint4* __restrict__ zero_rows, int zero_row_vecs) {
   __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
   __shared__ int s_cursor[B200MOE_MAX_EXPERTS];
-  __shared__ int s_whist[kRoutingWarps][B200MOE_MAX_EXPERTS];
+  extern __shared__ int s_whist[];  // [warps of this launch][num_experts]
   __shared__ int s_tmp[kRoutingWarps];
   __shared__ int s_bad;
 
@@ -108,7 +109,10 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     // the status word describes the forward this launch begins
     *status = (wait_flags && !s_peers_ready) ? B200MOE_STATUS_PEER_TIMEOUT : 0u;
     if (trace) {
-      for (int k = 0; k < kTraceKernels; ++k) trace[2 * k + 1] = 0ull;
+      // end times of the forward that begins; in small-call order the gate+up kernel runs
+      // in front of this one and its stamps belong to this forward already
+      for (int k = 0; k < kTraceKernels; ++k)
+        if (!(wait_at_end && k == kTraceGateUp)) trace[2 * k + 1] = 0ull;
       trace[2 * kTraceRouting] = global_timer_ns();
     }
   }
@@ -158,15 +162,8 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     offsets[0] = 0;
     // Split-K factor of the down projection: when few (segment, tile) units
     // exist, cut K so that about `target_ctas` blocks stream weights at once.
-    int splits = 1;
-    const int units = n_seg * down_tiles;
-    if (target_ctas < 0) {
-      splits = -target_ctas;  // forced by the caller (tuning)
-    } else {
-      splits = choose_down_splits(units, target_ctas, down_kblocks, rows16_of(n_valid, n_seg));
-    }
-    splits = max(1, min(splits, kDownSplitMax));
-    splits = min(splits, max(1, down_kblocks));
+    // (a negative `target_ctas` is a factor forced by the caller, for tuning sweeps)
+    const int splits = down_splits_for(n_seg, n_valid, down_tiles, down_kblocks, target_ctas);
     sched[kSchedNumSegments] = n_seg;
     sched[kSchedNumActive] = n_active;
     sched[kSchedNumValidRows] = n_valid;
@@ -180,8 +177,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
 
   // Pass 2: stable placement, one block-width of assignments per round.
   for (int base = 0; base < num_assign; base += threads) {
-    for (int i = tid; i < num_warps * num_experts; i += threads)
-      s_whist[i / num_experts][i % num_experts] = 0;
+    for (int i = tid; i < num_warps * num_experts; i += threads) s_whist[i] = 0;
     __syncthreads();
 
     const int a = base + tid;
@@ -191,14 +187,14 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     const int e = valid ? (int)e64 : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(peers & ((1u << lane) - 1u));
-    if (valid && rank == 0) s_whist[warp][e] = __popc(peers);
+    if (valid && rank == 0) s_whist[warp * num_experts + e] = __popc(peers);
     __syncthreads();
 
     if (is_expert) {
       int run = s_cursor[tid];
       for (int w = 0; w < num_warps; ++w) {
-        const int t = s_whist[w][tid];
-        s_whist[w][tid] = run;
+        const int t = s_whist[w * num_experts + tid];
+        s_whist[w * num_experts + tid] = run;
         run += t;
       }
       s_cursor[tid] = run;
@@ -206,7 +202,7 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     __syncthreads();
 
     if (valid) {
-      const int p = s_whist[warp][e] + rank;
+      const int p = s_whist[warp * num_experts + e] + rank;
       reverse_mapping[a] = p;
       permutation[p] = a;
       if (perm_tokens) perm_tokens[p] = a / top_k;
@@ -229,8 +225,19 @@ routing_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict_
     }
     // On an expert-parallel rank, ids outside the local range are other ranks' experts.
     if (tid == 0 && !foreign_ids_allowed) atomicOr(status, B200MOE_STATUS_BAD_EXPERT_ID);
+    // A forward in small-call order has no gather kernel: the rows past the valid ones,
+    // which that kernel zero-fills, are cleared here.
+    if (zero_rows) {
+      const size_t first = (size_t)n_valid * zero_row_vecs;
+      const size_t count = (size_t)(num_assign - n_valid) * zero_row_vecs;
+      for (size_t v = tid; v < count; v += threads) zero_rows[first + v] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   trace_end(trace, kTraceRouting);
+  // Small-call order: the kernel in front of this one is the gate+up GEMM, and the kernel
+  // behind it waits for this grid alone.  Leaving only once gate+up has completed makes
+  // "routing complete" imply "gate+up complete" for everything that follows.
+  if (wait_at_end) pdl_wait();
 }
 
 cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assign, int top_k,
@@ -240,20 +247,33 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int32_t* sched, uint32_t* status, int down_tiles, int down_kblocks,
                            int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
-                           unsigned long long wait_limit_ns, cudaStream_t stream) {
+                           unsigned long long wait_limit_ns, bool after_gate_up, bool pdl,
+                           void* zero_rows, int zero_row_vecs, cudaStream_t stream) {
   // One thread per expert and per assignment of a round, in whole warps; fewer warps make
   // the block-wide barriers of a decode-sized call cheaper.
   int threads = num_assign > num_experts ? num_assign : num_experts;
   threads = (threads + 31) / 32 * 32;
   if (threads > kRoutingThreads) threads = kRoutingThreads;
-  routing_kernel<<<1, threads, 0, stream>>>(
-      ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k, num_experts, counts,
-      offsets, reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
-      static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles, down_kblocks,
-      target_ctas, seg_rows, id_base, foreign_ids_allowed ? 1 : 0,
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = sizeof(int) * (size_t)(threads / 32) * num_experts;  // <= 32 KB
+  cfg.stream = stream;
+  // `after_gate_up`: small-call order, this kernel follows the gate+up GEMM in the stream
+  // and runs beside it (programmatic dependent launch); see the end of the kernel.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (after_gate_up && pdl) ? 1 : 0;
+  return cudaLaunchKernelEx(
+      &cfg, routing_kernel, ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k,
+      num_experts, counts, offsets, reverse_mapping, permutation, offsets_i32, perm_tokens,
+      perm_experts, static_cast<__nv_bfloat16*>(perm_weights), sched, status, down_tiles,
+      down_kblocks, target_ctas, seg_rows, id_base, foreign_ids_allowed ? 1 : 0,
       reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(status) + kTraceOffsetBytes),
-      wait_flags, wait_world, wait_epoch, wait_limit_ns);
-  return cudaGetLastError();
+      wait_flags, wait_world, wait_epoch, wait_limit_ns, after_gate_up ? 1 : 0,
+      static_cast<uint4*>(zero_rows), zero_row_vecs);
 }
 
 // ---------------------------------------------------------------------------
@@ -320,7 +340,8 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
                         reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
                         perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
                         reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas,
-                        kSegRows, 0, false, nullptr, 0, 0u, 0ull, stream);
+                        kSegRows, 0, false, nullptr, 0, 0u, 0ull, false, false, nullptr, 0,
+                        stream);
 }
 
 }  // namespace b200moe

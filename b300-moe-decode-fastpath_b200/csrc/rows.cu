@@ -15,13 +15,11 @@ constexpr int kRowThreads = 256;
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
                    uint4* __restrict__ out, int num_assign, int num_tokens, int top_k,
-                   int vec_per_row, int early_trigger, unsigned long long* __restrict__ trace) {
-  // early_trigger: let the gate+up grid start right away (its blocks then find their work
-  // from the expert ids themselves); otherwise it starts once routing has completed and
-  // may read the schedule at once.
-  if (early_trigger) pdl_launch_dependents();
+                   int vec_per_row, unsigned long long* __restrict__ trace) {
+  // The gate+up grid may start once every block here has passed its wait, that is, once
+  // the routing kernel has completed: it reads the schedule as soon as it starts.
   pdl_wait();
-  if (!early_trigger) pdl_launch_dependents();
+  pdl_launch_dependents();
   trace_start(trace, kTraceGather);
   const int row = blockIdx.x;
   const int64_t a = permutation[row];
@@ -331,14 +329,11 @@ static cudaError_t launch_with_pdl(const void* func, dim3 grid, dim3 block, void
 
 cudaError_t launch_gather(const void* hidden, const int64_t* permutation, void* out,
                           int num_assign, int num_tokens, int top_k, int hidden_size,
-                          bool early_trigger, unsigned long long* trace, bool pdl,
-                          cudaStream_t stream) {
+                          unsigned long long* trace, bool pdl, cudaStream_t stream) {
   int vec_per_row = hidden_size / 8;
   const uint4* h = static_cast<const uint4*>(hidden);
   uint4* o = static_cast<uint4*>(out);
-  int early = early_trigger ? 1 : 0;
-  void* args[] = {&h, &permutation, &o, &num_assign, &num_tokens, &top_k, &vec_per_row, &early,
-                  &trace};
+  void* args[] = {&h, &permutation, &o, &num_assign, &num_tokens, &top_k, &vec_per_row, &trace};
   return launch_with_pdl(reinterpret_cast<const void*>(&gather_rows_kernel), dim3(num_assign),
                          dim3(kRowThreads), args, pdl, stream);
 }

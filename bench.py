@@ -20,9 +20,18 @@ Percentiles use linear interpolation on the sorted samples (timing.py:23-29).
 contains the router's top-k (benchmark_goal_1b.py:530-546), which is outside
 this layer.
 
-``--impl reference`` times the reference's pure-PyTorch path -- restated in
-``oracle/moe_oracle.py`` because the reference package itself does not travel to
-the GPU box -- on the host CPU cores, same workload, same metric.
+``--impl reference`` times the reference's own pure-PyTorch path
+(``fastpath.b300_moe_forward(..., backend="torch")``) on the host CPU cores, same
+workload, same metric, when an unmodified copy of the reference package lies in
+``baseline/_ref`` (made by ``python bench.py --prepare-reference`` where the
+reference checkout is available; the directory is not part of the repository's
+history).  Without that copy it times the restatement in ``oracle/moe_oracle.py``
+and says so (``cpu_baseline.kind`` = ``"port"``).
+
+With N > 1 the layer runs expert-parallel; before anything is timed every token
+layout and transport is checked against the FP32 oracle and the assembled
+routing tensors against ``group_tokens`` (``parity`` in the JSON line; a miss
+ends the run with a non-zero exit code).
 """
 
 from __future__ import annotations
@@ -58,6 +67,10 @@ CONFIGS = {
                     routing="uniform", weight_kind="softmax"),
     "wide": dict(hidden=4096, inter=14336, experts=64, top_k=8, sweep=(64,),
                  routing="zipf", weight_kind="raw"),
+    # the wide layer cut to 16 experts: same tiles, rows per expert and routing law, a fourth
+    # of the weights (multi-GPU parity runs)
+    "wide_e16": dict(hidden=4096, inter=14336, experts=16, top_k=8, sweep=(64,),
+                     routing="zipf", weight_kind="raw"),
     "deepseek": dict(hidden=7168, inter=2048, experts=256, top_k=8, sweep=(1, 8, 32, 64),
                      routing="uniform", weight_kind="softmax"),
     "deepseek_hotspot": dict(hidden=7168, inter=2048, experts=256, top_k=8, sweep=(1, 8, 32, 64),
@@ -78,12 +91,43 @@ def apply_config(name: str) -> None:
                     f"{ROUTING}_T{tokens}")
         METRIC = f"moe_layer_decode_p50_us_mean_over_T{tokens}"
 L2_FLUSH_BYTES = 256 << 20
+L2_POLICY = ("flushed before every timed forward: 256 MiB written, then 256 MiB read to push the "
+             "dirty lines out; every forward also streams >= 352 MB of weights (> 126 MB L2)")
 FALLBACK_HBM_GBS = 6650.0
 STAGE_NAMES = ("routing", "gather", "gate_up_swiglu", "down", "combine")
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch at T=1 from
-# the committed ncu capture (profiles/); None until a capture exists.
-GATE_UP_T1_DRAM_TRAFFIC_BYTES = 473_528_320  # 469.84 MB read + 3.69 MB written
-GATE_UP_T1_DRAM_TRAFFIC_BYTES_FP8 = 239_050_752  # FP8 weights: 235.18 MB read + 3.87 MB written
+PARITY_BAR = 2e-2  # max |y - y_ref| <= 2e-2 x rms(y_ref) against the FP32 oracle
+# DRAM traffic of one launch of the dominant kernel, from the ncu captures summarised under
+# profiles/: a small data file next to the summaries, keyed by kernel and tagged with the
+# hash of the kernel source the capture was taken from.
+TRAFFIC_FILE = REPO / "profiles" / "dram_traffic.json"
+CSRC = REPO / "b300-moe-decode-fastpath_b200" / "csrc"
+
+
+def source_hash(names: list[str]) -> str:
+    import hashlib
+
+    digest = hashlib.sha256()
+    for name in names:
+        digest.update((CSRC / name).read_bytes())
+    return digest.hexdigest()[:16]
+
+
+def measured_traffic(key: str) -> tuple[int | None, str]:
+    """``dram__bytes_read.sum + dram__bytes_write.sum`` per launch for ``key``, or None
+    (with the reason) when no capture is recorded or the kernel source has changed since."""
+
+    try:
+        entry = json.loads(TRAFFIC_FILE.read_text())[key]
+    except (OSError, KeyError, ValueError):
+        return None, "no ncu capture recorded for this kernel and workload"
+    try:
+        current = source_hash(entry["sources"])
+    except OSError:
+        return None, "kernel sources not found"
+    if current != entry["source_hash"]:
+        return None, (f"kernel source changed since the capture ({entry['source_hash']} -> "
+                      f"{current}); re-capture and update profiles/dram_traffic.json")
+    return int(entry["dram_bytes_read"]) + int(entry["dram_bytes_write"]), entry["summary"]
 
 
 def percentile(sorted_values: list[float], q: float) -> float:
@@ -434,6 +478,157 @@ def write_reference_csv(path: str, result: dict[str, object], args, device) -> i
     return len(rows)
 
 
+# -----------------------------------------------------------------------------
+# parity, checked outside every timed region (the oracle is the checker, never the path)
+# -----------------------------------------------------------------------------
+def _parity_tokens(T: int, num_experts: int) -> list[int]:
+    """All tokens when the FP32 oracle of the whole layer fits the host (the 8-expert
+    layer), else three of them (the oracle then needs only the experts those route to)."""
+
+    if num_experts * HIDDEN * INTER <= 8 * 4096 * 14336:
+        return list(range(T))
+    return sorted({0, T // 2, T - 1})
+
+
+def _oracle_rows(hidden, ids, weights, tokens, expert_weights):
+    """FP32 oracle rows for ``tokens``; ``expert_weights`` maps expert id -> (gate_up, down)
+    CPU tensors and must hold every expert those tokens route to."""
+
+    from oracle import moe_oracle
+
+    picked = ids[tokens]
+    experts = sorted({int(e) for e in picked.reshape(-1).tolist()})
+    remap = {e: i for i, e in enumerate(experts)}
+    small_ids = torch.tensor([[remap[int(e)] for e in row] for row in picked.tolist()],
+                             dtype=torch.int64)
+    gate_up = torch.stack([expert_weights[e][0] for e in experts])
+    down = torch.stack([expert_weights[e][1] for e in experts])
+    ref, _ = moe_oracle.routed_moe(hidden[tokens], small_ids, weights[tokens], gate_up, down,
+                                   num_experts=len(experts), top_k=picked.shape[1])
+    return ref
+
+
+def single_gpu_parity(forward, cases, gate_up_cpu, down_cpu, sweep) -> dict[str, object]:
+    """The timed call at the smallest and the largest T against the FP32 oracle."""
+
+    from oracle import moe_oracle
+
+    experts = {e: (gate_up_cpu[e], down_cpu[e]) for e in range(gate_up_cpu.shape[0])}
+    detail, worst, floor = {}, 0.0, 0.0
+    for T in sorted({sweep[0], sweep[-1]}):
+        out = forward(T)
+        torch.cuda.synchronize(out.device)
+        hidden, ids, weights = cases[T]["host"]
+        tokens = _parity_tokens(T, len(experts))
+        ref = _oracle_rows(hidden, ids, weights, tokens, experts)
+        err = moe_oracle.relative_max_error(out[tokens].float().cpu(), ref)
+        detail[str(T)] = {"err_over_rms": round(err, 5), "floor": round(moe_oracle.bf16_floor(ref), 5),
+                          "tokens_checked": len(tokens)}
+        worst = max(worst, err)
+        floor = max(floor, detail[str(T)]["floor"])
+    return {"err_over_rms": round(worst, 5), "floor": floor, "bar": PARITY_BAR,
+            "status": 0 if worst <= PARITY_BAR else 1,
+            "oracle": "oracle/moe_oracle.routed_moe (FP32) on the same seeded inputs",
+            "per_T": detail}
+
+
+def expert_parallel_parity(engines, cases, gate_up, down, base, count, rank, world, device,
+                           dist, fp8_scales) -> dict[str, object]:
+    """Every token layout and transport of the N-GPU layer against the FP32 oracle, and the
+    assembled routing tensors bit-exact against ``group_tokens``; rank 0 judges.
+
+    The oracle needs the weights of the experts the checked tokens route to: their owners
+    broadcast them once (BF16, as resident; FP8 weights are dequantised first, so the
+    oracle sees what the kernels multiply by)."""
+
+    import numpy as np
+
+    from oracle import moe_oracle
+
+    if fp8_scales is not None:
+        from b200moe import dequantize_rows_fp8  # E4M3 value * row scale, as BF16
+
+        gate_up = dequantize_rows_fp8(gate_up, fp8_scales[0])
+        down = dequantize_rows_fp8(down, fp8_scales[1])
+    checked_T = sorted({SWEEP[0], SWEEP[-1]})
+    tokens = {T: _parity_tokens(T, EXPERTS) for T in checked_T}
+    needed = sorted({int(e) for T in checked_T
+                     for e in cases[T]["host"][1][tokens[T]].reshape(-1).tolist()})
+    expert_weights = {}
+    gu_buf = torch.empty_like(gate_up[0])
+    dn_buf = torch.empty_like(down[0])
+    for e in needed:
+        owner = e // count
+        if owner == rank:
+            gu_buf.copy_(gate_up[e - base])
+            dn_buf.copy_(down[e - base])
+        dist.broadcast(gu_buf, src=owner)
+        dist.broadcast(dn_buf, src=owner)
+        if rank == 0:
+            expert_weights[e] = (gu_buf.cpu(), dn_buf.cpu())
+    report = {"replicated_err_over_rms": 0.0, "sharded_err_over_rms": 0.0, "floor": 0.0,
+              "routing_bit_exact": True, "bar": PARITY_BAR, "status": 0,
+              "oracle": "oracle/moe_oracle.routed_moe (FP32) and group_tokens on the same "
+                        "seeded inputs; rank 0 judges every rank's rows",
+              "checked": {}}
+    for T in checked_T:
+        hidden, ids, weights = cases[T]["host"]
+        ref = want = None
+        if rank == 0:
+            ref = _oracle_rows(hidden, ids, weights, tokens[T], expert_weights)
+            want = moe_oracle.group_tokens(ids, EXPERTS)
+            report["floor"] = max(report["floor"], round(moe_oracle.bf16_floor(ref), 5))
+        for name, engine in engines.items():
+            out = engine.forward(*cases[T]["dev"], tokens="replicated")
+            assembled = engine.global_routing()
+            # every rank's replicated output goes to rank 0: all of them must pass
+            gathered = [torch.empty_like(out) for _ in range(world)]
+            dist.all_gather(gathered, out.contiguous())
+            entry = {}
+            if rank == 0:
+                errs = [moe_oracle.relative_max_error(g[tokens[T]].float().cpu(), ref)
+                        for g in gathered]
+                entry["replicated"] = round(max(errs), 5)
+                entry["ranks_identical"] = all(torch.equal(g, gathered[0]) for g in gathered)
+                exact = all(np.array_equal(assembled[key].cpu().numpy(), getattr(want, key))
+                            for key in ("expert_counts", "expert_offsets", "permutation",
+                                        "reverse_mapping"))
+                entry["routing_bit_exact"] = bool(exact)
+                report["routing_bit_exact"] &= bool(exact)
+                report["replicated_err_over_rms"] = max(report["replicated_err_over_rms"],
+                                                        entry["replicated"])
+            if T % world == 0:
+                per = T // world
+                shard = tuple(t[rank * per:(rank + 1) * per].contiguous()
+                              for t in cases[T]["dev"])
+                mine = engine.forward(*shard, tokens="sharded")
+                rows = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(rows, mine.contiguous())
+                if rank == 0:
+                    whole = torch.cat(rows)
+                    entry["sharded"] = round(moe_oracle.relative_max_error(
+                        whole[tokens[T]].float().cpu(), ref), 5)
+                    report["sharded_err_over_rms"] = max(report["sharded_err_over_rms"],
+                                                         entry["sharded"])
+            status = int(engine.workspace.status()) if engine.workspace is not None else 0
+            flag = torch.tensor([status], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            entry["device_status"] = int(flag.item())
+            report["checked"][f"T{T}_{name}"] = entry
+            if entry["device_status"] != 0:
+                report["status"] = 2
+    if rank == 0:
+        ok = (report["replicated_err_over_rms"] <= PARITY_BAR
+              and report["sharded_err_over_rms"] <= PARITY_BAR and report["routing_bit_exact"]
+              and all(e.get("ranks_identical", True) for e in report["checked"].values()))
+        if not ok and report["status"] == 0:
+            report["status"] = 1
+    verdict = torch.tensor([report["status"]], device=device)
+    dist.broadcast(verdict, src=0)
+    report["status"] = int(verdict.item())
+    return report
+
+
 def run_ours(args: argparse.Namespace) -> dict[str, object]:
     from b200moe import (B300MoEWorkspace, StagedLayer, b300_moe_forward,
                          b300_moe_forward_pinned, workloads)
@@ -656,12 +851,14 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "unit": "GB/s",
         "frac": round(achieved / peak, 3),
         "algorithmic_bytes": gu_bytes,
-        # the captures are of the Mixtral-shaped layer at T=1 (two active experts)
-        "traffic": (None if (args.config != "mixtral" or sweep[0] != 1)
-                    else GATE_UP_T1_DRAM_TRAFFIC_BYTES if fp8 is None
-                    else GATE_UP_T1_DRAM_TRAFFIC_BYTES_FP8),
         "frac_of_8000": round(achieved / 8000.0, 3),
     }
+    # the captures are of the Mixtral-shaped layer at T=1 (two active experts)
+    if args.config == "mixtral" and sweep[0] == 1:
+        roofline["traffic"], roofline["traffic_source"] = measured_traffic(
+            "gate_up_mixtral_T1_fp8" if fp8 is not None else "gate_up_mixtral_T1_bf16")
+    else:
+        roofline["traffic"], roofline["traffic_source"] = None, "captured for the mixtral T=1 case only"
 
     h2d = sum(sum(t.numel() * t.element_size() for t in cases[T]["host"]) for T in sweep)
     d2h = sum(cases[T]["host_out"].numel() * 2 for T in sweep)
@@ -682,9 +879,9 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "config": {
             "workload": WORKLOAD if fp8 is None else WORKLOAD.replace("_bf16_", "_fp8w_"),
             "tokens": list(sweep),
-            "l2": "flushed before every timed forward: 256 MiB written, then 256 MiB read to push the dirty lines out; every forward also streams >= 704 MB of weights (> 126 MB L2)",
             "step": "one forward at each T of the sweep",
         },
+        "l2_policy": L2_POLICY,
         "e2e": {
             "value": round(sum(e2e_p50s) / len(e2e_p50s), 2),
             "unit": "us",
@@ -736,7 +933,12 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         except Exception as error:  # never let the extra line break the contract line
             result["fp8_weights"] = {"unavailable": f"{type(error).__name__}: {error}"[:200]}
     if not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_baseline(gate_up, down, cases, budget_s=20.0)
+        gate_up_cpu, down_cpu = gate_up.cpu(), down.cpu()
+        result["parity"] = single_gpu_parity(forward, cases, gate_up_cpu, down_cpu, sweep)
+        result["cpu_baseline"] = cpu_baseline(gate_up_cpu, down_cpu, cases, budget_s=20.0)
+        if result["parity"]["status"] != 0:
+            print(json.dumps(result), flush=True)
+            raise SystemExit(3)
     if args.csv:
         result["csv"] = {"path": args.csv,
                          "rows": write_reference_csv(args.csv, result, args, device)}
@@ -799,6 +1001,23 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         cases[T] = {"host": host, "dev": dev, "stage_in": tuple(torch.empty_like(t) for t in dev),
                     "host_out": torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory(),
                     "local_active": local_active}
+
+    # parity first, outside every timed region: both transports, both token layouts
+    engines = {"nccl": baseline}
+    if layer is not baseline:
+        engines["p2p"] = layer
+    parity = expert_parallel_parity(engines, cases, gate_up, down, base, count, rank, world,
+                                    device, dist, fp8_scales)
+    if parity["status"] != 0:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "n_gpus": world, "parity": parity,
+                              "error": "parity check failed; nothing was timed"}), flush=True)
+        dist.barrier()
+        raise SystemExit(3)
+    if args.parity_only:
+        return None if rank != 0 else {"metric": METRIC, "n_gpus": world,
+                                       "config": {"workload": WORKLOAD, "tokens": list(SWEEP)},
+                                       "parity": parity}
 
     def forward(T):
         return layer.forward(*cases[T]["dev"], tokens="replicated")
@@ -967,15 +1186,19 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
         "config": {
             "workload": WORKLOAD if fp8_scales is None else WORKLOAD.replace("_bf16_", "_fp8w_"),
             "tokens": list(SWEEP),
-            "parallelism": f"expert-parallel ep{world}: {EXPERTS // world} experts per rank, "
-                           "tokens replicated, FP32 partial outputs combined by "
-                           + ("one peer-memory kernel over NVLink (b200moe_ep_reduce)"
-                              if transport == "p2p" else "NCCL all-reduce + cast"),
+            "step": "one forward at each T of the sweep",
+        },
+        "parallelism": {
+            "kind": f"expert-parallel ep{world}: {EXPERTS // world} experts per rank, tokens "
+                    "replicated, rows combined and reduced across ranks by "
+                    + ("one peer-memory kernel over NVLink (b200moe_ep_combine_reduce)"
+                       if transport == "p2p" else "combine kernel + NCCL all-reduce + cast"),
             "transport": transport,
             "transport_note": transport_note,
-            "l2": "flushed before every timed forward (256 MiB written, then 256 MiB read)",
-            "step": "one forward at each T of the sweep; every sample is the max over ranks",
+            "sample": "every sample is the max over ranks",
         },
+        "l2_policy": L2_POLICY,
+        "parity": parity,
         "e2e": {"value": round(sum(e2e_p50s) / len(e2e_p50s), 2), "unit": "us",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "what": "ExpertParallelMoE.forward with pinned host activations/routes copied in "
@@ -994,45 +1217,122 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
 
 
 # -----------------------------------------------------------------------------
-# CPU arms (the oracle restates the reference's torch backend)
+# CPU arms: the reference's torch backend on the host cores
 # -----------------------------------------------------------------------------
-def _cpu_forward(case_host, gate_up_cpu, down_cpu):
+REFERENCE_COPY = REPO / "baseline" / "_ref"
+REFERENCE_PACKAGES = ("fastpath", "baseline")
+
+
+def prepare_reference(source: str) -> str:
+    """Copy the reference's two pure-Python packages, unmodified, into ``baseline/_ref``.
+
+    The directory is listed in ``.gitignore`` (it is not this repository's code) but travels
+    with the working tree, so ``--impl reference`` can import the real reference on a
+    machine that has no checkout of it.  Returns a one-line description of what was done.
+    """
+
+    import shutil
+
+    root = Path(source)
+    missing = [name for name in REFERENCE_PACKAGES if not (root / name / "__init__.py").exists()]
+    if missing:
+        return f"not prepared: {root} has no {', '.join(missing)} package"
+    REFERENCE_COPY.mkdir(parents=True, exist_ok=True)
+    for name in REFERENCE_PACKAGES:
+        target = REFERENCE_COPY / name
+        if target.exists():
+            shutil.rmtree(target)
+        shutil.copytree(root / name, target, ignore=shutil.ignore_patterns("__pycache__", "*.so"))
+    return f"copied {', '.join(REFERENCE_PACKAGES)} from {root} to {REFERENCE_COPY}"
+
+
+def reference_forward():
+    """``(callable, kind, note)``: the reference's ``b300_moe_forward`` from ``baseline/_ref``
+    when that copy exists (kind ``"reference"``), else the oracle's restatement of the same
+    torch path (kind ``"port"``)."""
+
+    if (REFERENCE_COPY / "fastpath" / "__init__.py").exists():
+        try:
+            if str(REFERENCE_COPY) not in sys.path:
+                sys.path.insert(0, str(REFERENCE_COPY))
+            import fastpath  # the reference package, unmodified
+
+            def run(hidden, ids, weights, gate_up, down):
+                return fastpath.b300_moe_forward(hidden, ids, weights, gate_up, down,
+                                                 num_experts=EXPERTS, top_k=TOP_K,
+                                                 backend="torch")
+
+            return run, "reference", ("fastpath.b300_moe_forward(backend='torch') imported from "
+                                      "baseline/_ref (unmodified copy of the reference package)")
+        except Exception as error:  # say why, then time the restatement
+            note = f"baseline/_ref could not be imported ({type(error).__name__}: {error}); "
+    else:
+        note = "no baseline/_ref on this machine; "
     from oracle import moe_oracle
 
-    hidden, ids, weights = case_host
-    out, _ = moe_oracle.routed_moe(hidden, ids, weights, gate_up_cpu, down_cpu,
-                                   num_experts=EXPERTS, top_k=TOP_K,
-                                   compute_dtype=torch.bfloat16)
-    return out
+    def run_port(hidden, ids, weights, gate_up, down):
+        out, _ = moe_oracle.routed_moe(hidden, ids, weights, gate_up, down, num_experts=EXPERTS,
+                                       top_k=TOP_K, compute_dtype=torch.bfloat16)
+        return out
+
+    return run_port, "port", note + "timed the restatement in oracle/moe_oracle.py"
 
 
-def cpu_baseline(gate_up, down, cases, budget_s: float) -> dict[str, object]:
-    """The reference's BF16 torch path (restated) on the host cores, bounded sample."""
+def host_threads() -> int:
+    """All the cores this process may run on (torchrun exports OMP_NUM_THREADS=1)."""
 
-    gate_up_cpu, down_cpu = gate_up.cpu(), down.cpu()
-    per_t = {}
-    reps = 3
-    t_start = time.perf_counter()
-    for T in cases:
-        host = tuple(t.clone() for t in cases[T]["host"])
-        _cpu_forward(host, gate_up_cpu, down_cpu)
-        times = []
-        for _ in range(reps):
+    try:
+        count = max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        count = max(1, os.cpu_count() or 1)
+    try:
+        torch.set_num_threads(count)
+    except RuntimeError:
+        pass
+    return torch.get_num_threads()
+
+
+def time_cpu_path(run, cases_host, gate_up_cpu, down_cpu, warmup: int, reps: int,
+                  budget_s: float | None = None) -> tuple[dict[int, list[float]], float]:
+    """The one timing loop of both CPU legs: ``warmup`` untimed passes over the sweep, then
+    ``reps`` timed passes (``time.perf_counter_ns`` around each forward).  Returns the
+    samples in microseconds per T and the wall time of the timed passes."""
+
+    for _ in range(warmup):
+        for T in cases_host:
+            run(*cases_host[T], gate_up_cpu, down_cpu)
+    samples: dict[int, list[float]] = {T: [] for T in cases_host}
+    start = time.perf_counter()
+    for _ in range(reps):
+        for T in cases_host:
             t0 = time.perf_counter_ns()
-            _cpu_forward(host, gate_up_cpu, down_cpu)
-            times.append((time.perf_counter_ns() - t0) / 1e3)
-        per_t[str(T)] = round(percentile(sorted(times), 0.5), 1)
-        if time.perf_counter() - t_start > budget_s:
+            run(*cases_host[T], gate_up_cpu, down_cpu)
+            samples[T].append((time.perf_counter_ns() - t0) / 1e3)
+        if budget_s is not None and time.perf_counter() - start > budget_s:
             break
-    done = [per_t[k] for k in per_t]
+    return samples, time.perf_counter() - start
+
+
+def cpu_baseline(gate_up_cpu, down_cpu, cases, budget_s: float) -> dict[str, object]:
+    """The reference's BF16 torch path on the host cores, bounded sample (our arm's leg)."""
+
+    run, kind, note = reference_forward()
+    cores = host_threads()
+    cases_host = {T: tuple(t.clone() for t in cases[T]["host"]) for T in cases}
+    samples, _ = time_cpu_path(run, cases_host, gate_up_cpu, down_cpu, warmup=2, reps=5,
+                               budget_s=budget_s)
+    per_t = {str(T): round(percentile(sorted(v), 0.5), 1) for T, v in samples.items() if v}
+    done = list(per_t.values())
     return {
         "value": round(sum(done) / len(done), 1),
         "unit": "us",
-        "cores": torch.get_num_threads(),
+        "cores": cores,
         "host_cpus": os.cpu_count(),
-        "kind": "port",
-        "sample": f"1 warm-up + {reps} forwards at each T in {sorted(int(k) for k in per_t)} of "
-                  "the same workload, BF16 torch ops as the reference's torch backend",
+        "kind": kind,
+        "note": note,
+        "sample": f"2 warm-up + up to 5 forwards at each T in {sorted(int(k) for k in per_t)} of "
+                  "the same workload (BF16 tensors, the reference's torch backend), "
+                  f"bounded to {budget_s:.0f} s",
         "per_T_p50_us": per_t,
     }
 
@@ -1043,12 +1343,8 @@ def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
         return None
     from b200moe import workloads
 
-    # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm runs on rank 0 alone and is
-    # meant to use all the host cores the process may run on
-    try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except (AttributeError, RuntimeError):
-        pass
+    run, kind, note = reference_forward()
+    cores = host_threads()
     gate_up, down = workloads.make_expert_weights(EXPERTS, HIDDEN, INTER, seed=1236, std=0.02,
                                                   device="cpu")
     cases = {}
@@ -1056,20 +1352,12 @@ def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
         cases[T] = (workloads.make_hidden(T, HIDDEN, seed=1234),
                     workloads.make_routing(T, EXPERTS, TOP_K, ROUTING, 1235),
                     workloads.make_routing_weights(T, TOP_K, WEIGHT_KIND, 1235))
-    samples = {T: [] for T in SWEEP}
-    for _ in range(args.warmup):
-        for T in SWEEP:
-            _cpu_forward(cases[T], gate_up, down)
-    wall0 = time.perf_counter()
-    for _ in range(args.steps):
-        for T in SWEEP:
-            t0 = time.perf_counter_ns()
-            _cpu_forward(cases[T], gate_up, down)
-            samples[T].append((time.perf_counter_ns() - t0) / 1e3)
-    wall = time.perf_counter() - wall0
+    samples, wall = time_cpu_path(run, cases, gate_up, down, warmup=max(args.warmup, 1),
+                                  reps=args.steps)
     p50s = [percentile(sorted(samples[T]), 0.5) for T in SWEEP]
     value = round(sum(p50s) / len(p50s), 1)
-    sample = "every T of the sweep, whole workload, BF16 torch ops on the host CPU"
+    sample = ("every T of the sweep, whole workload, BF16 tensors through the reference's torch "
+              "backend on the host CPU")
     return {
         "impl": "reference",
         "metric": METRIC,
@@ -1086,8 +1374,8 @@ def run_reference(args: argparse.Namespace) -> dict[str, object] | None:
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": list(SWEEP),
                    "step": "one forward at each T of the sweep"},
-        "cpu_baseline": {"value": value, "unit": "us", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "us", "cores": cores, "kind": kind,
+                         "note": note, "sample": sample},
         "e2e": {"value": value, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "per_T_p50_us": {str(T): round(p, 1) for T, p in zip(SWEEP, p50s)},
@@ -1118,11 +1406,21 @@ def main() -> int:
     parser.add_argument("--library-gemm-baseline", action="store_true",
                         help="N=1: also time torch._grouped_mm and the per-expert matmul loop "
                              "(the library GEMMs the reference's compiled path calls)")
+    parser.add_argument("--parity-only", action="store_true",
+                        help="N > 1: run the parity check of every token layout and transport "
+                             "against the oracle, print it and exit without timing anything")
+    parser.add_argument("--prepare-reference", nargs="?", const="/root/reference", default=None,
+                        metavar="CHECKOUT",
+                        help="copy the reference's fastpath/ and baseline/ packages from CHECKOUT "
+                             "into baseline/_ref (for --impl reference) and exit")
     args = parser.parse_args()
+    if args.prepare_reference is not None:
+        print(prepare_reference(args.prepare_reference))
+        return 0
     apply_config(args.config)
     if args.weights == "fp8":
         args.no_cpu_baseline = True  # the CPU port restates the reference's BF16 layer
-    if args.config in ("wide", "deepseek", "deepseek_hotspot"):
+    if args.config in ("wide", "wide_e16", "deepseek", "deepseek_hotspot"):
         args.no_cpu_baseline = True  # ~21 GiB of weights: the CPU port is not timed on these
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps

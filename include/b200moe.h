@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 4
+#define B200MOE_ABI_VERSION 5
 
 /* host-side contract errors */
 #define B200MOE_E_NULL        (-1)  /* a required pointer is NULL */
@@ -69,6 +69,13 @@ extern "C" {
  * which names quantised expert weights as future work (docs/goal_1b_report.md:313-314);
  * the "cutlass_nvfp4" name keeps failing loudly (b200moe_nvfp4_available() == 0). */
 #define B200MOE_FLAG_FP8_WEIGHTS   0x8u
+/* hidden_states, expert_indices, expert_weights and output live in pinned host memory that
+ * the kernels read and write over PCIe.  b200moe_forward then keeps the regular kernel order
+ * (routing, gather, gate+up, down, combine) whatever the size of the call. */
+#define B200MOE_FLAG_HOST_IO       0x10u
+/* b200moe_forward stops after the down projection: the caller combines the rows itself
+ * (b200moe_ep_combine_reduce on an expert-parallel rank).  `output` is not used. */
+#define B200MOE_FLAG_SKIP_COMBINE  0x20u
 /* With B200MOE_FLAG_FP8_WEIGHTS the staged entry points keep their meaning, with two
  * details: b200moe_gather also writes the gathered rows as E4M3 planes into scratch, which
  * b200moe_gate_up_swiglu consumes; b200moe_down first turns the activation rows into planes
@@ -188,7 +195,12 @@ int b200moe_routing(const B200MoeArgs* args, void* stream);
  *  - The segment schedule stays inside the library, so the GEMM stages cannot
  *    follow this entry point; it serves callers that need the routing tensors.
  *    An expert id outside [0, E) shows up as reverse_mapping == -1 for that
- *    assignment and as a shorter count total.
+ *    assignment and as a shorter count total (the status word lives in the
+ *    library's array, so B200MOE_STATUS_BAD_EXPERT_ID cannot be read back).
+ *  - Fields it does not read: scratch, scratch_bytes, flags (in particular
+ *    B200MOE_FLAG_LOCAL_EXPERTS and B200MOE_FLAG_FP8_WEIGHTS), expert_id_base,
+ *    ep_wait_flags / ep_world / ep_epoch / ep_wait_limit_us.  It always routes the
+ *    global id range [0, num_experts) with 128-row segments.
  */
 int b200moe_routing_static(const B200MoeArgs* args, void* stream);
 
@@ -258,6 +270,14 @@ int b200moe_combine_bf16(const void* expert_rows /*[T*K,H] bf16*/,
  * The whole layer: stages 1..5 enqueued back to back on `stream` by one call.
  * Replaces _call_compiled_bf16 (fastpath/b300_moe.py:620-760).  No allocation,
  * no synchronisation, no host read-back.
+ *
+ * Kernel order.  Regular: routing, gather, gate+up, down, combine.  A BF16 call with at
+ * most 32 assignments (T * top_k) runs in small-call order instead: the gate+up GEMM is
+ * the first kernel -- every block finds its work unit from expert_indices with a few warp
+ * votes, fetches its token rows from hidden_states itself and, for the first tile of each
+ * expert, also writes them to permuted_hidden -- the routing kernel runs beside it, and
+ * down and combine follow.  Results and every output buffer are the same in both orders;
+ * small-call order takes the routing and gather launches off the critical path.
  */
 int b200moe_forward(const B200MoeArgs* args, void* stream);
 
@@ -290,11 +310,37 @@ typedef struct B200MoeEpReduceArgs {
   void*    output;                   /* [T,H] bf16 */
   uint32_t* status;                  /* device status word, or NULL */
   uint32_t flags;                    /* B200MOE_FLAG_PDL */
+  /* b200moe_ep_combine_reduce only */
+  int32_t  first_token;              /* first of the num_tokens rows this rank outputs */
+  unsigned int* block_counter;       /* one zero-initialised uint32 in this device's memory */
 } B200MoeEpReduceArgs;
 
 #define B200MOE_EP_MAX_WORLD 8
 
 int b200moe_ep_reduce(const B200MoeEpReduceArgs* args, void* stream);
+
+/*
+ * Stage 5 of an expert-parallel rank: combine and cross-rank reduce in ONE kernel.  No
+ * counterpart in the reference.  Follows a b200moe_forward with B200MOE_FLAG_LOCAL_EXPERTS |
+ * B200MOE_FLAG_SKIP_COMBINE on the same `layer` arguments (expert_indices holding the
+ * GLOBAL ids of all layer->num_tokens tokens, num_experts the experts of this rank).
+ *
+ * Every block computes this rank's routing-weighted sum for its token from the down
+ * projection's FP32 rows (as b200moe_combine does), stores it to this rank's partial
+ * buffer only if the rank owns an expert of the token, and the last block publishes
+ * `epoch` into flags[rank] of every rank.  Blocks of the rows this rank outputs
+ * (first_token .. first_token + num_tokens) then wait, bounded as in b200moe_ep_reduce,
+ * until every rank has published, add the partial rows of the ranks that own an expert of
+ * the token in rank order -- found from the token's ids, so a token routed to K experts
+ * reads at most K rows instead of `world` -- and round once to BF16.  On a timeout the rows
+ * are written as zeros and B200MOE_STATUS_PEER_TIMEOUT is set.
+ *
+ * partial_ptrs[r] is the start of rank r's FP32 [layer->num_tokens, H] buffer (not offset by
+ * first_token).  Calls with more than 8 blocks per SM (T * ceil(H / 1024) > 8 * SMs) run as
+ * the two separate kernels instead, with the same result.
+ */
+int b200moe_ep_combine_reduce(const B200MoeArgs* layer, const B200MoeEpReduceArgs* ep,
+                              void* stream);
 
 /*
  * Expert-parallel dispatch of sharded tokens over NVLink peer memory.  No counterpart
@@ -380,10 +426,8 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              1 = 128 B, 2 = 256 B (default)
  *   B200MOE_TUNE_EVICT_FIRST   1: weight tiles are loaded with an L2
  *                              evict-first hint (default 0)
- *   B200MOE_TUNE_EARLY_START   how early the gate+up grid starts: 0 after routing
- *                              (default), 1 at once, each block deriving its work
- *                              unit from the expert ids itself, 2 as 1 and blocks
- *                              with <= 32 rows also fetch their token rows themselves
+ *   B200MOE_TUNE_SMALL_CALL_MAX  most assignments (T * top_k) for which b200moe_forward
+ *                              uses small-call order (0..32, default 32; 0 = never)
  *   B200MOE_TUNE_DOWN_SPLITS   force the split-K factor of the down projection (1..8;
  *                              0 = chosen on the device from the routing result)
  *   B200MOE_TUNE_FP8_SEG_ROWS  longest segment of the FP8-weight path: 16, 32, 48 or 64 rows
@@ -395,7 +439,7 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
 #define B200MOE_TUNE_STAGE_KB     1
 #define B200MOE_TUNE_L2_PROMOTION 2
 #define B200MOE_TUNE_EVICT_FIRST  3
-#define B200MOE_TUNE_EARLY_START  4
+#define B200MOE_TUNE_SMALL_CALL_MAX 4
 #define B200MOE_TUNE_DOWN_TARGET  5
 #define B200MOE_TUNE_DOWN_SPLITS  6
 #define B200MOE_TUNE_FP8_SEG_ROWS 7

@@ -98,7 +98,7 @@ def test_native_backends_on_cpu_tensors_raise_and_never_fall_back(backend) -> No
 
 
 def test_torch_backend_is_not_an_execution_path() -> None:
-    with pytest.raises(RuntimeError, match="oracle"):
+    with pytest.raises(RuntimeError, match="not an execution path"):
         _call(_case(), backend="torch", quant_mode="none")
 
 

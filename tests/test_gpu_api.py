@@ -151,7 +151,7 @@ def test_explicit_failures_on_device(cuda_device) -> None:
     tensors = _case(cuda_device)
     with pytest.raises(RuntimeError, match="NVFP4|nvfp4"):
         b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="cutlass_nvfp4")
-    with pytest.raises(RuntimeError, match="oracle"):
+    with pytest.raises(RuntimeError, match="not an execution path"):
         b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="torch")
     odd = _case(cuda_device, hidden=30 * 2 + 2, inter=46 * 2 + 2)  # 62, 94: not multiples of 8
     workspace = B300MoEWorkspace(device=cuda_device)
@@ -270,7 +270,7 @@ def test_peer_reduce_kernel_with_all_ranks_buffers_on_one_gpu(cuda_device) -> No
 
 def test_peer_reduce_wait_is_bounded_and_reports_a_missing_peer(cuda_device) -> None:
     """A peer that never publishes: the wait gives up after its limit, sets the status
-    bit and leaves the output alone; the context stays usable."""
+    bit and writes zeros; the context stays usable."""
 
     world, T, H = 2, 3, 64
     partials = [torch.ones(T, H, device=cuda_device) for _ in range(world)]
@@ -280,13 +280,123 @@ def test_peer_reduce_wait_is_bounded_and_reports_a_missing_peer(cuda_device) -> 
     _ep_reduce_call(cuda_device, partials, flags, rank=0, epoch=1, limit_us=2000, status=status,
                     output=output)
     assert int(status.item()) & 0x4
-    assert float(output.float().min()) == 7.0 and float(output.float().max()) == 7.0
+    # the rows that could not be completed read as zeros, never as stale memory
+    assert float(output.float().min()) == 0.0 and float(output.float().max()) == 0.0
     flags[0][1] = 1  # the peer arrives: the same call now completes
     status.zero_()
     _ep_reduce_call(cuda_device, partials, flags, rank=0, epoch=1, limit_us=2000, status=status,
                     output=output)
     assert int(status.item()) == 0
     assert float(output.float().min()) == 2.0
+
+
+def _emulated_ranks(device, world, T, H, I, E, K, seed=9, routing="zipf"):
+    """Every rank's local forward up to the down projection, one after another on one GPU."""
+
+    from b200moe import B300MoEWorkspace, workloads
+    from b200moe.expert_parallel import expert_range, local_partial_forward
+
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing=routing, weight_kind="raw", std=None, device=device, seed=seed)
+    ranks = []
+    for rank in range(world):
+        base, count = expert_range(rank, world, E)
+        workspace = B300MoEWorkspace(device=device)
+        _, call = local_partial_forward(
+            hidden, ids, weights, gate_up[base:base + count].contiguous(),
+            down[base:base + count].contiguous(), top_k=K, expert_id_base=base,
+            num_experts_global=E, workspace=workspace, skip_combine=True)
+        ranks.append((workspace, call))
+    torch.cuda.synchronize(device)
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gate_up.cpu(),
+                                   down.cpu(), num_experts=E, top_k=K)
+    return ranks, ref
+
+
+def _combine_reduce_call(device, ranks, rank, partials, flags, counter, epoch, first, rows,
+                         limit_us=0):
+    import ctypes
+
+    from b200moe import _lib
+
+    world = len(ranks)
+    workspace, (layer_args, _keep) = ranks[rank]
+    H = partials[0].shape[1]
+    args = _lib.B200MoeEpReduceArgs()
+    p_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in partials])
+    f_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in flags])
+    args.partial_ptrs = ctypes.cast(p_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.flag_ptrs = ctypes.cast(f_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.world, args.rank, args.hidden_size = world, rank, H
+    args.num_tokens, args.first_token = rows, first
+    args.epoch, args.wait_limit_us = epoch, limit_us
+    output = torch.full((rows, H), 7.0, dtype=torch.bfloat16, device=device)
+    args.output = output.data_ptr()
+    args.status = workspace.scratch.data_ptr()
+    args.block_counter = counter.data_ptr()
+    args.flags = 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    code = _lib.load().b200moe_ep_combine_reduce(ctypes.byref(layer_args), ctypes.byref(args),
+                                                 stream)
+    _lib.check(code, "b200moe_ep_combine_reduce")
+    torch.cuda.synchronize(device)
+    return output
+
+
+@pytest.mark.parametrize("spec", [(4, 16, 256, 384, 8, 2), (8, 64, 512, 256, 16, 4),
+                                  (2, 1300, 64, 96, 8, 2)],
+                         ids=["world4", "world8", "two_kernel_path_T1300"])
+def test_fused_combine_reduce_with_all_ranks_buffers_on_one_gpu(spec, cuda_device) -> None:
+    """The one-kernel combine + cross-rank reduce of an expert-parallel rank, with every
+    rank's buffers on this GPU.  Kernels of different ranks are never in flight together
+    here: every flag is pre-set to the epoch, and the ranks run twice in turn -- the first
+    round leaves every rank's partial rows in its buffer, the second reads them all.  The
+    result must meet the oracle bar, be identical on every rank, and a sharded caller's rows
+    must equal the same rows of the replicated result.  The third case is large enough to
+    take the two-kernel path inside the same entry point."""
+
+    world, T, H, I, E, K = spec
+    ranks, ref = _emulated_ranks(cuda_device, world, T, H, I, E, K)
+    partials = [torch.full((T, H), float("nan"), device=cuda_device) for _ in range(world)]
+    flags = [torch.full((8,), 3, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    outputs = None
+    for _round in range(2):
+        outputs = [_combine_reduce_call(cuda_device, ranks, r, partials, flags, counter, 3, 0, T)
+                   for r in range(world)]
+    for r in range(world):
+        assert ranks[r][0].status() == 0
+        assert torch.equal(outputs[r], outputs[0])
+    assert int(counter.item()) == 0  # the last block of every launch reset it
+    err = moe_oracle.relative_max_error(outputs[0].float().cpu(), ref)
+    assert err <= 2e-2, err
+    # a sharded caller: rank 1 outputs only its own T/world rows
+    per = T // world
+    mine = _combine_reduce_call(cuda_device, ranks, 1, partials, flags, counter, 3, per, per)
+    assert torch.equal(mine, outputs[0][per:2 * per])
+
+
+def test_fused_combine_reduce_reports_a_missing_peer(cuda_device) -> None:
+    """A peer that never publishes its flag: the wait runs out after its limit, the rows come
+    back as zeros with the status bit set, and the same call completes once the flag is there."""
+
+    world, T, H, I, E, K = 2, 4, 128, 256, 4, 2
+    ranks, _ = _emulated_ranks(cuda_device, world, T, H, I, E, K, routing="uniform")
+    partials = [torch.zeros(T, H, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = _combine_reduce_call(cuda_device, ranks, 0, partials, flags, counter, 1, 0, T,
+                               limit_us=2000)
+    assert ranks[0][0].status() & 0x4
+    assert not out.any()
+    with pytest.raises(RuntimeError):
+        ranks[0][0].raise_for_status()
+    assert [int(f[0]) for f in flags] == [1, 1]  # rank 0 did publish its own epoch
+    flags[0][1] = 1
+    ranks[0][0].scratch[:4].zero_()
+    out = _combine_reduce_call(cuda_device, ranks, 0, partials, flags, counter, 1, 0, T,
+                               limit_us=2000)
+    assert ranks[0][0].status() == 0
 
 
 @pytest.mark.parametrize("use_pdl", [False, True])
@@ -360,38 +470,117 @@ def test_router_then_layer_end_to_end(cuda_device) -> None:
     assert moe_oracle.relative_max_error(out.float().cpu(), ref) <= 2e-2
 
 
-def test_early_start_modes_agree_bitwise_and_timeline_is_ordered(cuda_device) -> None:
-    """The three ways the gate+up grid can start (after routing; at once with its own
-    derivation of the work units; additionally fetching its token rows itself) are
-    scheduling choices only: outputs are bit-identical.  The in-kernel timeline reports the
-    five kernels in dependency order."""
+def _forward_with_buffers(tensors, E, K, cuda_device, **kwargs):
+    """One forward on a fresh workspace; returns the output, the metadata and copies of the
+    public buffers a caller can observe."""
+
+    from b200moe import B300MoEWorkspace, b300_moe_forward
+
+    workspace = B300MoEWorkspace(device=cuda_device)
+    out, meta = b300_moe_forward(*tensors, num_experts=E, top_k=K, workspace=workspace,
+                                 return_metadata=True, **kwargs)
+    torch.cuda.synchronize(cuda_device)
+    rows = tensors[1].numel()
+    valid = int(meta["expert_counts"].sum())
+    buffers = {name: workspace.buffers[name][:rows].clone()
+               for name in ("permuted_hidden", "swiglu_output", "permuted_token_indices",
+                            "permuted_expert_indices", "permuted_weights", "expert_output")}
+    return out, meta, buffers, valid, workspace
+
+
+SMALL_CALL_CASES = [
+    # T, H, I, E, K, routing
+    (1, 512, 768, 8, 2, "uniform"),
+    (4, 512, 768, 32, 8, "concentrated"),   # 32 assignments, 4 rows on each of 8 experts
+    (16, 256, 384, 8, 2, "zipf"),           # 32 assignments
+    (5, 512, 768, 16, 4, "zipf"),
+    (3, 1024, 256, 256, 8, "uniform"),
+    (2, 2880, 2880, 32, 8, "concentrated"),  # ragged tiles (I, H not multiples of 128)
+    (1, 4096, 14336, 8, 2, "uniform"),      # Mixtral-shaped, one token
+]
+
+
+@pytest.mark.parametrize("spec", SMALL_CALL_CASES, ids=lambda s: "T{}_H{}_I{}_E{}_K{}_{}".format(*s))
+@pytest.mark.parametrize("use_pdl", [True, False])
+def test_small_call_order_equals_regular_order_bitwise(spec, use_pdl, cuda_device) -> None:
+    """Calls with at most 32 assignments run gate+up first and the routing kernel beside it.
+    That is a scheduling choice only: output, routing tensors and every public buffer are
+    bit-identical to the regular order, and the output meets the oracle bar."""
+
+    from b200moe import _lib, workloads
+    from oracle import moe_oracle
+
+    T, H, I, E, K, routing = spec
+    tensors = workloads.make_case(T, H, I, E, K, routing=routing, std=0.02 if H >= 2048 else None,
+                                  device=cuda_device, seed=77 + T)
+    lib = _lib.load()
+    results = {}
+    try:
+        for most in (0, 32):
+            assert lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, most) == 0
+            results[most] = _forward_with_buffers(tensors, E, K, cuda_device, use_pdl=use_pdl,
+                                                  check_status=True)
+    finally:
+        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, 32)
+    (out0, meta0, buf0, valid0, _), (out1, meta1, buf1, valid1, ws1) = results[0], results[32]
+    assert torch.equal(out0, out1)
+    for key in ("expert_counts", "expert_offsets", "permutation", "reverse_mapping"):
+        assert torch.equal(meta0[key], meta1[key]), key
+    assert valid0 == valid1 == T * K
+    for name in buf0:
+        assert torch.equal(buf0[name], buf1[name]), name
+    timeline = ws1.timeline()
+    assert "gather" not in timeline  # the gate+up blocks did the gather
+    assert timeline["gate_up"][0] <= timeline["routing"][0] + 50.0
+    assert timeline["gate_up"][1] <= timeline["down"][1] <= timeline["combine"][1]
+    assert timeline["down_first_data"][0] >= timeline["gate_up"][1]
+    if H < 2048:  # the large shape is covered against the oracle in test_gpu_layer.py
+        cpu = [t.float().cpu() if t.is_floating_point() else t.cpu() for t in tensors]
+        ref, _ = moe_oracle.routed_moe(*cpu, num_experts=E, top_k=K)
+        assert moe_oracle.relative_max_error(out1.float().cpu(), ref) <= 2e-2
+
+
+def test_small_call_order_with_dropped_ids_and_local_experts(cuda_device) -> None:
+    """Small-call order under the two conditions that change which rows exist: an id outside
+    [0, E) (row dropped, status bit, zero-filled gather row) and an expert-parallel rank's
+    local id range (foreign ids dropped silently)."""
 
     from b200moe import B300MoEWorkspace, _lib, b300_moe_forward, workloads
+    from b200moe.expert_parallel import local_partial_forward
 
     lib = _lib.load()
-    cases = [
-        workloads.make_case(5, 512, 768, 16, 4, routing="zipf", std=None, device=cuda_device),
-        workloads.make_case(64, 256, 384, 8, 8, routing="concentrated", std=None,
-                            device=cuda_device),  # 64 rows per expert: above the own-rows limit
-    ]
+    T, H, I, E, K = 6, 256, 384, 8, 4
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        T, H, I, E, K, routing="uniform", std=None, device=cuda_device, seed=5)
+    bad = ids.clone()
+    bad[1, 2] = E + 3
+    bad[4, 0] = -1
+    outs = {}
     try:
-        for tensors in cases:
-            E, K = tensors[3].shape[0], tensors[1].shape[1]
-            outputs = []
-            for mode in (0, 1, 2):
-                assert lib.b200moe_tune(_lib.TUNE_EARLY_START, mode) == 0
-                workspace = B300MoEWorkspace(device=cuda_device)
-                outputs.append(b300_moe_forward(*tensors, num_experts=E, top_k=K,
-                                                workspace=workspace, check_status=True))
-                timeline = workspace.timeline()
-                assert set(timeline) >= {"routing", "gather", "gate_up", "down", "combine"}
-                assert timeline["routing"][0] == 0.0
-                assert timeline["gate_up"][1] <= timeline["down"][1] <= timeline["combine"][1]
-                assert timeline["down_first_data"][0] >= timeline["gate_up"][1]
-                assert 0.0 < timeline["combine"][1] < 1e5
-            assert torch.equal(outputs[0], outputs[1]) and torch.equal(outputs[0], outputs[2])
+        for most in (0, 32):
+            lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, most)
+            ws = B300MoEWorkspace(device=cuda_device)
+            out = b300_moe_forward(hidden, bad, weights, gate_up, down, num_experts=E, top_k=K,
+                                   workspace=ws)
+            torch.cuda.synchronize(cuda_device)
+            assert ws.status() & _lib.STATUS_BAD_EXPERT_ID
+            rows = T * K
+            outs[most] = (out, ws.buffers["permuted_hidden"][:rows].clone(),
+                          ws.buffers["reverse_mapping"][:rows].clone())
+            # the two rows past the valid ones are zero, as the gather kernel leaves them
+            assert not ws.buffers["permuted_hidden"][rows - 2:rows].any()
+            # one rank of two: experts [4, 8) only
+            ws2 = B300MoEWorkspace(device=cuda_device)
+            part, _ = local_partial_forward(hidden, ids, weights, gate_up[4:].contiguous(),
+                                            down[4:].contiguous(), top_k=K, expert_id_base=4,
+                                            num_experts_global=E, workspace=ws2)
+            torch.cuda.synchronize(cuda_device)
+            assert ws2.status() == 0
+            outs[most] += (part.clone(),)
     finally:
-        lib.b200moe_tune(_lib.TUNE_EARLY_START, 0)
+        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, 32)
+    for a, b in zip(outs[0], outs[32]):
+        assert torch.equal(a, b)
 
 
 def test_peer_dispatch_kernel_and_routing_wait_on_one_gpu(cuda_device) -> None:
@@ -496,7 +685,7 @@ def test_legacy_dispatch_and_combine(tokens, experts, top_k, cuda_device) -> Non
     expected = (ordered.reshape(tokens, top_k, H) * weights.cpu().float().unsqueeze(-1)).sum(1)
     torch.testing.assert_close(out.float().cpu(), expected, atol=1e-2 * max(1.0, top_k ** 0.5),
                                rtol=1e-2)
-    with pytest.raises(RuntimeError, match="oracle"):
+    with pytest.raises(RuntimeError, match="not an execution path"):
         dispatch_tokens(hidden, ids, experts, backend="torch")
     with pytest.raises(TypeError, match="int64"):
         dispatch_tokens(hidden, ids.int(), experts)

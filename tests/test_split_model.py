@@ -46,7 +46,7 @@ def test_split_model_keeps_its_measured_choices(tmp_path) -> None:
         "  return 0;\n}\n"
     )
     binary = tmp_path / "split_model"
-    subprocess.run(["nvcc", "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", str(CSRC),
+    subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(CSRC),
                     "-I", str(REPO / "include"), "-o", str(binary), str(source)],
                    check=True, capture_output=True)
     lines = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.split("\n")

@@ -6,7 +6,9 @@ GPU, a plugin interface that forbids allocation after start-up.  It keeps the
 kernel's scratch inside the library.  This test drives both entry points through
 the C ABI on the same inputs and requires identical tensors, twice in a row, the
 second time with different routes so that anything left over from the first call
-would show.  Routing is integer work: the comparison is exact.
+would show.  Routing is integer work: the comparison is exact.  The same outputs are also
+compared with the CPU oracle's ``group_tokens`` directly, and a repeated call must leave the
+device's free memory and PyTorch's allocation counter where they were.
 
 The file name sorts last on purpose: if this test fails, a run that stops at the
 first failure has already run everything else.
@@ -84,11 +86,62 @@ def _assert_same(expected, outputs, label):
         assert torch.equal(outputs[key], expected[key]), f"{label}: {key} differs"
 
 
+def _assert_matches_oracle(outputs, tokens, experts, top_k, pattern, seed, label):
+    """The static entry point's tensors against the oracle's grouping of the same ids."""
+
+    import numpy as np
+
+    from b200moe import workloads
+    from oracle import moe_oracle
+
+    ids = workloads.make_case(tokens, 64, 96, experts, top_k, routing=pattern, seed=seed,
+                              std=None)[1]
+    want = moe_oracle.group_tokens(ids, experts)
+    for key in ("expert_counts", "expert_offsets", "permutation", "reverse_mapping",
+                "permuted_token_indices", "permuted_expert_indices"):
+        assert np.array_equal(outputs[key].cpu().numpy(), getattr(want, key)), f"{label}: {key}"
+    assert np.array_equal(outputs["expert_offsets_i32"].cpu().numpy(),
+                          want.expert_offsets[1:].astype(np.int32)), label
+
+
 def test_static_routing_matches_regular_routing_on_two_calls_in_a_row(cuda_device) -> None:
     first = _run_both(cuda_device, tokens=64, experts=32, top_k=8, pattern="zipf", seed=11)
     _assert_same(*first, "first call")
+    _assert_matches_oracle(first[1], 64, 32, 8, "zipf", 11, "first call")
     second = _run_both(cuda_device, tokens=17, experts=16, top_k=2, pattern="empty_half", seed=12)
     _assert_same(*second, "second call")
+    _assert_matches_oracle(second[1], 17, 16, 2, "empty_half", 12, "second call")
+
+
+def test_static_routing_leaves_device_memory_alone(cuda_device) -> None:
+    """The property the entry point exists for: after a first call (which looks up the
+    array's address), another call changes neither the device's free memory nor PyTorch's
+    count of allocated bytes."""
+
+    from b200moe import StagedLayer, _lib, workloads
+
+    hidden, ids, weights, gate_up, down = workloads.make_case(
+        32, 64, 96, 16, 4, routing="uniform", seed=5, std=None, device=cuda_device)
+    layer = StagedLayer(hidden, ids, weights, gate_up, down, num_experts=16, top_k=4)
+    outputs = _routing_outputs(cuda_device, 16, 32 * 4)
+    args = _lib.B200MoeArgs()
+    ctypes.memmove(ctypes.byref(args), ctypes.byref(layer._args), ctypes.sizeof(args))
+    for name, tensor in outputs.items():
+        setattr(args, name, tensor.data_ptr())
+    args.scratch, args.scratch_bytes = None, 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+    lib = _lib.load()
+    _lib.check(lib.b200moe_routing_static(ctypes.byref(args), stream), "b200moe_routing_static")
+    torch.cuda.synchronize(cuda_device)
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    torch_before = torch.cuda.memory_allocated(cuda_device)
+    for _ in range(3):
+        _lib.check(lib.b200moe_routing_static(ctypes.byref(args), stream),
+                   "b200moe_routing_static")
+    torch.cuda.synchronize(cuda_device)
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after == free_before
+    assert torch.cuda.memory_allocated(cuda_device) == torch_before
 
 
 def test_static_routing_state_does_not_leak_between_calls(cuda_device) -> None:
