@@ -28,6 +28,7 @@ FLAG_F32_OUTPUT = 0x4
 FLAG_FP8_WEIGHTS = 0x8
 FLAG_HOST_IO = 0x10
 FLAG_SKIP_COMBINE = 0x20
+FLAG_EP_PUSH = 0x40
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
@@ -56,6 +57,7 @@ EXPORTS = (
     "b200moe_combine_bf16",
     "b200moe_ep_reduce",
     "b200moe_ep_combine_reduce",
+    "b200moe_ep_push_max_blocks",
     "b200moe_ep_push",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
@@ -123,6 +125,9 @@ class B200MoeEpReduceArgs(ctypes.Structure):
         ("flags", ctypes.c_uint32),
         ("first_token", ctypes.c_int32),
         ("block_counter", ctypes.c_void_p),
+        ("inbox_ptrs", ctypes.POINTER(ctypes.c_void_p)),
+        ("inbox_cap_tokens", ctypes.c_int32),
+        ("tokens_per_rank", ctypes.c_int32),
     ]
 
 
@@ -191,6 +196,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200moe_ep_combine_reduce.restype = ctypes.c_int
     lib.b200moe_ep_combine_reduce.argtypes = [args_p, ctypes.POINTER(B200MoeEpReduceArgs),
                                               ctypes.c_void_p]
+    lib.b200moe_ep_push_max_blocks.restype = ctypes.c_int
+    lib.b200moe_ep_push_max_blocks.argtypes = [ctypes.POINTER(ctypes.c_int)]
     lib.b200moe_combine_bf16.restype = ctypes.c_int
     lib.b200moe_combine_bf16.argtypes = [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,

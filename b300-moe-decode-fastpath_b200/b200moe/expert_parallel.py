@@ -76,10 +76,17 @@ class ExpertParallelMoE:
         transport: str = "nccl",
         fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
         wait_limit_us: int = 0,
+        combine: str = "auto",
     ) -> None:
         """``fp8_scales = (gate_up_scale [E_local, 2I], down_scale [E_local, H])`` marks the two
         weight tensors as E4M3 codes (uint8) of the FP8-weight path (``b200moe.fp8``).
-        ``wait_limit_us`` bounds every device-side wait for a peer (0: one second)."""
+        ``wait_limit_us`` bounds every device-side wait for a peer (0: one second).
+        ``combine`` (``transport="p2p"`` only) selects how rows cross the ranks: ``"push"``
+        stores flagged rows into the receivers' inboxes (lowest latency; needs
+        ``2 * world * capacity_tokens * H * 8`` bytes per rank and a grid that is resident at
+        once), ``"pull"`` publishes one flag per rank and lets receivers read the owners' rows
+        (any size), ``"auto"`` takes push when both conditions hold and the inbox stays under
+        512 MiB."""
 
         self.wait_limit_us = int(wait_limit_us)
 
@@ -116,10 +123,36 @@ class ExpertParallelMoE:
         self.transport = transport
         self.capacity_tokens = capacity_tokens
         self._epoch = 0
+        if combine not in ("auto", "push", "pull"):
+            raise ValueError("combine must be 'auto', 'push' or 'pull'")
+        self.combine = "pull"
         if transport == "p2p":
+            self.combine = self._choose_combine(combine)
             self._setup_peer_memory()
 
     # ------------------------------------------------------------------ peer memory
+    def _inbox_bytes(self) -> int:
+        return 2 * self.world * self.capacity_tokens * self.hidden_size * 8
+
+    def _choose_combine(self, wanted: str) -> str:
+        """``"push"`` needs every call's grid (tokens x ceil(H / 1024) blocks) resident at once."""
+
+        if wanted == "pull":
+            return "pull"
+        blocks = ctypes.c_int(0)
+        with torch.cuda.device(self.gate_up.device):
+            _lib.check(_lib.load().b200moe_ep_push_max_blocks(ctypes.byref(blocks)),
+                       "b200moe_ep_push_max_blocks")
+        chunks = (self.hidden_size // 8 + 127) // 128
+        fits = self.capacity_tokens * chunks <= blocks.value
+        if wanted == "push":
+            if not fits:
+                raise ValueError(
+                    f"combine='push' needs capacity_tokens * ceil(H / 1024) <= {blocks.value} "
+                    f"blocks on this GPU, got {self.capacity_tokens * chunks}")
+            return "push"
+        return "push" if fits and self._inbox_bytes() <= (512 << 20) else "pull"
+
     def _setup_peer_memory(self) -> None:
         """Symmetric (peer-mapped) buffers for the native combine: two FP32 partial-output
         buffers used alternately, and one flag word per rank.  Allocated once; every rank
@@ -145,6 +178,18 @@ class ExpertParallelMoE:
             for parity in (0, 1)
         ]
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in flag_handle.buffer_ptrs])
+        self._inbox = self._inbox_ptrs = None
+        if self.combine == "push":
+            # flagged rows land here: [epoch parity][source rank][token][H] words of 8 bytes
+            self._inbox = symm_mem.empty((self._inbox_bytes() // 4,), dtype=torch.int32,
+                                         device=device)
+            self._inbox.zero_()
+            inbox_handle = symm_mem.rendezvous(self._inbox, group)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=self.group)
+            self._inbox_ptrs = (ctypes.c_void_p * self.world)(
+                *[int(p) for p in inbox_handle.buffer_ptrs])
+            self._inbox_handle = inbox_handle
         # dispatch of sharded tokens: gathered activations / ids / weights, two sets
         cap, H, K = self.capacity_tokens, self.hidden_size, self.top_k
         self._g_hidden = symm_mem.empty((2, cap, H), dtype=torch.bfloat16, device=device)
@@ -219,10 +264,16 @@ class ExpertParallelMoE:
             args.wait_limit_us = self.wait_limit_us
             args.block_counter = self._reduce_counter.data_ptr()
             args.flags = _lib.FLAG_PDL if self.use_pdl else 0
+            if self.combine == "push":
+                args.flags |= _lib.FLAG_EP_PUSH
+                args.inbox_ptrs = ctypes.cast(self._inbox_ptrs, ctypes.POINTER(ctypes.c_void_p))
+                args.inbox_cap_tokens = self.capacity_tokens
             self._reduce_args = args
         args.partial_ptrs = ctypes.cast(self._partial_ptrs[parity],
                                         ctypes.POINTER(ctypes.c_void_p))
         args.num_tokens, args.first_token = tokens, first_token
+        # sharded callers output `tokens` rows each; replicated callers all of them
+        args.tokens_per_rank = tokens if tokens != self.last_tokens else 0
         args.epoch = self._epoch & 0xFFFFFFFF
         args.output = output.data_ptr()
         args.status = self.workspace.scratch.data_ptr()

@@ -98,6 +98,17 @@ cudaError_t launch_ep_combine_reduce(const int64_t* reverse_mapping, const void*
                                      unsigned long long wait_limit_ns, unsigned long long* trace,
                                      bool pdl, cudaStream_t stream);
 
+int ep_combine_reduce_resident_blocks(int sm_count);
+int ep_combine_push_resident_blocks(int sm_count);
+cudaError_t launch_ep_combine_push(const int64_t* reverse_mapping, const void* weights,
+                                   const float* slices, const int32_t* sched, void* expert_out,
+                                   const int64_t* ids, void* const* inbox_ptrs,
+                                   void* const* progress_ptrs, void* output, uint32_t* status,
+                                   size_t slice_elems, int cap_tokens, int num_tokens, int top_k,
+                                   int hidden, int experts_per_rank, int world, int rank,
+                                   int first_token, int out_tokens, int tokens_per_rank,
+                                   uint32_t epoch, unsigned long long wait_limit_ns,
+                                   unsigned long long* trace, bool pdl, cudaStream_t stream);
 cudaError_t launch_router_topk(const void* logits, bool logits_f32, int num_tokens,
                                int num_experts, int top_k, int64_t* ids, void* weights_bf16,
                                float* weights_f32, cudaStream_t stream);
@@ -568,7 +579,9 @@ const char* b200moe_error_string(int code) {
     case B200MOE_E_ARCH: return "device is not compute capability 10.0 (sm_100a)";
     case B200MOE_E_UNSUPPORTED: return "not implemented (NVFP4 is never substituted by BF16)";
     case B200MOE_E_LIMIT:
-      return "T * top_k exceeds the 4096 assignments the static routing scratch is sized for";
+      return "the call exceeds a fixed limit of this entry point (b200moe_routing_static: "
+             "4096 assignments; b200moe_ep_combine_reduce with B200MOE_FLAG_EP_PUSH: a grid "
+             "that is resident at once)";
     default: break;
   }
   if (code > 0) return cudaGetErrorString((cudaError_t)code);
@@ -738,9 +751,19 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* a, void* stream) {
                                static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_ep_push_max_blocks(int* blocks) {
+  if (!blocks) return B200MOE_E_NULL;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  *blocks = ep_combine_push_resident_blocks(dev.sm_count);
+  return 0;
+}
+
 int b200moe_ep_combine_reduce(const B200MoeArgs* a, const B200MoeEpReduceArgs* e, void* stream) {
-  if (!e || !e->partial_ptrs || !e->flag_ptrs || !e->output || !e->block_counter)
-    return B200MOE_E_NULL;
+  if (!e || !e->flag_ptrs || !e->output) return B200MOE_E_NULL;
+  const bool push = (e->flags & B200MOE_FLAG_EP_PUSH) != 0;
+  if (push ? !e->inbox_ptrs : (!e->partial_ptrs || !e->block_counter)) return B200MOE_E_NULL;
   Ctx c;
   int rc = prepare(a, stream, &c);
   if (rc) return rc;
@@ -752,18 +775,36 @@ int b200moe_ep_combine_reduce(const B200MoeArgs* a, const B200MoeEpReduceArgs* e
   if (!aligned16(e->output) || (a->expert_output && !aligned16(a->expert_output)))
     return B200MOE_E_ALIGN;
   for (int r = 0; r < e->world; ++r) {
-    if (!e->partial_ptrs[r] || !e->flag_ptrs[r]) return B200MOE_E_NULL;
-    if (!aligned16(e->partial_ptrs[r])) return B200MOE_E_ALIGN;
+    const void* data = push ? e->inbox_ptrs[r] : e->partial_ptrs[r];
+    if (!data || !e->flag_ptrs[r]) return B200MOE_E_NULL;
+    if (!aligned16(data)) return B200MOE_E_ALIGN;
   }
   const unsigned long long limit_ns =
       (e->wait_limit_us ? (unsigned long long)e->wait_limit_us : 1000000ull) * 1000ull;
   const bool pdl = (e->flags & B200MOE_FLAG_PDL) != 0;
   const int chunks = (a->hidden_size / 8 + 127) / 128;
   const size_t slice_elems = (size_t)a->rows_cap * a->hidden_size;
+  if (push) {
+    if (e->inbox_cap_tokens < a->num_tokens || e->epoch == 0u) return B200MOE_E_SHAPE;
+    if (e->tokens_per_rank < 0 ||
+        (e->tokens_per_rank > 0 && (long long)e->tokens_per_rank * e->world < a->num_tokens))
+      return B200MOE_E_SHAPE;
+    // blocks push before they wait and never wait for their own grid; the grid must still
+    // be resident at once so that every rank's pushing blocks get to run
+    if ((long long)a->num_tokens * chunks > (long long)ep_combine_push_resident_blocks(c.dev.sm_count))
+      return B200MOE_E_LIMIT;
+    return (int)launch_ep_combine_push(
+        a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched, a->expert_output,
+        a->expert_indices, e->inbox_ptrs, e->flag_ptrs, e->output, e->status, slice_elems,
+        e->inbox_cap_tokens, a->num_tokens, a->top_k, a->hidden_size, a->num_experts, e->world,
+        e->rank, e->first_token, e->num_tokens, e->tokens_per_rank, e->epoch, limit_ns,
+        trace_of(c.s), pdl, c.stream);
+  }
   // The fused kernel's blocks wait for other GPUs while the publishing block of their own
   // grid may not have run yet, so it is used only while the whole grid is resident at once
-  // (eight 128-thread blocks per SM is well inside what an SM holds).
-  if ((long long)a->num_tokens * chunks <= 8ll * c.dev.sm_count)
+  // (what the occupancy calculation says fits; kernels that share the GPU for a while --
+  // the tail of the down projection -- delay blocks but do not depend on them).
+  if ((long long)a->num_tokens * chunks <= (long long)ep_combine_reduce_resident_blocks(c.dev.sm_count))
     return (int)launch_ep_combine_reduce(
         a->reverse_mapping, a->expert_weights, c.s.partials, c.s.sched, a->expert_output,
         a->expert_indices, e->partial_ptrs, e->flag_ptrs, e->block_counter, e->output,

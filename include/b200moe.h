@@ -41,7 +41,7 @@ extern "C" {
 #define B200MOE_E_DRIVER      (-5)  /* cuTensorMapEncodeTiled could not be resolved / failed */
 #define B200MOE_E_ARCH        (-6)  /* current device is not compute capability 10.0 */
 #define B200MOE_E_UNSUPPORTED (-7)  /* feature is declared but not implemented (NVFP4) */
-#define B200MOE_E_LIMIT       (-8)  /* T*K exceeds B200MOE_STATIC_ROUTING_MAX_ASSIGNMENTS */
+#define B200MOE_E_LIMIT       (-8)  /* the call exceeds a fixed limit of the entry point */
 
 /* bits of the device status word */
 #define B200MOE_STATUS_BAD_EXPERT_ID  0x1u  /* some expert id was outside [0, E); its row was dropped */
@@ -313,6 +313,11 @@ typedef struct B200MoeEpReduceArgs {
   /* b200moe_ep_combine_reduce only */
   int32_t  first_token;              /* first of the num_tokens rows this rank outputs */
   unsigned int* block_counter;       /* one zero-initialised uint32 in this device's memory */
+  /* b200moe_ep_combine_reduce with B200MOE_FLAG_EP_PUSH only */
+  void* const* inbox_ptrs;           /* every rank's inbox, valid on THIS device (see below) */
+  int32_t  inbox_cap_tokens;         /* tokens one inbox slot holds (>= layer->num_tokens) */
+  int32_t  tokens_per_rank;          /* sharded tokens: rank t / tokens_per_rank outputs token t;
+                                        0: tokens are replicated, every rank outputs all */
 } B200MoeEpReduceArgs;
 
 #define B200MOE_EP_MAX_WORLD 8
@@ -336,11 +341,31 @@ int b200moe_ep_reduce(const B200MoeEpReduceArgs* args, void* stream);
  * are written as zeros and B200MOE_STATUS_PEER_TIMEOUT is set.
  *
  * partial_ptrs[r] is the start of rank r's FP32 [layer->num_tokens, H] buffer (not offset by
- * first_token).  Calls with more than 8 blocks per SM (T * ceil(H / 1024) > 8 * SMs) run as
- * the two separate kernels instead, with the same result.
+ * first_token).  Calls whose grid (T * ceil(H / 1024) blocks) exceeds what the GPU holds at
+ * once run as the two separate kernels instead, with the same result.
  */
 int b200moe_ep_combine_reduce(const B200MoeArgs* layer, const B200MoeEpReduceArgs* ep,
                               void* stream);
+
+/*
+ * B200MOE_FLAG_EP_PUSH in ep->flags selects the low-latency variant of
+ * b200moe_ep_combine_reduce: instead of publishing one flag per rank and letting the peers
+ * read its partial rows, every block stores its row straight into the inbox of each rank that
+ * outputs the token, each 4-byte value together with the 4-byte epoch in one 8-byte word, so
+ * that no fence and no flag round trip separate the combine from the peers' sums; receivers
+ * poll their own memory.  partial_ptrs and block_counter are not used.
+ *   inbox_ptrs[r]   rank r's inbox: 2 * world * inbox_cap_tokens * H words of 8 bytes, zero
+ *                   before the first epoch, laid out [epoch parity][source rank][token][H]
+ *   flag_ptrs[r]    rank r's uint32[world] array; here it carries progress: every rank stores
+ *                   its epoch there when its kernel starts, and a rank waits (bounded) for the
+ *                   target's previous epoch before it reuses an inbox slot
+ *   epoch           1, 2, 3, ... (never 0), the same on every rank for one layer call
+ * One layer instance uses either this variant or the other for all its calls.  The grid
+ * (T * ceil(H / 1024) blocks) must be resident at once: larger calls return B200MOE_E_LIMIT
+ * (b200moe_ep_push_max_blocks gives the bound for the current device).
+ */
+#define B200MOE_FLAG_EP_PUSH 0x40u
+int b200moe_ep_push_max_blocks(int* blocks);
 
 /*
  * Expert-parallel dispatch of sharded tokens over NVLink peer memory.  No counterpart

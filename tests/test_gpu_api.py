@@ -376,6 +376,97 @@ def test_fused_combine_reduce_with_all_ranks_buffers_on_one_gpu(spec, cuda_devic
     assert torch.equal(mine, outputs[0][per:2 * per])
 
 
+def _combine_push_call(device, ranks, rank, inboxes, flags, epoch, first, rows, cap,
+                       tokens_per_rank, limit_us):
+    import ctypes
+
+    from b200moe import _lib
+
+    world = len(ranks)
+    workspace, (layer_args, _keep) = ranks[rank]
+    H = layer_args.hidden_size
+    args = _lib.B200MoeEpReduceArgs()
+    i_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in inboxes])
+    f_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in flags])
+    args.inbox_ptrs = ctypes.cast(i_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.flag_ptrs = ctypes.cast(f_ptrs, ctypes.POINTER(ctypes.c_void_p))
+    args.world, args.rank, args.hidden_size = world, rank, H
+    args.num_tokens, args.first_token = rows, first
+    args.inbox_cap_tokens, args.tokens_per_rank = cap, tokens_per_rank
+    args.epoch, args.wait_limit_us = epoch, limit_us
+    output = torch.full((rows, H), 7.0, dtype=torch.bfloat16, device=device)
+    args.output = output.data_ptr()
+    args.status = workspace.scratch.data_ptr()
+    args.flags = _lib.FLAG_EP_PUSH
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    code = _lib.load().b200moe_ep_combine_reduce(ctypes.byref(layer_args), ctypes.byref(args),
+                                                 stream)
+    _lib.check(code, "b200moe_ep_combine_reduce (push)")
+    torch.cuda.synchronize(device)
+    return output
+
+
+@pytest.mark.parametrize("spec", [(4, 16, 256, 384, 8, 2), (8, 64, 512, 256, 16, 4)],
+                         ids=["world4", "world8"])
+def test_push_combine_reduce_with_all_ranks_inboxes_on_one_gpu(spec, cuda_device) -> None:
+    """The flagged-row push variant with every rank's inbox on this GPU.  Ranks run one after
+    another, never together: in the first round a rank that runs before the owners of its
+    tokens finds its inbox incomplete, gives up after its (short) limit, zeroes the rows and
+    sets the status bit -- which is the bounded-wait behaviour -- while its own rows still land
+    in every inbox; in the second round every inbox holds this epoch's rows and all ranks
+    complete.  Results meet the oracle bar, agree across ranks and with the pull variant's
+    rank-order sum; a sharded caller gets exactly its rows."""
+
+    from b200moe import _lib
+
+    world, T, H, I, E, K = spec
+    ranks, ref = _emulated_ranks(cuda_device, world, T, H, I, E, K)
+    cap = T
+    inboxes = [torch.zeros(2 * world * cap * H * 2, dtype=torch.int32, device=cuda_device)
+               for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    epoch = 1
+    first_round = [_combine_push_call(cuda_device, ranks, r, inboxes, flags, epoch, 0, T, cap, 0,
+                                      limit_us=1500) for r in range(world)]
+    timed_out = [bool(ranks[r][0].status() & _lib.STATUS_PEER_TIMEOUT) for r in range(world)]
+    assert timed_out[0]  # rank 0 ran before every other owner
+    assert first_round[0].shape == (T, H)
+    for r in range(world):
+        ranks[r][0].scratch[:4].zero_()
+    outputs = [_combine_push_call(cuda_device, ranks, r, inboxes, flags, epoch, 0, T, cap, 0,
+                                  limit_us=1500) for r in range(world)]
+    for r in range(world):
+        assert ranks[r][0].status() == 0
+        assert torch.equal(outputs[r], outputs[0])
+    err = moe_oracle.relative_max_error(outputs[0].float().cpu(), ref)
+    assert err <= 2e-2, err
+    # every rank announced its epoch in slot `rank` of every rank's progress array
+    assert all(int(f[r]) == epoch for f in flags for r in range(world))
+    # same sum order as the pull variant: bit-identical results
+    partials = [torch.zeros(T, H, device=cuda_device) for _ in range(world)]
+    pflags = [torch.full((8,), 3, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    pulled = None
+    for _round in range(2):
+        pulled = [_combine_reduce_call(cuda_device, ranks, r, partials, pflags, counter, 3, 0, T)
+                  for r in range(world)]
+    assert torch.equal(pulled[0], outputs[0])
+    # sharded tokens at the next epoch: rank 1 outputs its own T/world rows only, and only
+    # pushes aimed at it land in its inbox
+    per = T // world
+    for r in range(world):
+        flags[r][:] = epoch  # every rank has begun the previous epoch
+    for _round in range(2):
+        rows = [_combine_push_call(cuda_device, ranks, r, inboxes, flags, epoch + 1, r * per,
+                                   per, cap, per, limit_us=1500) for r in range(world)]
+        for r in range(world):
+            if _round == 0:
+                ranks[r][0].scratch[:4].zero_()
+    for r in range(world):
+        assert ranks[r][0].status() == 0
+        assert torch.equal(rows[r], outputs[0][r * per:(r + 1) * per])
+
+
 def test_fused_combine_reduce_reports_a_missing_peer(cuda_device) -> None:
     """A peer that never publishes its flag: the wait runs out after its limit, the rows come
     back as zeros with the status bit set, and the same call completes once the flag is there."""
