@@ -209,6 +209,117 @@ def _run_native(
     return output, routed
 
 
+class _CallPlan:
+    """What a repeated call needs, remembered on the workspace after one fully checked call.
+
+    A decode loop calls the layer with the same weights, dimensions and options thousands of
+    times; only the three per-step tensors change.  Once a call has passed every check of
+    :func:`b300_moe_forward`, the facts those checks established are kept here, and a later
+    call that matches them (same shapes, dtypes, device, weight storage, options, stream and
+    allocation) goes straight to the native library: it compares a handful of attributes,
+    allocates the output, rewrites the per-call fields of the bound argument struct and
+    records the workspace's completion event.  Anything that does not match takes the fully
+    checked path again, which also covers every error case.
+    """
+
+    __slots__ = ("h_shape", "r_shape", "device", "device_index", "gate_up_ptr", "down_ptr",
+                 "gate_up_shape", "num_experts", "top_k", "backend", "quant_mode_in",
+                 "gemm_policy", "use_pdl", "allocations", "stream", "stream_ptr", "args",
+                 "args_ref", "flags", "fn", "last_shape")
+
+
+def _remember_plan(workspace, hidden_states, expert_indices, gate_up_weight, down_weight,
+                   num_experts, top_k, backend, quant_mode_in, gemm_policy, use_pdl, shape,
+                   flags) -> None:
+    plan = _CallPlan()
+    plan.h_shape = hidden_states.shape
+    plan.r_shape = expert_indices.shape
+    plan.device = hidden_states.device
+    plan.device_index = hidden_states.device.index
+    plan.gate_up_ptr = gate_up_weight.data_ptr()
+    plan.down_ptr = down_weight.data_ptr()
+    plan.gate_up_shape = gate_up_weight.shape
+    plan.num_experts, plan.top_k = num_experts, top_k
+    plan.backend, plan.quant_mode_in, plan.gemm_policy = backend, quant_mode_in, gemm_policy
+    plan.use_pdl = use_pdl
+    plan.allocations = workspace.allocation_count
+    plan.stream = torch.cuda.current_stream(hidden_states.device)
+    plan.stream_ptr = int(plan.stream.cuda_stream)
+    plan.args = workspace._args_cache[1]
+    plan.args_ref = ctypes.byref(plan.args)
+    plan.flags = flags
+    plan.fn = _lib.load().b200moe_forward
+    plan.last_shape = (shape.num_tokens, shape.num_experts, shape.top_k, shape.hidden_size,
+                       shape.intermediate_size)
+    workspace._plan = plan
+
+
+def _repeat_call(workspace, hidden_states, expert_indices, expert_weights, gate_up_weight,
+                 down_weight, num_experts, top_k, quant_mode, backend, gemm_policy, use_pdl):
+    """The output of a call that matches the workspace's remembered plan, or ``None``."""
+
+    plan = workspace._plan
+    if (
+        plan is None
+        or hidden_states.shape != plan.h_shape
+        or expert_indices.shape != plan.r_shape
+        or expert_weights.shape != plan.r_shape
+        or hidden_states.dtype is not torch.bfloat16
+        or expert_weights.dtype is not torch.bfloat16
+        or expert_indices.dtype is not torch.int64
+        or hidden_states.device != plan.device
+        or expert_indices.device != plan.device
+        or expert_weights.device != plan.device
+        or gate_up_weight.data_ptr() != plan.gate_up_ptr
+        or down_weight.data_ptr() != plan.down_ptr
+        or gate_up_weight.shape != plan.gate_up_shape
+        or num_experts != plan.num_experts
+        or top_k != plan.top_k
+        or backend != plan.backend
+        or quant_mode != plan.quant_mode_in
+        or gemm_policy != plan.gemm_policy
+        or use_pdl != plan.use_pdl
+        or not hidden_states.is_contiguous()
+        or not expert_indices.is_contiguous()
+        or not expert_weights.is_contiguous()
+        or hidden_states.requires_grad
+        or expert_weights.requires_grad
+        or gate_up_weight.requires_grad
+        or down_weight.requires_grad
+        or torch.cuda.current_device() != plan.device_index
+    ):
+        return None
+    with workspace._lock:
+        # same allocation, same stream as the last use (no cross-stream ordering to do), and
+        # no graph capture under way (a capture takes the checked path, which knows its rules)
+        if (
+            workspace._allocations != plan.allocations
+            or workspace._last_stream != plan.stream_ptr
+            or torch._C._cuda_getCurrentRawStream(plan.device_index) != plan.stream_ptr
+            or torch._C._cuda_isCurrentStreamCapturing()
+        ):
+            return None
+        output = torch.empty_like(hidden_states)
+        args = plan.args
+        args.hidden_states = hidden_states.data_ptr()
+        args.expert_indices = expert_indices.data_ptr()
+        args.expert_weights = expert_weights.data_ptr()
+        args.num_tokens = plan.h_shape[0]
+        args.output = output.data_ptr()
+        args.flags = plan.flags
+        args.expert_id_base = 0
+        args.ep_wait_flags = None
+        args.ep_world = 0
+        code = plan.fn(plan.args_ref, plan.stream_ptr)
+        if code:
+            _lib.check(code, "b200moe_forward")
+        workspace._reuses += 1
+        workspace._last_reused = True
+        workspace._last_shape = plan.last_shape
+        workspace._event.record(plan.stream)
+    return output
+
+
 def b300_moe_forward(
     hidden_states: torch.Tensor,
     expert_indices: torch.Tensor,
@@ -245,6 +356,14 @@ def b300_moe_forward(
 
     if not isinstance(return_metadata, bool):
         raise TypeError("return_metadata must be a bool")
+    if workspace is not None and not return_metadata and not check_status and \
+            type(workspace) is B300MoEWorkspace:
+        repeated = _repeat_call(workspace, hidden_states, expert_indices, expert_weights,
+                                gate_up_weight, down_weight, num_experts, top_k, quant_mode,
+                                backend, gemm_policy, use_pdl)
+        if repeated is not None:
+            return repeated
+    quant_mode_in = quant_mode
     backend = normalize_backend(backend)
     gemm_policy = normalize_gemm_policy(gemm_policy)
     shape = validate_routed_moe_inputs(
@@ -336,6 +455,10 @@ def b300_moe_forward(
                 "active_experts": active_experts,
             }
         active._record_use()
+        if workspace is not None:
+            _remember_plan(active, hidden_states, expert_indices, gate_up_weight, down_weight,
+                           num_experts, top_k, backend, quant_mode_in, gemm_policy, use_pdl,
+                           shape, _lib.FLAG_PDL if use_pdl else 0)
         if check_status:
             active.raise_for_status()
 

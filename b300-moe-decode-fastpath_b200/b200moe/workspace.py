@@ -72,6 +72,7 @@ class B300MoEWorkspace:
         self._event: torch.cuda.Event | None = None
         self._recorded_streams: set[int] = set()
         self._args_cache: tuple[object, object] | None = None  # bound native argument struct
+        self._plan = None  # facts established by the last fully checked forward (forward.py)
         self._lock = threading.RLock()
 
     # -- read-only state --------------------------------------------------------
@@ -228,6 +229,7 @@ class B300MoEWorkspace:
         self._scratch_base = None
         self._recorded_streams = set()
         self._args_cache = None
+        self._plan = None
         if native and device.type == "cuda":
             need = _lib.scratch_bytes(tokens, top_k, num_experts, hidden, inter)
             base = torch.empty(need + _SCRATCH_ALIGN, device=device, dtype=torch.uint8)

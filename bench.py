@@ -792,14 +792,19 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         graph_samples[T] = [a.elapsed_time(b) * 1e3 for a, b in pairs]
         del graph
 
-    # host cost of one call: enqueue 20 forwards back to back without synchronising
+    # host cost of one call: the time the call takes to return with an empty launch queue
+    # (a synchronise before every call, so that no launch waits for queue space behind
+    # earlier forwards); median of 30
     host_us = {}
     for T in sweep:
-        torch.cuda.synchronize(device)
-        t0 = time.perf_counter()
-        for _ in range(20):
+        forward(T)
+        times = []
+        for _ in range(30):
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter_ns()
             forward(T)
-        host_us[T] = (time.perf_counter() - t0) / 20 * 1e6
+            times.append((time.perf_counter_ns() - t0) / 1e3)
+        host_us[T] = percentile(sorted(times), 0.5)
     torch.cuda.synchronize(device)
 
     # per-stage timing through the staged C-ABI entry points (isolated launches)
@@ -1140,11 +1145,15 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
 
     host_us = {}
     for T in SWEEP:
-        torch.cuda.synchronize(device)
-        t0 = time.perf_counter()
-        for _ in range(20):
+        forward(T)
+        times = []
+        for _ in range(30):
+            torch.cuda.synchronize(device)
+            dist.barrier()  # keep the ranks together: a forward waits for its peers
+            t0 = time.perf_counter_ns()
             forward(T)
-        host_us[T] = (time.perf_counter() - t0) / 20 * 1e6
+            times.append((time.perf_counter_ns() - t0) / 1e3)
+        host_us[T] = percentile(sorted(times), 0.5)
     torch.cuda.synchronize(device)
 
     # per-rank stage timing of the dominant kernel at the largest T (all local experts active)
