@@ -11,6 +11,8 @@ from .forward import ARCHITECTURE, b300_moe_forward, b300_moe_forward_pinned
 from .fp8 import (Fp8ExpertWeights, b300_moe_forward_fp8, dequantize_expert_weights_fp8,
                   dequantize_rows_fp8, quantize_expert_weights_fp8, quantize_rows_fp8)
 from .graphed import GraphedMoEDecodeLayer
+from .nvfp4 import (Nvfp4ExpertWeights, b300_moe_forward_nvfp4, prepared_nvfp4_weights,
+                    quantize_expert_weights_nvfp4)
 from .ops import DispatchResult, combine_tokens, dispatch_tokens
 from .router import topk_routing
 from .stages import StagedLayer
@@ -23,10 +25,12 @@ __all__ = [
     "DispatchResult",
     "Fp8ExpertWeights",
     "GraphedMoEDecodeLayer",
+    "Nvfp4ExpertWeights",
     "RoutedMoEShape",
     "StagedLayer",
     "b300_moe_forward",
     "b300_moe_forward_fp8",
+    "b300_moe_forward_nvfp4",
     "b300_moe_forward_pinned",
     "build_info",
     "combine_tokens",
@@ -34,7 +38,9 @@ __all__ = [
     "dequantize_expert_weights_fp8",
     "dequantize_rows_fp8",
     "dispatch_tokens",
+    "prepared_nvfp4_weights",
     "quantize_expert_weights_fp8",
+    "quantize_expert_weights_nvfp4",
     "quantize_rows_fp8",
     "topk_routing",
     "validate_routed_moe_inputs",

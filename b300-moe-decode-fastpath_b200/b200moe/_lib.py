@@ -29,6 +29,7 @@ FLAG_FP8_WEIGHTS = 0x8
 FLAG_HOST_IO = 0x10
 FLAG_SKIP_COMBINE = 0x20
 FLAG_EP_PUSH = 0x40
+FLAG_NVFP4_WEIGHTS = 0x80
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 
@@ -61,6 +62,9 @@ EXPORTS = (
     "b200moe_ep_push",
     "b200moe_status_ptr",
     "b200moe_nvfp4_available",
+    "b200moe_nvfp4_scale_bytes",
+    "b200moe_nvfp4_quantize",
+    "b200moe_nvfp4_rows_to_planes",
     "b200moe_tune",
     "b200moe_router_topk",
     "b200moe_fp8_quantize_rows",
@@ -105,6 +109,8 @@ class B200MoeArgs(ctypes.Structure):
         ("ep_wait_limit_us", ctypes.c_uint32),
         ("gate_up_scale", ctypes.c_void_p),
         ("down_scale", ctypes.c_void_p),
+        ("gate_up_block_scale", ctypes.c_void_p),
+        ("down_block_scale", ctypes.c_void_p),
     ]
 
 
@@ -213,6 +219,19 @@ def _declare(lib: ctypes.CDLL) -> None:
     ]
     lib.b200moe_nvfp4_available.restype = ctypes.c_int
     lib.b200moe_nvfp4_available.argtypes = []
+    lib.b200moe_nvfp4_scale_bytes.restype = ctypes.c_int
+    lib.b200moe_nvfp4_scale_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.POINTER(ctypes.c_size_t)]
+    lib.b200moe_nvfp4_quantize.restype = ctypes.c_int
+    lib.b200moe_nvfp4_quantize.argtypes = [
+        ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+    ]
+    lib.b200moe_nvfp4_rows_to_planes.restype = ctypes.c_int
+    lib.b200moe_nvfp4_rows_to_planes.argtypes = [
+        ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p, ctypes.c_void_p,
+    ]
     lib.b200moe_router_topk.restype = ctypes.c_int
     lib.b200moe_router_topk.argtypes = [
         ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,

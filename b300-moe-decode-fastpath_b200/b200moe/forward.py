@@ -55,13 +55,12 @@ def _resolve_native_backend(
         raise RuntimeError(
             f"backend={backend!r} requires B200 compute capability (10, 0), got {capability}"
         )
-    if backend == "cutlass_nvfp4":
+    if backend == "cutlass_nvfp4" and not _lib.load().b200moe_nvfp4_available():
         # Same promise as the reference (b300_moe.py:571-596): NVFP4 is never
         # quietly replaced by the BF16 kernels.
-        available = bool(_lib.load().b200moe_nvfp4_available())
         raise RuntimeError(
             "cutlass_nvfp4 is unavailable: no NVFP4 grouped GEMM is compiled into "
-            f"libb200moe.so (nvfp4_available={available}); no fallback was used"
+            "libb200moe.so (nvfp4_available=False); no fallback was used"
         )
     if hidden_states.dtype != torch.bfloat16:
         raise TypeError(f"{backend} requires bfloat16 inputs and weights")
@@ -393,6 +392,19 @@ def b300_moe_forward(
     build_info = _resolve_native_backend(
         backend, hidden_states, expert_weights, gate_up_weight, down_weight, shape
     )
+    if backend == "cutlass_nvfp4":
+        # The contract's BF16 weight tensors, used in their NVFP4 form (prepared once per
+        # weight tensor); the NVFP4 kernels run, nothing else.
+        from .nvfp4 import b300_moe_forward_nvfp4, prepared_nvfp4_weights
+
+        if shape.hidden_size % 64 or shape.intermediate_size % 64:
+            raise ValueError("cutlass_nvfp4 requires hidden_size and intermediate_size "
+                             "divisible by 64")
+        return b300_moe_forward_nvfp4(
+            hidden_states, expert_indices, expert_weights,
+            prepared_nvfp4_weights(gate_up_weight, down_weight), num_experts=num_experts,
+            top_k=top_k, workspace=workspace, return_metadata=return_metadata,
+            check_status=check_status, use_pdl=use_pdl, backend_name=backend)
     active = workspace if workspace is not None else B300MoEWorkspace(device=hidden_states.device)
 
     with active._lock:

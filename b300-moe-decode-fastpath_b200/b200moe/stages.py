@@ -37,12 +37,24 @@ class StagedLayer:
         workspace: B300MoEWorkspace | None = None,
         use_pdl: bool = True,
         fp8_weights=None,
+        nvfp4_weights=None,
     ) -> None:
-        """``fp8_weights`` (an ``Fp8ExpertWeights``) selects the FP8-weight kernels; the two
-        BF16 weight arguments are then ignored and may be ``None``."""
+        """``fp8_weights`` (an ``Fp8ExpertWeights``) or ``nvfp4_weights`` (an
+        ``Nvfp4ExpertWeights``) selects the kernels of that weight format; the two BF16 weight
+        arguments are then ignored and may be ``None``."""
 
         flags = _lib.FLAG_PDL if use_pdl else 0
-        if fp8_weights is not None:
+        if nvfp4_weights is not None:
+            from .nvfp4 import _validate as validate_nvfp4
+
+            self.shape = validate_nvfp4(hidden_states, expert_indices, expert_weights,
+                                        nvfp4_weights, num_experts, top_k)
+            gate_up_weight, down_weight = nvfp4_weights.gate_up_q, nvfp4_weights.down_q
+            _resolve_native_backend("b200_nvfp4", hidden_states, expert_weights,
+                                    nvfp4_weights.gate_up_scale, nvfp4_weights.down_scale,
+                                    self.shape)
+            flags |= _lib.FLAG_NVFP4_WEIGHTS
+        elif fp8_weights is not None:
             from .fp8 import _validate as validate_fp8
 
             self.shape = validate_fp8(hidden_states, expert_indices, expert_weights, fp8_weights,
@@ -80,7 +92,7 @@ class StagedLayer:
         self.output = torch.empty_like(hidden_states)
         # keep the inputs alive for as long as their addresses sit in the struct
         self._inputs = (hidden_states, expert_indices, expert_weights, gate_up_weight, down_weight,
-                        fp8_weights)
+                        fp8_weights, nvfp4_weights)
         # a private struct: the workspace keeps its own bound struct for forward calls
         self._args = _lib.B200MoeArgs()
         bound = _native_args(
@@ -98,6 +110,11 @@ class StagedLayer:
         if fp8_weights is not None:
             self._args.gate_up_scale = fp8_weights.gate_up_scale.data_ptr()
             self._args.down_scale = fp8_weights.down_scale.data_ptr()
+        if nvfp4_weights is not None:
+            self._args.gate_up_scale = nvfp4_weights.gate_up_scale.data_ptr()
+            self._args.down_scale = nvfp4_weights.down_scale.data_ptr()
+            self._args.gate_up_block_scale = nvfp4_weights.gate_up_block_scale.data_ptr()
+            self._args.down_block_scale = nvfp4_weights.down_block_scale.data_ptr()
         lib = _lib.load()
         self._calls = {
             "routing": lib.b200moe_routing,

@@ -2,7 +2,7 @@
 
     python b300-moe-decode-fastpath_b200/build.py [--force] [--verbose]
 
-The library has no Python, PyTorch, CUTLASS or pybind dependency: eight `.cu`
+The library has no Python, PyTorch, CUTLASS or pybind dependency: ten `.cu`
 files, the CUDA runtime (static) and nothing else.  Exactly one `-gencode` is
 passed, like the reference's single-architecture build
 (fastpath/build.py:52-57, setup.py:49-54), but for `sm_100a`.
@@ -21,7 +21,7 @@ PACKAGE_ROOT = Path(__file__).resolve().parent
 CSRC = PACKAGE_ROOT / "csrc"
 INCLUDE = PACKAGE_ROOT.parent / "include"
 SOURCES = ("api.cu", "routing.cu", "rows.cu", "grouped_gemm.cu", "grouped_gemm_fp8.cu",
-           "quant.cu", "ep_reduce.cu", "router.cu")
+           "grouped_gemm_nvfp4.cu", "quant.cu", "nvfp4_quant.cu", "ep_reduce.cu", "router.cu")
 HEADERS = (CSRC / "common.cuh", INCLUDE / "b200moe.h")
 LIBRARY = PACKAGE_ROOT / "b200moe" / "libb200moe.so"
 GENCODE = "arch=compute_100a,code=sm_100a"

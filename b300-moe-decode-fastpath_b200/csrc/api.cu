@@ -79,6 +79,36 @@ cudaError_t launch_fp8_quantize_rows(const void* w, long long rows, int cols, ui
 cudaError_t launch_fp8_dequantize_rows(const uint8_t* q, const float* scale, long long rows,
                                        int cols, void* out, cudaStream_t stream);
 
+cudaError_t launch_nvfp4_quantize(const void* w, int experts, int rows, int cols, int halves,
+                                  uint8_t* packed, uint8_t* sf, float* tensor_scale,
+                                  uint32_t* amax_scratch, cudaStream_t stream);
+cudaError_t launch_gather_nvfp4(const void* hidden, const int64_t* permutation, void* out,
+                                uint8_t* planes, uint8_t* scales, float* row_scale,
+                                uint32_t* act_amax, int num_assign, int num_tokens, int top_k,
+                                int hidden_size, int rows_cap, unsigned long long* trace,
+                                bool pdl, cudaStream_t stream);
+cudaError_t launch_act_planes_nvfp4(const void* act_hi, const void* act_lo,
+                                    const uint32_t* act_amax, uint8_t* planes, uint8_t* scales,
+                                    float* row_scale, int num_assign, int inter, int rows_cap,
+                                    bool pdl, cudaStream_t stream);
+cudaError_t launch_rows_to_planes_nvfp4(const float* rows, int num_rows, int cols,
+                                        uint8_t* planes, uint8_t* scales, float* row_scale,
+                                        cudaStream_t stream);
+cudaError_t launch_gate_up_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_x,
+                                 const int32_t* sched, int sched_cap, uint32_t* status,
+                                 void* act_hi, void* act_lo, uint32_t* act_amax,
+                                 const uint8_t* sfa, const float* tensor_scale,
+                                 const uint8_t* sfb,
+                                 const float* token_scale, int inter, int hidden, int rows_cap,
+                                 int max_rows, int grid, int sm_count, bool pdl,
+                                 cudaStream_t stream);
+cudaError_t launch_down_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_act,
+                              const int32_t* sched, int sched_cap, uint32_t* status,
+                              float* partials, const uint8_t* sfa, const float* tensor_scale,
+                              const uint8_t* sfb, const float* token_scale, int hidden, int inter,
+                              int rows_cap, int max_rows, int grid, int sm_count, bool pdl,
+                              cudaStream_t stream);
+
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
                                 const void* weights, void* out, int num_tokens, int top_k,
                                 int hidden_size, cudaStream_t stream);
@@ -132,6 +162,10 @@ int down_split_request(int sm_count) {
 }
 
 constexpr int kMaxDevices = 64;
+// The NVFP4 kernels are compiled in and pass their parity tests on a B200 (tests/test_gpu_nvfp4.py).
+// With 0 the capability probe answers 0 and b300_moe_forward(backend="cutlass_nvfp4") fails
+// loudly, as the reference's backend of that name always does.
+constexpr int kNvfp4Ready = 1;
 
 struct DeviceInfo {
   bool probed = false;
@@ -233,6 +267,8 @@ int segment_bound(int rows, int experts, int seg_rows = kSegRows) {
 }
 
 bool fp8_weights(const B200MoeArgs* a) { return (a->flags & B200MOE_FLAG_FP8_WEIGHTS) != 0; }
+bool nvfp4_weights(const B200MoeArgs* a) { return (a->flags & B200MOE_FLAG_NVFP4_WEIGHTS) != 0; }
+
 
 int tiles128(int n) { return (n + 127) / 128; }
 
@@ -246,6 +282,14 @@ struct Scratch {
   float* a_scale;
   uint32_t* a_amax;
 };
+
+// NVFP4 path: the token planes and their block scales share the scratch bytes of the FP8
+// path's planes (4 planes of W / 2 bytes per row, then 4 x W / 16 scale bytes per row, with
+// W = max(H, I): 2.25 of the 3 bytes per element that region holds).
+uint8_t* nvfp4_token_scales(const Scratch& s, int rows_cap, int hidden, int inter) {
+  const size_t widest = (size_t)(hidden > inter ? hidden : inter);
+  return s.q_planes + 2 * (size_t)rows_cap * widest;
+}
 
 int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts, int hidden,
                   int inter, Scratch* out) {
@@ -305,10 +349,12 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              a->reverse_mapping, a->permutation, a->expert_offsets_i32,
                              a->permuted_token_indices, a->permuted_expert_indices,
                              a->permuted_weights, s.sched, s.status, tiles128(a->hidden_size),
-                             fp8_weights(a) ? (a->intermediate_size + 127) / 128
-                                            : (a->intermediate_size + 63) / 64,
+                             nvfp4_weights(a) ? (a->intermediate_size + 255) / 256
+                             : fp8_weights(a) ? (a->intermediate_size + 127) / 128
+                                              : (a->intermediate_size + 63) / 64,
                              down_split_request(dev.sm_count),
-                             fp8_weights(a) ? g_fp8_seg_rows : kSegRows,
+                             nvfp4_weights(a) ? kSegRowsNvfp4
+                             : fp8_weights(a) ? g_fp8_seg_rows : kSegRows,
                              local ? a->expert_id_base : 0, local,
                              static_cast<const uint32_t*>(a->ep_wait_flags), a->ep_world,
                              a->ep_epoch,
@@ -422,6 +468,66 @@ int do_down_fp8(const void* act_hi, const void* w, const float* row_scale, int r
                               stream);
 }
 
+// NVFP4 weights: byte tensor maps of the packed weights (two elements per byte) and of the
+// token planes; scales travel outside the tensor maps.
+int do_gate_up_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments,
+                     const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
+  const int hidden = a->hidden_size, inter = a->intermediate_size, experts = a->num_experts;
+  CUtensorMap map_w, map_x;
+  {
+    const uint64_t dims[4] = {(uint64_t)hidden / 2, (uint64_t)inter, 2, (uint64_t)experts};
+    const uint32_t box[4] = {128, 128, 2, 1};  // 128 gate rows + the 128 matching up rows
+    int rc = encode_map(&map_w, a->gate_up_weight, 4, dims, box, true);
+    if (rc) return rc;
+  }
+  int rc = encode_plane_map(&map_x, s.q_planes, hidden / 2, a->rows_cap, kNvfp4Planes);
+  if (rc) return rc;
+  const int grid = segment_bound(assignments, experts, kSegRowsNvfp4) * tiles128(inter);
+  return (int)launch_gate_up_nvfp4(
+      map_w, map_x, s.sched, max_segments(a->rows_cap, experts), s.status, a->swiglu_output,
+      s.act_lo, s.a_amax, static_cast<const uint8_t*>(a->gate_up_block_scale), a->gate_up_scale,
+      nvfp4_token_scales(s, a->rows_cap, hidden, inter), s.x_scale, inter, hidden, a->rows_cap,
+      assignments, grid, dev.sm_count, pdl, stream);
+}
+
+int do_down_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments, const DeviceInfo& dev,
+                  bool pdl, cudaStream_t stream) {
+  const int hidden = a->hidden_size, inter = a->intermediate_size, experts = a->num_experts;
+  CUtensorMap map_w, map_act;
+  {
+    const uint64_t dims[3] = {(uint64_t)inter / 2, (uint64_t)hidden, (uint64_t)experts};
+    const uint32_t box[3] = {128, 128, 1};
+    int rc = encode_map(&map_w, a->down_weight, 3, dims, box, true);
+    if (rc) return rc;
+  }
+  int rc = encode_plane_map(&map_act, s.q_planes, inter / 2, a->rows_cap, kNvfp4Planes);
+  if (rc) return rc;
+  uint8_t* token_scales = nvfp4_token_scales(s, a->rows_cap, hidden, inter);
+  const int grid = down_grid(segment_bound(assignments, experts, kSegRowsNvfp4),
+                             tiles128(hidden), (inter + 255) / 256, dev.sm_count);
+  // the activation rows become planes (in the bytes the gathered rows' planes occupied)
+  rc = (int)launch_act_planes_nvfp4(a->swiglu_output, s.act_lo, s.a_amax, s.q_planes,
+                                    token_scales, s.a_scale, assignments, inter, a->rows_cap, pdl,
+                                    stream);
+  if (rc) return rc;
+  return (int)launch_down_nvfp4(map_w, map_act, s.sched, max_segments(a->rows_cap, experts),
+                                s.status, s.partials,
+                                static_cast<const uint8_t*>(a->down_block_scale), a->down_scale,
+                                token_scales, s.a_scale, hidden, inter, a->rows_cap, assignments,
+                                grid, dev.sm_count, pdl, stream);
+}
+
+// geometry and pointers the NVFP4 path needs on top of the common checks
+int check_nvfp4(const B200MoeArgs* a) {
+  if (!a->gate_up_scale || !a->down_scale || !a->gate_up_block_scale || !a->down_block_scale)
+    return B200MOE_E_NULL;
+  if (a->hidden_size % 64 || a->intermediate_size % 64) return B200MOE_E_ALIGN;
+  if (!aligned16(a->gate_up_block_scale) || !aligned16(a->down_block_scale))
+    return B200MOE_E_ALIGN;
+  if (fp8_weights(a)) return B200MOE_E_SHAPE;
+  return 0;
+}
+
 unsigned long long* trace_of(const Scratch& s) {
   return reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(s.status) +
                                                kTraceOffsetBytes);
@@ -468,7 +574,8 @@ int stage_routing(const B200MoeArgs* a, const Ctx& c, bool after_gate_up = false
 // are in place when the forward is enqueued (not pushed by peers during it).
 bool small_call(const B200MoeArgs* a, int assignments) {
   int most = g_small_call_max < kSmallCallMaxAssign ? g_small_call_max : kSmallCallMaxAssign;
-  return assignments <= most && !fp8_weights(a) && a->ep_wait_flags == nullptr &&
+  return assignments <= most && !fp8_weights(a) && !nvfp4_weights(a) &&
+         a->ep_wait_flags == nullptr &&
          (a->flags & B200MOE_FLAG_HOST_IO) == 0;
 }
 
@@ -488,6 +595,14 @@ SmallCall small_call_of(const B200MoeArgs* a, const Ctx& c) {
 int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (!a->hidden_states || !a->permutation || !a->permuted_hidden) return B200MOE_E_NULL;
   if (!aligned16(a->hidden_states) || !aligned16(a->permuted_hidden)) return B200MOE_E_ALIGN;
+  if (nvfp4_weights(a)) {
+    if (a->hidden_size % 64 || a->intermediate_size % 64) return B200MOE_E_ALIGN;
+    return (int)launch_gather_nvfp4(
+        a->hidden_states, a->permutation, a->permuted_hidden, c.s.q_planes,
+        nvfp4_token_scales(c.s, a->rows_cap, a->hidden_size, a->intermediate_size), c.s.x_scale,
+        c.s.a_amax, c.assignments, a->num_tokens, a->top_k, a->hidden_size, a->rows_cap, trace_of(c.s), pdl,
+        c.stream);
+  }
   if (fp8_weights(a))
     return (int)launch_gather_fp8(a->hidden_states, a->permutation, a->permuted_hidden,
                                   c.s.q_planes, c.s.x_scale, c.s.a_amax, c.assignments,
@@ -502,6 +617,10 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall*
   if (!aligned16(a->permuted_hidden) || !aligned16(a->gate_up_weight) ||
       !aligned16(a->swiglu_output))
     return B200MOE_E_ALIGN;
+  if (nvfp4_weights(a)) {
+    int rc = check_nvfp4(a);
+    return rc ? rc : do_gate_up_nvfp4(a, c.s, c.assignments, c.dev, pdl, c.stream);
+  }
   if (fp8_weights(a)) {
     if (!a->gate_up_scale) return B200MOE_E_NULL;
     if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
@@ -517,6 +636,10 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall*
 int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr) {
   if (!a->swiglu_output || !a->down_weight) return B200MOE_E_NULL;
   if (!aligned16(a->swiglu_output) || !aligned16(a->down_weight)) return B200MOE_E_ALIGN;
+  if (nvfp4_weights(a)) {
+    int rc = check_nvfp4(a);
+    return rc ? rc : do_down_nvfp4(a, c.s, c.assignments, c.dev, pdl, c.stream);
+  }
   if (fp8_weights(a)) {
     if (!a->down_scale) return B200MOE_E_NULL;
     if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
@@ -556,10 +679,11 @@ int b200moe_build_info(char* json, size_t cap) {
       "\"wrapper_compiled_architecture\": \"sm_100a\", \"uses_fallback\": false, "
       "\"bf16_grouped_gemm_provider\": \"b200moe tcgen05 grouped GEMM (in-tree, hand-written)\", "
       "\"bf16_provider_implementation\": \"tcgen05.mma kind::f16, TMEM accumulators, TMA 128B-swizzle loads\", "
-      "\"cutlass_version\": null, \"cuda_runtime_version\": %d, \"nvfp4_compiled\": false, "
+      "\"cutlass_version\": null, \"cuda_runtime_version\": %d, \"nvfp4_compiled\": %s, "
       "\"fp8_weights_compiled\": true, "
       "\"abi_version\": %d, \"segment_rows\": %d, \"down_split_max\": %d}",
-      (int)CUDART_VERSION, B200MOE_ABI_VERSION, kSegRows, kDownSplitMax);
+      (int)CUDART_VERSION, kNvfp4Ready ? "true" : "false", B200MOE_ABI_VERSION, kSegRows,
+      kDownSplitMax);
   if (json && cap > 0) {
     size_t c = (size_t)n < cap - 1 ? (size_t)n : cap - 1;
     memcpy(json, buf, c);
@@ -604,7 +728,46 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status) {
   return 0;
 }
 
-int b200moe_nvfp4_available(void) { return 0; }
+int b200moe_nvfp4_available(void) { return kNvfp4Ready; }
+
+int b200moe_nvfp4_scale_bytes(int rows, int cols, int halves, size_t* bytes_per_expert) {
+  if (!bytes_per_expert) return B200MOE_E_NULL;
+  if (rows < 1 || cols < 64 || (halves != 1 && halves != 2)) return B200MOE_E_SHAPE;
+  if (cols % 64) return B200MOE_E_ALIGN;
+  *bytes_per_expert = (size_t)halves * ((rows + 127) / 128) * ((cols + 63) / 64) * 512;
+  return 0;
+}
+
+int b200moe_nvfp4_quantize(const void* weights_bf16, int num_experts, int rows, int cols,
+                           int halves, uint8_t* packed_out, uint8_t* block_scale_out,
+                           float* tensor_scale_out, uint32_t* amax_scratch, void* stream) {
+  if (!weights_bf16 || !packed_out || !block_scale_out || !tensor_scale_out || !amax_scratch)
+    return B200MOE_E_NULL;
+  if (num_experts < 1 || num_experts > B200MOE_MAX_EXPERTS || rows < 1 || cols < 64 ||
+      (halves != 1 && halves != 2))
+    return B200MOE_E_SHAPE;
+  if (cols % 64 || !aligned16(weights_bf16) || !aligned16(packed_out) ||
+      !aligned16(block_scale_out))
+    return B200MOE_E_ALIGN;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_nvfp4_quantize(weights_bf16, num_experts, rows, cols, halves, packed_out,
+                                    block_scale_out, tensor_scale_out, amax_scratch,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_nvfp4_rows_to_planes(const float* rows_f32, int num_rows, int cols, uint8_t* planes,
+                                 uint8_t* block_scales, float* row_scale, void* stream) {
+  if (!rows_f32 || !planes || !block_scales || !row_scale) return B200MOE_E_NULL;
+  if (num_rows < 1 || cols < 16) return B200MOE_E_SHAPE;
+  if (cols % 16 || !aligned16(planes)) return B200MOE_E_ALIGN;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  return (int)launch_rows_to_planes_nvfp4(rows_f32, num_rows, cols, planes, block_scales,
+                                          row_scale, static_cast<cudaStream_t>(stream));
+}
 
 int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, int num_experts,
                         int top_k, int64_t* expert_indices, void* weights_bf16,
@@ -928,6 +1091,7 @@ int b200moe_forward(const B200MoeArgs* a, void* stream) {
     if (!a->gate_up_scale || !a->down_scale) return B200MOE_E_NULL;
     if (a->hidden_size % 16 || a->intermediate_size % 16) return B200MOE_E_ALIGN;
   }
+  if (nvfp4_weights(a) && (rc = check_nvfp4(a))) return rc;
   if (small_call(a, c.assignments)) {
     // Small-call order: the gate+up GEMM first (its blocks need nothing from the routing
     // kernel and also do the gather), the routing kernel beside it, then down and combine.

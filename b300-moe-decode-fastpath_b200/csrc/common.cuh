@@ -137,6 +137,8 @@ struct ScratchLayout {
   size_t total;
 };
 
+constexpr int kNvfp4Planes = 4;      // E2M1 planes per token row of the NVFP4-weight path
+constexpr int kSegRowsNvfp4 = 64;    // its longest segment: four planes of 64 rows, N = 64 per MMA
 constexpr int kFp8Planes = 3;        // activation rows of the down projection
 constexpr int kFp8PlanesHidden = 2;  // BF16 hidden rows of gate+up: exact with a power-of-two scale
 
@@ -343,6 +345,19 @@ __device__ __forceinline__ void tma_load_4d_hint(uint32_t dst, const CUtensorMap
       "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
       : "memory");
 }
+// Untiled bulk copy global -> shared memory of this CTA (both 16-byte aligned, size a
+// multiple of 16 bytes), completion on an mbarrier of this CTA.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -442,6 +457,41 @@ __device__ __forceinline__ uint32_t umma_idesc_e4m3_m128(uint32_t n) {
          | (0u << 10)          // B format E4M3
          | ((n >> 3) << 17)    // N / 8
          | ((128u >> 4) << 24);  // M / 16
+}
+
+// Block-scaled FP4: D[tmem] (+)= (A * scale_a)[smem] * (B * scale_b)[smem]^T with E2M1
+// elements, one unsigned-E4M3 scale per 16 elements along K held in tensor memory, FP32
+// accumulate, K = 64 per instruction, issued by ONE thread.
+__device__ __forceinline__ void umma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], "
+      "p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Instruction descriptor of the block-scaled kinds: E2M1 x E2M1, both operands K-major,
+// unsigned-E4M3 scales, M = 128, K = 64.
+__device__ __forceinline__ uint32_t umma_idesc_nvfp4_m128(uint32_t n) {
+  return (1u << 7)             // A format E2M1
+         | (1u << 10)          // B format E2M1
+         | ((n >> 3) << 17)    // N / 8
+         | (0u << 23)          // scale format: unsigned E4M3
+         | ((128u >> 4) << 24);  // M / 16
+}
+// Scale factors shared memory -> tensor memory: 32 rows of 16 bytes (one 128-row x 4-scale
+// tile) land in 4 consecutive columns, lane l / column c holding the four scales of row
+// c * 32 + l, replicated into all four lane quarters.
+__device__ __forceinline__ void tmem_copy_scales(uint32_t dst_tmem, uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address
+  d |= (uint64_t)(128u >> 4) << 32;               // 8-row x 16-byte atoms are 128 bytes apart
+  d |= (uint64_t)1 << 46;                         // descriptor version; no swizzle
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(d)
+               : "memory");
 }
 
 // Four E4M3 bytes (K order k0..k3 from the low byte up) -> two packed BF16 pairs (k0,k1)

@@ -286,11 +286,17 @@ class ClockSampler:
 
 
 WEIGHT_ELEMENT_BYTES = 2  # 1 with --weights fp8
+WEIGHT_FORMAT = "bf16"    # "fp8" / "nvfp4" with --weights
 
 
 def weight_bytes(active_experts: int) -> dict[str, int]:
     """Algorithmic expert-weight bytes one forward must stream from HBM."""
 
+    if WEIGHT_FORMAT == "nvfp4":
+        # packed E2M1 (half a byte) + one E4M3 scale per 16 elements + one FP32 per matrix
+        gate_up = active_experts * (2 * HIDDEN * INTER // 2 + 2 * HIDDEN * INTER // 16 + 4)
+        down = active_experts * (HIDDEN * INTER // 2 + HIDDEN * INTER // 16 + 4)
+        return {"gate_up": gate_up, "down": down, "total": gate_up + down}
     gate_up = active_experts * 2 * HIDDEN * INTER * WEIGHT_ELEMENT_BYTES  # [2I,H] per expert
     down = active_experts * HIDDEN * INTER * WEIGHT_ELEMENT_BYTES         # [H,I] per expert
     if WEIGHT_ELEMENT_BYTES == 1:  # + one FP32 scale per weight row
@@ -676,6 +682,16 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         WEIGHT_ELEMENT_BYTES = 1
         fp8 = quantize_expert_weights_fp8(gate_up, down)
         torch.cuda.synchronize(device)
+    nvfp4 = None
+    if args.weights == "nvfp4":
+        from b200moe import b300_moe_forward_nvfp4, quantize_expert_weights_nvfp4
+
+        global WEIGHT_FORMAT
+        WEIGHT_FORMAT = "nvfp4"
+        nvfp4 = quantize_expert_weights_nvfp4(gate_up, down)
+        torch.cuda.synchronize(device)
+    quantised = fp8 is not None or nvfp4 is not None
+    tag = "fp8" if fp8 is not None else "nvfp4" if nvfp4 is not None else None
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=device)
 
@@ -705,6 +721,9 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         }
 
     def layer_call(inputs, workspace) -> torch.Tensor:
+        if nvfp4 is not None:
+            return b300_moe_forward_nvfp4(*inputs, nvfp4, num_experts=EXPERTS, top_k=TOP_K,
+                                          workspace=workspace)
         if fp8 is not None:
             return b300_moe_forward_fp8(*inputs, fp8, num_experts=EXPERTS, top_k=TOP_K,
                                         workspace=workspace)
@@ -723,7 +742,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         return out
 
     def forward_pinned(T: int) -> torch.Tensor:
-        if fp8 is not None:  # the pinned-host entry point exists for BF16 weights only
+        if quantised:  # timed for BF16 weights only
             return forward_e2e(T)
         # same end-to-end work without staging copies: the kernels read the pinned host
         # inputs and write the pinned host output themselves
@@ -814,7 +833,8 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     for T in sweep:
         c = cases[T]
         layer = StagedLayer(*c["dev"], gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
-                            workspace=c["workspace"], use_pdl=False, fp8_weights=fp8)
+                            workspace=c["workspace"], use_pdl=False, fp8_weights=fp8,
+                            nvfp4_weights=nvfp4)
         layer.forward()
         stage_us: dict[str, dict[str, float]] = {}
         for name in STAGE_NAMES:
@@ -854,7 +874,7 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "gate_up_gbs": round(wb["gate_up"] / stage_us["gate_up_swiglu"]["p50"] / 1e3, 1),
             "down_gbs": round(wb["down"] / stage_us["down"]["p50"] / 1e3, 1),
         }
-        if args.library_gemm_baseline and fp8 is None:
+        if args.library_gemm_baseline and not quantised:
             per_t[str(T)]["library_gemm_us"] = library_gemm_baseline(
                 c, gate_up, down, flush_l2, stage_reps)
 
@@ -869,6 +889,8 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         HIDDEN * 2 + 2 * INTER * 2)  # + token rows in, hi/lo activations out (tiny)
     kernel_name = ("grouped_gemm_fp8_kernel<gate_up> (tcgen05 kind::f8f6f4, SwiGLU epilogue)"
                    if fp8 is not None else
+                   "grouped_gemm_nvfp4_kernel<gate_up> (tcgen05 kind::mxf4nvf4 block-scaled, "
+                   "SwiGLU epilogue)" if nvfp4 is not None else
                    "grouped_gemm_kernel<gate_up> (tcgen05, SwiGLU epilogue)")
     gu_us = [t1["stages_us"]["gate_up"]["p50"]]
     achieved = gu_bytes / gu_us[0] / 1e3
@@ -886,14 +908,14 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
     # the captures are of the Mixtral-shaped layer at T=1 (two active experts)
     if args.config == "mixtral" and sweep[0] == 1:
         roofline["traffic"], roofline["traffic_source"] = measured_traffic(
-            "gate_up_mixtral_T1_fp8" if fp8 is not None else "gate_up_mixtral_T1_bf16")
+            f"gate_up_mixtral_T1_{tag or 'bf16'}")
     else:
         roofline["traffic"], roofline["traffic_source"] = None, "captured for the mixtral T=1 case only"
 
     h2d = sum(cases[T]["host_pack"].numel() for T in sweep)
     d2h = sum(cases[T]["host_out"].numel() * 2 for T in sweep)
     result = {
-        "metric": METRIC if fp8 is None else METRIC + "_fp8_weights",
+        "metric": METRIC if not quantised else METRIC + f"_{tag}_weights",
         "value": round(value, 2),
         "unit": "us",
         "n_gpus": 1,
@@ -904,10 +926,12 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
         "higher_is_better": False,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "bf16" if fp8 is None else "fp8_e4m3 weights x bf16 activations, fp32 accumulate",
+        "dtype": ("bf16" if not quantised else
+                  "fp8_e4m3 weights x bf16 activations, fp32 accumulate" if fp8 is not None else
+                  "nvfp4 weights (e2m1, e4m3 block scales) x bf16 activations, fp32 accumulate"),
         "data": "synthetic",
         "config": {
-            "workload": WORKLOAD if fp8 is None else WORKLOAD.replace("_bf16_", "_fp8w_"),
+            "workload": WORKLOAD if not quantised else WORKLOAD.replace("_bf16_", f"_{tag}w_"),
             "tokens": list(sweep),
             "step": "one forward at each T of the sweep",
         },
@@ -929,12 +953,45 @@ def run_ours(args: argparse.Namespace) -> dict[str, object]:
             "what": "b300_moe_forward_pinned: the same host-resident inputs and output, read and "
                     "written by the kernels directly over PCIe (no staging copies)",
         },
-        "gpu_launches": (5 if fp8 is None else 6) * len(sweep) * args.steps,
+        # BF16: five kernels, four for calls of at most 32 assignments; quantised weights: six
+        "gpu_launches": (6 * len(sweep) if quantised else
+                         sum(4 if T * TOP_K <= 32 else 5 for T in sweep)) * args.steps,
         "clocks": clocks,
         "roofline": roofline,
         "per_T": per_t,
     }
-    if fp8 is None and not args.no_fp8_extra:
+    if not quantised and not args.no_fp8_extra:
+        # the same sweep with NVFP4 expert weights (the reference's cutlass_nvfp4 name)
+        try:
+            from b200moe import _lib as native, b300_moe_forward_nvfp4, quantize_expert_weights_nvfp4
+
+            if not native.load().b200moe_nvfp4_available():
+                raise RuntimeError("the library reports nvfp4_available = 0")
+            nw = quantize_expert_weights_nvfp4(gate_up, down)
+            torch.cuda.synchronize(device)
+
+            def forward_nvfp4(T: int) -> torch.Tensor:
+                c = cases[T]
+                return b300_moe_forward_nvfp4(*c["dev"], nw, num_experts=EXPERTS, top_k=TOP_K,
+                                              workspace=c["workspace"])
+
+            timed_pass(forward_nvfp4, 3)
+            nv_samples = timed_pass(forward_nvfp4, max(10, min(args.steps, 30)))
+            nv_p50 = {str(T): summary(nv_samples[T])["p50"] for T in sweep}
+            nv_mean = sum(nv_p50.values()) / len(nv_p50)
+            result["nvfp4_weights"] = {
+                "what": "b300_moe_forward_nvfp4 (backend name cutlass_nvfp4): E2M1 expert weights "
+                        "with E4M3 block scales, BF16 activations, same inputs and protocol",
+                "value": round(nv_mean, 2),
+                "unit": "us",
+                "per_T_p50_us": nv_p50,
+                "speedup_over_bf16": round(value / nv_mean, 3),
+                "weight_bytes_ratio": round(nw.nbytes / (gate_up.numel() * 2 + down.numel() * 2), 4),
+            }
+            del nw
+        except Exception as error:  # never let the extra line break the contract line
+            result["nvfp4_weights"] = {"unavailable": f"{type(error).__name__}: {error}"[:200]}
+    if fp8 is None and nvfp4 is None and not args.no_fp8_extra:
         # the same sweep with FP8 (E4M3) expert weights, reported beside the BF16 line
         # (a separate entry point and a different weight format: not part of `value`)
         try:
@@ -1433,7 +1490,7 @@ def main() -> int:
                         help="N > 1: combine over NVLink peer memory (default) or NCCL")
     parser.add_argument("--only-tokens", type=int, nargs="*", default=None,
                         help="restrict the sweep (profiling runs); the default is the full sweep")
-    parser.add_argument("--weights", choices=("bf16", "fp8"), default="bf16",
+    parser.add_argument("--weights", choices=("bf16", "fp8", "nvfp4"), default="bf16",
                         help="bf16 (default, the configuration the metric is quoted on) or "
                              "fp8: E4M3 expert weights (b300_moe_forward_fp8 / fp8_scales)")
     parser.add_argument("--no-fp8-extra", action="store_true",
@@ -1455,8 +1512,8 @@ def main() -> int:
         print(prepare_reference(args.prepare_reference))
         return 0
     apply_config(args.config)
-    if args.weights == "fp8":
-        args.no_cpu_baseline = True  # the CPU port restates the reference's BF16 layer
+    if args.weights != "bf16":
+        args.no_cpu_baseline = True  # the CPU legs run the reference's BF16 layer
     if args.config in ("wide", "wide_e16", "deepseek", "deepseek_hotspot"):
         args.no_cpu_baseline = True  # ~21 GiB of weights: the CPU port is not timed on these
     if args.impl == "reference":

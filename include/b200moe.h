@@ -76,6 +76,16 @@ extern "C" {
 /* b200moe_forward stops after the down projection: the caller combines the rows itself
  * (b200moe_ep_combine_reduce on an expert-parallel rank).  `output` is not used. */
 #define B200MOE_FLAG_SKIP_COMBINE  0x20u
+/* Expert weights are NVFP4: gate_up_weight / down_weight point to packed E2M1 elements
+ * ([E,2I,H/2] and [E,H,I/2] bytes, two elements per byte, the even one in the low nibble),
+ * gate_up_block_scale / down_block_scale to their unsigned-E4M3 block scales (one per 16
+ * elements of the reduction dimension, in 512-byte tiles of 128 rows x 4 scales), and
+ * gate_up_scale / down_scale to one FP32 scale per expert matrix; all three are produced by
+ * b200moe_nvfp4_quantize.  weight = tensor scale * block scale * element.  Activations,
+ * accumulation and output are as in the BF16 path.  Needs H and I divisible by 64.  This is
+ * what the reference's "cutlass_nvfp4" backend names and never had
+ * (csrc/quantization_kernels.cu:3-13).  Not combined with B200MOE_FLAG_FP8_WEIGHTS. */
+#define B200MOE_FLAG_NVFP4_WEIGHTS 0x80u
 /* With B200MOE_FLAG_FP8_WEIGHTS the staged entry points keep their meaning, with two
  * details: b200moe_gather also writes the gathered rows as E4M3 planes into scratch, which
  * b200moe_gate_up_swiglu consumes; b200moe_down first turns the activation rows into planes
@@ -149,8 +159,11 @@ typedef struct B200MoeArgs {
   uint32_t ep_epoch;
   uint32_t ep_wait_limit_us;
   /* B200MOE_FLAG_FP8_WEIGHTS only: dequantised weight = E4M3 value * scale of its row */
-  const float* gate_up_scale;        /* [E, 2I] fp32 */
-  const float* down_scale;           /* [E, H]  fp32 */
+  const float* gate_up_scale;        /* [E, 2I] fp32   (NVFP4: [E] fp32, one per expert matrix) */
+  const float* down_scale;           /* [E, H]  fp32   (NVFP4: [E] fp32) */
+  /* B200MOE_FLAG_NVFP4_WEIGHTS only: block scales as b200moe_nvfp4_quantize lays them out */
+  const void* gate_up_block_scale;   /* [E][2][ceil(I/128)][H/64][512] bytes */
+  const void* down_block_scale;      /* [E][ceil(H/128)][I/64][512] bytes */
 } B200MoeArgs;
 
 /*
@@ -405,9 +418,38 @@ int b200moe_status_ptr(void* scratch, size_t scratch_bytes, uint32_t** status);
 
 /*
  * NVFP4 capability probe.  Mirrors nvfp4_grouped_gemm_available_cuda
- * (csrc/quantization_kernels.cu:7-13): always 0; BF16 is never substituted.
+ * (csrc/quantization_kernels.cu:7-13), which always answers 0; here it answers 1: the
+ * block-scaled FP4 grouped GEMMs are compiled in.  BF16 is never substituted for NVFP4.
  */
 int b200moe_nvfp4_available(void);
+
+/*
+ * NVFP4 weight preparation, run once when the model is loaded.  No counterpart in the
+ * reference.  `weights_bf16` is [num_experts][halves * rows][cols] BF16 (halves = 2 for the
+ * gate+up matrix with rows = I, whose gate and up halves get separate scale tilings; 1 for
+ * the down matrix with rows = H; cols is the reduction dimension, a multiple of 64).  Per
+ * expert matrix: tensor_scale = max|w| / (6 * 448) (1 when all zero); per block of 16
+ * elements: block_scale = E4M3(max|block| / 6 / tensor_scale), round to nearest even;
+ * element = E2M1(w / (tensor_scale * block_scale)), round to nearest even, saturating.
+ *   packed_out        [num_experts][halves * rows][cols / 2] bytes
+ *   block_scale_out   num_experts * b200moe_nvfp4_scale_bytes(rows, cols, halves) bytes, zeroed
+ *                     by the caller (rows of a partial last tile stay zero)
+ *   tensor_scale_out  [num_experts] fp32
+ *   amax_scratch      [num_experts] uint32 of device scratch
+ */
+int b200moe_nvfp4_scale_bytes(int rows, int cols, int halves, size_t* bytes_per_expert);
+int b200moe_nvfp4_quantize(const void* weights_bf16, int num_experts, int rows, int cols,
+                           int halves, uint8_t* packed_out, uint8_t* block_scale_out,
+                           float* tensor_scale_out, uint32_t* amax_scratch, void* stream);
+/*
+ * The rule by which the NVFP4 kernels hold a token row, exposed for tests: FP32 rows
+ * [num_rows][cols] -> four E2M1 planes [4][num_rows][cols / 2] bytes, their unsigned-E4M3
+ * block scales [4][num_rows][cols / 16] bytes and one power-of-two FP32 scale per row, with
+ * row ~= row_scale * sum over planes of block_scale * element; every plane quantises what
+ * the planes before it left over.
+ */
+int b200moe_nvfp4_rows_to_planes(const float* rows_f32, int num_rows, int cols, uint8_t* planes,
+                                 uint8_t* block_scales, float* row_scale, void* stream);
 
 /*
  * FP8 (E4M3) weight preparation, run once when the model is loaded.  No counterpart in the

@@ -65,6 +65,22 @@ def quantize_e2m1(x) -> np.ndarray:
     return (code | sign).astype(np.uint8)
 
 
+def _quantize_e2m1_f64(x) -> np.ndarray:
+    """:func:`quantize_e2m1` on float64 input (no rounding to float32 first)."""
+
+    x = np.asarray(x, dtype=np.float64)
+    mag = np.abs(x)
+    grid = E2M1_MAGNITUDES.astype(np.float64)
+    hi = np.clip(np.searchsorted(grid, mag, side="left"), 0, 7)
+    lo = np.clip(hi - 1, 0, 7)
+    d_lo = np.abs(mag - grid[lo])
+    d_hi = np.abs(grid[hi] - mag)
+    pick_hi = (d_hi < d_lo) | ((d_hi == d_lo) & ((hi & 1) == 0))
+    code = np.where(pick_hi, hi, lo)
+    code = np.where(mag >= E2M1_MAX, 7, code)
+    return (code | (np.signbit(x).astype(np.int64) << 3)).astype(np.uint8)
+
+
 def dequantize_e2m1(codes) -> np.ndarray:
     return e2m1_table()[np.asarray(codes, dtype=np.uint8) & 0xF]
 
@@ -170,8 +186,8 @@ def split_planes(rows, planes: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]
 
     ``t = row_scale_pow2(rows)``; the residual starts as ``x``; for every plane and block:
     ``s = e4m3_round_up(max|residual block| / 6 / t)`` (rounded up, so the largest element
-    never saturates), ``q = e2m1(residual / (t * s))``, ``residual -= t * s * q`` (exact in
-    float32).  Returns ``(codes uint8 [planes, R, C], scales uint8 [planes, R, C/16],
+    never saturates), ``q = e2m1(residual / (t * s))`` with the exact quotient rounded to
+    nearest even, ``residual -= t * s * q`` (exact in float32).  Returns ``(codes uint8 [planes, R, C], scales uint8 [planes, R, C/16],
     t float32 [R])`` with ``x ~= t * sum_p s_p * q_p``.
     """
 
@@ -187,7 +203,9 @@ def split_planes(rows, planes: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]
         sf = _e4m3_round_up((amax / np.float32(E2M1_MAX)).astype(np.float32) / t[:, None])
         step = (fp8_oracle.dequantize_e4m3(sf).astype(np.float32) * t[:, None]).astype(np.float32)
         safe = np.where(step > 0, step, np.float32(1.0))
-        codes = quantize_e2m1((residual / safe[..., None]).astype(np.float32))
+        # the exact quotient decides (float64 holds the quotient of two float32 values far
+        # more precisely than the gap to any E2M1 midpoint that is not hit exactly)
+        codes = _quantize_e2m1_f64(residual.astype(np.float64) / safe[..., None].astype(np.float64))
         codes = np.where(step[..., None] > 0, codes, 0).astype(np.uint8)
         residual = (residual - dequantize_e2m1(codes) * step[..., None]).astype(np.float32)
         all_codes.append(codes.reshape(count, cols))

@@ -57,10 +57,10 @@ def test_build_info_attests_sm100a_and_no_fallback(lib) -> None:
     info = _lib.build_info()
     assert info["compiled_architecture"] == "sm_100a"
     assert info["uses_fallback"] is False
-    assert info["nvfp4_compiled"] is False
+    assert info["nvfp4_compiled"] is True
     assert "tcgen05" in info["bf16_grouped_gemm_provider"]
     assert lib.b200moe_abi_version() == _lib.ABI_VERSION
-    assert lib.b200moe_nvfp4_available() == 0
+    assert lib.b200moe_nvfp4_available() == 1
 
 
 def test_args_struct_matches_the_header_field_order() -> None:
@@ -128,7 +128,7 @@ def test_header_is_plain_c_and_links_from_c(lib, tmp_path) -> None:
         "  if (b200moe_scratch_bytes(64, 3, 8, 4096, 14336, &bytes) != B200MOE_E_SHAPE) return 3;\n"
         "  if (b200moe_forward(NULL, NULL) != B200MOE_E_NULL) return 4;\n"
         "  if (b200moe_build_info(info, sizeof info) <= 0 || !strstr(info, \"sm_100a\")) return 5;\n"
-        "  if (b200moe_nvfp4_available() != 0) return 6;\n"
+        "  if (b200moe_nvfp4_available() != 1) return 6;\n"
         "  return 0;\n}\n"
     )
     include = str(HEADER.parent)

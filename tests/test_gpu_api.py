@@ -149,7 +149,9 @@ def test_explicit_failures_on_device(cuda_device) -> None:
     from b200moe import B300MoEWorkspace, b300_moe_forward
 
     tensors = _case(cuda_device)
-    with pytest.raises(RuntimeError, match="NVFP4|nvfp4"):
+    # the NVFP4 backend runs (tests/test_gpu_nvfp4.py) but needs H and I divisible by 64;
+    # it never falls back to the BF16 kernels
+    with pytest.raises(ValueError, match="divisible by 64"):
         b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="cutlass_nvfp4")
     with pytest.raises(RuntimeError, match="not an execution path"):
         b300_moe_forward(*tensors, num_experts=16, top_k=2, backend="torch")

@@ -167,12 +167,13 @@ def test_contract_errors(cuda_device) -> None:
     g72, d72, h72, i72, w72 = _case(4, 72, 128, 2, 3)
     with pytest.raises(ValueError, match="multiple of 16"):
         quantize_expert_weights_fp8(g72.to(cuda_device), d72.to(cuda_device))
-    # the reference's quantised backend name still fails loudly
+    # FP8 weights are their own entry point: the backend names of b300_moe_forward never
+    # select them, and a quantised backend name is never paired with another quant_mode
     from b200moe import b300_moe_forward
 
-    with pytest.raises(RuntimeError, match="cutlass_nvfp4 is unavailable"):
+    with pytest.raises(ValueError, match="requires quant_mode='nvfp4'"):
         b300_moe_forward(*dev, gate_up.to(cuda_device), down.to(cuda_device), num_experts=E,
-                         top_k=K, backend="cutlass_nvfp4")
+                         top_k=K, backend="cutlass_nvfp4", quant_mode="bf16")
 
 
 def test_staged_calls_and_graph_replay_equal_the_forward(cuda_device) -> None:
