@@ -40,6 +40,8 @@ TUNE_SMALL_CALL_MAX = 4
 TUNE_DOWN_TARGET = 5
 TUNE_DOWN_SPLITS = 6
 TUNE_FP8_SEG_ROWS = 7
+TUNE_NVFP4_PREFETCH = 8
+TUNE_NVFP4_ISSUERS = 9
 
 EXPORTS = (
     "b200moe_abi_version",
@@ -230,7 +232,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200moe_nvfp4_rows_to_planes.restype = ctypes.c_int
     lib.b200moe_nvfp4_rows_to_planes.argtypes = [
         ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
-        ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p,
     ]
     lib.b200moe_router_topk.restype = ctypes.c_int
     lib.b200moe_router_topk.argtypes = [

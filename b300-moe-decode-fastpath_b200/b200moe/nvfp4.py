@@ -12,8 +12,8 @@ Format (published NVFP4): element E2M1 (0, 0.5, 1, 1.5, 2, 3, 4, 6 and negatives
 byte), one unsigned-E4M3 scale per 16 elements of the reduction dimension, one FP32 scale per
 expert matrix; ``weight = tensor_scale * block_scale * element``.  The weights feed
 ``tcgen05.mma kind::mxf4nvf4.block_scale`` as they are.  That instruction needs E2M1 on both
-sides, so every token row is held as four E2M1 planes with their own block scales (plane p
-quantises what planes 0..p-1 left over), all accumulated into one FP32 accumulator; the layer
+sides, so every token row is held as four E2M1 planes in fixed point (plane p rounds, in a unit
+eight times finer, what planes 0..p-1 left over), all accumulated in FP32; the layer
 equals the FP32 reference evaluated on the dequantised weights within the usual 2e-2 x RMS bar.
 """
 
@@ -117,23 +117,23 @@ def quantize_expert_weights_nvfp4(gate_up_weight: torch.Tensor, down_weight: tor
     return Nvfp4ExpertWeights(gq, gsf, gs, dq, dsf, ds)
 
 
-def rows_to_planes_nvfp4(rows: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """FP32 ``[R, C]`` rows -> ``(planes uint8 [4, R, C/2], block scales uint8 [4, R, C/16],
-    row scale float32 [R])`` by the rule the kernels use for token rows (for tests)."""
+def rows_to_planes_nvfp4(rows: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """FP32 ``[R, C]`` rows -> ``(planes uint8 [4, R, C/2], row scale float32 [R])`` by the
+    rule the kernels use for token rows: ``row ~= t * (p0 + p1/8 + p2/64 + p3/512)`` (for
+    tests)."""
 
     if rows.device.type != "cuda" or rows.dtype != torch.float32 or rows.ndim != 2 or \
             not rows.is_contiguous():
         raise TypeError("rows_to_planes_nvfp4 needs a contiguous CUDA float32 [R, C] tensor")
     count, cols = rows.shape
     planes = torch.empty(PLANES, count, cols // 2, dtype=torch.uint8, device=rows.device)
-    scales = torch.empty(PLANES, count, cols // 16, dtype=torch.uint8, device=rows.device)
     row_scale = torch.empty(count, dtype=torch.float32, device=rows.device)
     with torch.cuda.device(rows.device):
         code = _lib.load().b200moe_nvfp4_rows_to_planes(
-            rows.data_ptr(), count, cols, planes.data_ptr(), scales.data_ptr(),
-            row_scale.data_ptr(), _stream(rows.device))
+            rows.data_ptr(), count, cols, planes.data_ptr(), row_scale.data_ptr(),
+            _stream(rows.device))
     _lib.check(code, "b200moe_nvfp4_rows_to_planes")
-    return planes, scales, row_scale
+    return planes, row_scale
 
 
 # ---------------------------------------------------------------------------------------

@@ -83,30 +83,28 @@ cudaError_t launch_nvfp4_quantize(const void* w, int experts, int rows, int cols
                                   uint8_t* packed, uint8_t* sf, float* tensor_scale,
                                   uint32_t* amax_scratch, cudaStream_t stream);
 cudaError_t launch_gather_nvfp4(const void* hidden, const int64_t* permutation, void* out,
-                                uint8_t* planes, uint8_t* scales, float* row_scale,
-                                uint32_t* act_amax, int num_assign, int num_tokens, int top_k,
-                                int hidden_size, int rows_cap, unsigned long long* trace,
-                                bool pdl, cudaStream_t stream);
+                                uint8_t* planes, float* row_scale, int num_assign,
+                                int num_tokens, int top_k, int hidden_size, int rows_cap,
+                                unsigned long long* trace, bool pdl, cudaStream_t stream);
 cudaError_t launch_act_planes_nvfp4(const void* act_hi, const void* act_lo,
-                                    const uint32_t* act_amax, uint8_t* planes, uint8_t* scales,
-                                    float* row_scale, int num_assign, int inter, int rows_cap,
-                                    bool pdl, cudaStream_t stream);
+                                    const float* tile_amax, uint8_t* planes, float* row_scale,
+                                    int num_assign, int inter, int rows_cap, bool pdl,
+                                    cudaStream_t stream);
 cudaError_t launch_rows_to_planes_nvfp4(const float* rows, int num_rows, int cols,
-                                        uint8_t* planes, uint8_t* scales, float* row_scale,
+                                        uint8_t* planes, float* row_scale,
                                         cudaStream_t stream);
 cudaError_t launch_gate_up_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_x,
                                  const int32_t* sched, int sched_cap, uint32_t* status,
-                                 void* act_hi, void* act_lo, uint32_t* act_amax,
+                                 void* act_hi, void* act_lo, float* tile_amax,
                                  const uint8_t* sfa, const float* tensor_scale,
-                                 const uint8_t* sfb,
                                  const float* token_scale, int inter, int hidden, int rows_cap,
-                                 int max_rows, int grid, int sm_count, bool pdl,
-                                 cudaStream_t stream);
+                                 int grid, int sm_count, int prefetch_slots, int issuers,
+                                 bool pdl, cudaStream_t stream);
 cudaError_t launch_down_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_act,
                               const int32_t* sched, int sched_cap, uint32_t* status,
                               float* partials, const uint8_t* sfa, const float* tensor_scale,
-                              const uint8_t* sfb, const float* token_scale, int hidden, int inter,
-                              int rows_cap, int max_rows, int grid, int sm_count, bool pdl,
+                              const float* token_scale, int hidden, int inter, int rows_cap,
+                              int grid, int sm_count, int prefetch_slots, bool pdl,
                               cudaStream_t stream);
 
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
@@ -151,6 +149,8 @@ namespace {
 int g_l2_promotion = 2;  // 0 none, 1 128 B, 2 256 B
 int g_down_target = 0;   // blocks the down projection's split-K aims at (0: 2 per SM)
 
+int g_nvfp4_prefetch = 8;   // NVFP4 GEMMs: weight slots requested before the wait for the previous kernel
+int g_nvfp4_issuers = 2;    // NVFP4 gate+up: threads issuing MMAs (1 or 2)
 int g_fp8_seg_rows = kSegRowsFp8;  // segment length of the FP8-weight path (16, 32, 48 or 64)
 int g_down_splits = 0;   // forced split-K factor of the down projection (0: chosen on the device)
 int g_small_call_max = kSmallCallMaxAssign;  // most assignments that run in small-call order (0: never)
@@ -283,12 +283,12 @@ struct Scratch {
   uint32_t* a_amax;
 };
 
-// NVFP4 path: the token planes and their block scales share the scratch bytes of the FP8
-// path's planes (4 planes of W / 2 bytes per row, then 4 x W / 16 scale bytes per row, with
-// W = max(H, I): 2.25 of the 3 bytes per element that region holds).
-uint8_t* nvfp4_token_scales(const Scratch& s, int rows_cap, int hidden, int inter) {
+// NVFP4 path: the token planes and the per-tile activation maxima share the scratch bytes of
+// the FP8 path's planes (4 planes of W / 2 bytes per row, then one float per row and 128
+// columns of I, with W = max(H, I): at most 2.04 of the 3 bytes per element that region holds).
+float* nvfp4_tile_amax(const Scratch& s, int rows_cap, int hidden, int inter) {
   const size_t widest = (size_t)(hidden > inter ? hidden : inter);
-  return s.q_planes + 2 * (size_t)rows_cap * widest;
+  return reinterpret_cast<float*>(s.q_planes + 2 * (size_t)rows_cap * widest);
 }
 
 int carve_scratch(void* scratch, size_t scratch_bytes, int rows_cap, int experts, int hidden,
@@ -476,7 +476,7 @@ int do_gate_up_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments,
   CUtensorMap map_w, map_x;
   {
     const uint64_t dims[4] = {(uint64_t)hidden / 2, (uint64_t)inter, 2, (uint64_t)experts};
-    const uint32_t box[4] = {128, 128, 2, 1};  // 128 gate rows + the 128 matching up rows
+    const uint32_t box[4] = {128, 128, 1, 1};  // 128 gate rows or the 128 matching up rows
     int rc = encode_map(&map_w, a->gate_up_weight, 4, dims, box, true);
     if (rc) return rc;
   }
@@ -485,9 +485,9 @@ int do_gate_up_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments,
   const int grid = segment_bound(assignments, experts, kSegRowsNvfp4) * tiles128(inter);
   return (int)launch_gate_up_nvfp4(
       map_w, map_x, s.sched, max_segments(a->rows_cap, experts), s.status, a->swiglu_output,
-      s.act_lo, s.a_amax, static_cast<const uint8_t*>(a->gate_up_block_scale), a->gate_up_scale,
-      nvfp4_token_scales(s, a->rows_cap, hidden, inter), s.x_scale, inter, hidden, a->rows_cap,
-      assignments, grid, dev.sm_count, pdl, stream);
+      s.act_lo, nvfp4_tile_amax(s, a->rows_cap, hidden, inter),
+      static_cast<const uint8_t*>(a->gate_up_block_scale), a->gate_up_scale, s.x_scale, inter,
+      hidden, a->rows_cap, grid, dev.sm_count, g_nvfp4_prefetch, g_nvfp4_issuers, pdl, stream);
 }
 
 int do_down_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments, const DeviceInfo& dev,
@@ -502,19 +502,18 @@ int do_down_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments, const
   }
   int rc = encode_plane_map(&map_act, s.q_planes, inter / 2, a->rows_cap, kNvfp4Planes);
   if (rc) return rc;
-  uint8_t* token_scales = nvfp4_token_scales(s, a->rows_cap, hidden, inter);
   const int grid = down_grid(segment_bound(assignments, experts, kSegRowsNvfp4),
                              tiles128(hidden), (inter + 255) / 256, dev.sm_count);
   // the activation rows become planes (in the bytes the gathered rows' planes occupied)
-  rc = (int)launch_act_planes_nvfp4(a->swiglu_output, s.act_lo, s.a_amax, s.q_planes,
-                                    token_scales, s.a_scale, assignments, inter, a->rows_cap, pdl,
-                                    stream);
+  rc = (int)launch_act_planes_nvfp4(a->swiglu_output, s.act_lo,
+                                    nvfp4_tile_amax(s, a->rows_cap, hidden, inter), s.q_planes,
+                                    s.a_scale, assignments, inter, a->rows_cap, pdl, stream);
   if (rc) return rc;
   return (int)launch_down_nvfp4(map_w, map_act, s.sched, max_segments(a->rows_cap, experts),
                                 s.status, s.partials,
                                 static_cast<const uint8_t*>(a->down_block_scale), a->down_scale,
-                                token_scales, s.a_scale, hidden, inter, a->rows_cap, assignments,
-                                grid, dev.sm_count, pdl, stream);
+                                s.a_scale, hidden, inter, a->rows_cap, grid, dev.sm_count,
+                                g_nvfp4_prefetch, pdl, stream);
 }
 
 // geometry and pointers the NVFP4 path needs on top of the common checks
@@ -598,9 +597,8 @@ int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
   if (nvfp4_weights(a)) {
     if (a->hidden_size % 64 || a->intermediate_size % 64) return B200MOE_E_ALIGN;
     return (int)launch_gather_nvfp4(
-        a->hidden_states, a->permutation, a->permuted_hidden, c.s.q_planes,
-        nvfp4_token_scales(c.s, a->rows_cap, a->hidden_size, a->intermediate_size), c.s.x_scale,
-        c.s.a_amax, c.assignments, a->num_tokens, a->top_k, a->hidden_size, a->rows_cap, trace_of(c.s), pdl,
+        a->hidden_states, a->permutation, a->permuted_hidden, c.s.q_planes, c.s.x_scale,
+        c.assignments, a->num_tokens, a->top_k, a->hidden_size, a->rows_cap, trace_of(c.s), pdl,
         c.stream);
   }
   if (fp8_weights(a))
@@ -758,15 +756,15 @@ int b200moe_nvfp4_quantize(const void* weights_bf16, int num_experts, int rows, 
 }
 
 int b200moe_nvfp4_rows_to_planes(const float* rows_f32, int num_rows, int cols, uint8_t* planes,
-                                 uint8_t* block_scales, float* row_scale, void* stream) {
-  if (!rows_f32 || !planes || !block_scales || !row_scale) return B200MOE_E_NULL;
+                                 float* row_scale, void* stream) {
+  if (!rows_f32 || !planes || !row_scale) return B200MOE_E_NULL;
   if (num_rows < 1 || cols < 16) return B200MOE_E_SHAPE;
   if (cols % 16 || !aligned16(planes)) return B200MOE_E_ALIGN;
   DeviceInfo dev;
   int rc = current_device_info(&dev);
   if (rc) return rc;
-  return (int)launch_rows_to_planes_nvfp4(rows_f32, num_rows, cols, planes, block_scales,
-                                          row_scale, static_cast<cudaStream_t>(stream));
+  return (int)launch_rows_to_planes_nvfp4(rows_f32, num_rows, cols, planes, row_scale,
+                                          static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, int num_experts,
@@ -836,6 +834,14 @@ int b200moe_tune(int knob, int value) {
     case B200MOE_TUNE_SMALL_CALL_MAX:
       if (value < 0 || value > kSmallCallMaxAssign) return B200MOE_E_SHAPE;
       g_small_call_max = value;
+      return 0;
+    case B200MOE_TUNE_NVFP4_PREFETCH:
+      if (value < 0 || value > 8) return B200MOE_E_SHAPE;
+      g_nvfp4_prefetch = value;
+      return 0;
+    case B200MOE_TUNE_NVFP4_ISSUERS:
+      if (value < 1 || value > 2) return B200MOE_E_SHAPE;
+      g_nvfp4_issuers = value;
       return 0;
     default:
       return B200MOE_E_SHAPE;

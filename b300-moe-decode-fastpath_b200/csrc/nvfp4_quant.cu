@@ -1,5 +1,5 @@
 // NVFP4 data preparation: expert weights -> packed E2M1 + block scales (once, at load time),
-// and token rows -> E2M1 planes with block scales (every forward).
+// and token rows -> E2M1 planes with fixed scales (every forward).
 //
 // No counterpart in the reference, whose NVFP4 backend is a stub that always fails
 // (csrc/quantization_kernels.cu:7-13) and names what a real one needs (:3-6): a 4-bit E2M1
@@ -15,9 +15,13 @@
 // plain bulk copy brings a pipeline stage's scales into shared memory ready for the copy.
 //
 // The block-scaled MMA needs E2M1 on both sides, so the token rows are held as four E2M1
-// planes: plane p quantises, with its own block scales, what planes 0..p-1 left over;
-// x ~= t * sum_p scale_p * element_p with a power-of-two row scale t.  Four planes reproduce
-// a row to 5e-5 of its RMS (BF16 inputs carry 2e-3).
+// planes in fixed point: with a power-of-two row scale t that puts max |row| / t into
+// [2, 4), plane p rounds what planes 0..p-1 left over, divided by t * 8^-p, to E2M1:
+//   x ~= t * (e0 + e1 / 8 + e2 / 64 + e3 / 512),   |x - that| <= t * 2^-10 <= max |row| * 2^-11.
+// Every residual is at most 4 in its plane's unit, where the E2M1 grid is at most 1 apart,
+// so each plane removes three bits; all of it is exact FP32 arithmetic.  The scale of a plane
+// is the same for every block of every row, so the scale factors of the token operand are
+// constants that the GEMM kernels put into tensor memory once (they are never stored).
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -25,7 +29,7 @@
 namespace b200moe {
 
 constexpr int kNvfp4Block = 16;
-constexpr int kNvfp4RowThreads = 256;
+constexpr int kNvfp4RowThreads = 128;   // token-row kernels: one thread per 8 elements of a chunk
 
 __device__ __forceinline__ float e4m3_value(uint32_t code) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
@@ -41,10 +45,11 @@ __device__ __forceinline__ uint32_t e2m1_code(float x) {
   return idx | ((__float_as_uint(x) >> 28) & 8u);
 }
 __device__ __forceinline__ float e2m1_value(uint32_t code) {
-  // magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6
+  // magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6: from index 2 on, 2^(i / 2 - 1) * (1 + (i & 1) / 2),
+  // written straight into the exponent and the top mantissa bit
   const uint32_t i = code & 7u;
-  const float m = i < 2u ? 0.5f * (float)i : ldexpf(1.0f + 0.5f * (float)(i & 1u), (int)(i >> 1) - 1);
-  return (code & 8u) ? -m : m;
+  const uint32_t bits = i < 2u ? (i ? 0x3F000000u : 0u) : (((126u + (i >> 1)) << 23) | ((i & 1u) << 22));
+  return __uint_as_float(bits | ((code & 8u) << 28));
 }
 
 // Byte offset of scale `sf_index` (= k / 16) of row `r` inside one matrix's swizzled scale
@@ -140,59 +145,59 @@ __device__ __forceinline__ float nv_block_max(float v, float* tmp) {
   return m;
 }
 
-// power of two t with max|row| / t in [256, 512); 1 for an all-zero row
+// power of two t with max|row| / t in [2, 4); 1 for an all-zero row (and never below 2^-100,
+// so that t / 8 and t * 8^-3 stay normal numbers)
 __device__ __forceinline__ float row_scale_pow2(float amax) {
   if (!(amax > 0.0f)) return 1.0f;
   int e;
   frexpf(amax, &e);
-  return ldexpf(1.0f, e - 9);
+  return ldexpf(1.0f, max(e - 2, -100));
 }
 
-// 16 values -> kNvfp4Planes planes of 8 packed bytes and one scale byte each.
-__device__ __forceinline__ void block_to_planes(float (&res)[16], float t, uint8_t* planes,
-                                                size_t plane_stride, size_t data_offset,
-                                                uint8_t* scales, size_t scale_stride,
-                                                size_t scale_offset) {
+// 8 values -> kNvfp4Planes planes of 4 packed bytes each.
+__device__ __forceinline__ void octet_to_planes(float (&res)[8], float t, uint8_t* planes,
+                                                size_t plane_stride, size_t data_offset) {
+  float step = t;
 #pragma unroll
   for (int p = 0; p < kNvfp4Planes; ++p) {
-    float amax = 0.0f;
+    // round(residual / step) to E2M1 without dividing: step is a power of two, so the seven
+    // midpoints times step are exact and the comparisons decide exactly
+    const float m025 = 0.25f * step, m075 = 0.75f * step, m125 = 1.25f * step,
+                m175 = 1.75f * step, m250 = 2.5f * step, m350 = 3.5f * step, m500 = 5.0f * step;
+    uint32_t word = 0u;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(res[j]));
-    // smallest E4M3 value >= amax / 6 / t: the largest element never saturates
-    const float target = __fdiv_rn(__fdiv_rn(amax, 6.0f), t);
-    uint32_t code = __nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3);
-    if (e4m3_value(code) < target && code < 0x7Eu) code += 1u;
-    const float step = __fmul_rn(e4m3_value(code), t);
-    uint32_t lo = 0u, hi = 0u;
-    if (step > 0.0f) {
-      // round(residual / step) to E2M1 without dividing: step has four significant bits,
-      // so the seven midpoints times step are exact and the comparisons decide exactly
-      const float m025 = 0.25f * step, m075 = 0.75f * step, m125 = 1.25f * step,
-                  m175 = 1.75f * step, m250 = 2.5f * step, m350 = 3.5f * step, m500 = 5.0f * step;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float m = fabsf(res[j]);
-        const uint32_t idx = (uint32_t)(m > m025) + (uint32_t)(m >= m075) + (uint32_t)(m > m125) +
-                             (uint32_t)(m >= m175) + (uint32_t)(m > m250) + (uint32_t)(m >= m350) +
-                             (uint32_t)(m > m500);
-        const uint32_t q = idx | ((__float_as_uint(res[j]) >> 28) & 8u);
-        if (j < 8) lo |= q << (4 * j);
-        else hi |= q << (4 * (j - 8));
-        res[j] = __fsub_rn(res[j], __fmul_rn(e2m1_value(q), step));
-      }
+    for (int j = 0; j < 8; ++j) {
+      const float m = fabsf(res[j]);
+      const uint32_t idx = (uint32_t)(m > m025) + (uint32_t)(m >= m075) + (uint32_t)(m > m125) +
+                           (uint32_t)(m >= m175) + (uint32_t)(m > m250) + (uint32_t)(m >= m350) +
+                           (uint32_t)(m > m500);
+      const uint32_t q = idx | ((__float_as_uint(res[j]) >> 28) & 8u);
+      word |= q << (4 * j);
+      res[j] = __fsub_rn(res[j], __fmul_rn(e2m1_value(q), step));
     }
-    *reinterpret_cast<uint2*>(planes + p * plane_stride + data_offset) = make_uint2(lo, hi);
-    scales[p * scale_stride + scale_offset] = (uint8_t)code;
+    *reinterpret_cast<uint32_t*>(planes + p * plane_stride + data_offset) = word;
+    step *= 0.125f;
+  }
+}
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& x, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = __bfloat1622float2(h[j]);
+    f[2 * j] = v.x;
+    f[2 * j + 1] = v.y;
   }
 }
 
 // Gather for the NVFP4 path: permuted_hidden[p, :] = hidden[permutation[p] / K, :] as in
-// gather_rows_kernel, plus the row's planes, block scales and row scale in scratch.
+// gather_rows_kernel, plus the row's planes and row scale in scratch.  One block per (row,
+// chunk of 1024 columns): every block reads the whole row for its maximum (8 KB, from L2
+// after the first) and converts its own chunk, one thread per 8 columns.
 __global__ void __launch_bounds__(kNvfp4RowThreads)
 gather_rows_nvfp4_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ permutation,
                          uint4* __restrict__ out, uint8_t* __restrict__ planes,
-                         uint8_t* __restrict__ scales, float* __restrict__ row_scale,
-                         uint32_t* __restrict__ act_amax, int num_assign, int num_tokens,
+                         float* __restrict__ row_scale, int num_assign, int num_tokens,
                          int top_k, int hidden_size, int rows_cap,
                          unsigned long long* __restrict__ trace) {
   __shared__ float s_tmp[kNvfp4RowThreads / 32];
@@ -201,95 +206,79 @@ gather_rows_nvfp4_kernel(const uint4* __restrict__ hidden, const int64_t* __rest
   trace_start(trace, kTraceGather);
   const int row = blockIdx.x;
   const int vec_per_row = hidden_size / 8;
+  const int own = blockIdx.y * kNvfp4RowThreads + threadIdx.x;
   const int64_t a = permutation[row];
   const bool valid = a >= 0 && a < (int64_t)num_assign && (a / top_k) < (int64_t)num_tokens;
   const uint4* src = hidden + (valid ? (size_t)(a / top_k) * vec_per_row : 0);
-  uint4* dst = out + (size_t)row * vec_per_row;
   float amax = 0.0f;
+  uint4 mine = make_uint4(0u, 0u, 0u, 0u);
   for (int v = threadIdx.x; v < vec_per_row; v += kNvfp4RowThreads) {
+    // this block's chunk comes round in turn blockIdx.y of this loop
     uint4 x = make_uint4(0u, 0u, 0u, 0u);
     if (valid) x = __ldg(src + v);
-    dst[v] = x;
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+    if (v == own) mine = x;
+    float f[8];
+    bf16x8_to_float(x, f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __bfloat1622float2(h[i]);
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-    }
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
   }
   amax = nv_block_max(amax, s_tmp);
   const float t = row_scale_pow2(amax);
-  if (threadIdx.x == 0) {
-    row_scale[row] = t;
-    act_amax[row] = 0u;   // the gate+up kernel accumulates the row's max |activation| next
-  }
-  const size_t plane_stride = (size_t)rows_cap * (hidden_size / 2);
-  const size_t scale_stride = (size_t)rows_cap * (hidden_size / kNvfp4Block);
-  for (int b = threadIdx.x; b < hidden_size / kNvfp4Block; b += kNvfp4RowThreads) {
-    uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
-    if (valid) {
-      x0 = __ldg(src + 2 * b);
-      x1 = __ldg(src + 2 * b + 1);
-    }
-    const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&x0);
-    const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&x1);
-    float res[16];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f0 = __bfloat1622float2(h0[j]), f1 = __bfloat1622float2(h1[j]);
-      res[2 * j] = f0.x; res[2 * j + 1] = f0.y; res[8 + 2 * j] = f1.x; res[8 + 2 * j + 1] = f1.y;
-    }
-    block_to_planes(res, t, planes, plane_stride, (size_t)row * (hidden_size / 2) + (size_t)b * 8,
-                    scales, scale_stride, (size_t)row * (hidden_size / kNvfp4Block) + b);
+  if (threadIdx.x == 0 && blockIdx.y == 0) row_scale[row] = t;
+  if (own < vec_per_row) {
+    out[(size_t)row * vec_per_row + own] = mine;
+    float res[8];
+    bf16x8_to_float(mine, res);
+    octet_to_planes(res, t, planes, (size_t)rows_cap * (hidden_size / 2),
+                    (size_t)row * (hidden_size / 2) + (size_t)own * 4);
   }
   trace_end(trace, kTraceGather);
 }
 
-// Between the two NVFP4 GEMMs: activation rows (hi + lo BF16 halves, maximum already known
-// from the gate+up epilogue) -> planes, block scales and a row scale, in the bytes the
-// gathered rows' planes occupied.  One block per (row, 256 blocks of 16 columns): the row
-// scale only needs the maximum, so the chunks of a row are independent.
+// Between the two NVFP4 GEMMs: activation rows (hi + lo BF16 halves) -> planes and a row
+// scale, in the bytes the gathered rows' planes occupied.  The gate+up epilogue left the
+// maximum |activation| of every (row, 128-column tile); the row scale only needs their
+// maximum, so the chunks of a row are independent: one block per (row, 1024 columns), one
+// thread per 8 columns.
 __global__ void __launch_bounds__(kNvfp4RowThreads)
 act_planes_nvfp4_kernel(const uint4* __restrict__ act_hi, const uint4* __restrict__ act_lo,
-                        const uint32_t* __restrict__ act_amax, uint8_t* __restrict__ planes,
-                        uint8_t* __restrict__ scales, float* __restrict__ row_scale, int inter,
-                        int rows_cap) {
+                        const float* __restrict__ tile_amax, uint8_t* __restrict__ planes,
+                        float* __restrict__ row_scale, int inter, int rows_cap) {
+  __shared__ float s_tmp[kNvfp4RowThreads / 32];
   // the down grid may become resident and prefetch weight tiles now; it waits for this
   // grid's completion before it touches the planes
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
-  const float t = row_scale_pow2(__uint_as_float(act_amax[row]));
-  if (threadIdx.x == 0 && blockIdx.y == 0) row_scale[row] = t;
-  const int b = blockIdx.y * kNvfp4RowThreads + threadIdx.x;
-  if (b >= inter / kNvfp4Block) return;
   const int vec_per_row = inter / 8;
-  const uint4* hi = act_hi + (size_t)row * vec_per_row;
-  const uint4* lo = act_lo + (size_t)row * vec_per_row;
-  float res[16];
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const uint4 xh = hi[2 * b + half], xl = lo[2 * b + half];
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xh);
-    const __nv_bfloat162* l = reinterpret_cast<const __nv_bfloat162*>(&xl);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 fh = __bfloat1622float2(h[j]), fl = __bfloat1622float2(l[j]);
-      res[8 * half + 2 * j] = __fadd_rn(fh.x, fl.x);
-      res[8 * half + 2 * j + 1] = __fadd_rn(fh.y, fl.y);
-    }
+  const int own = blockIdx.y * kNvfp4RowThreads + threadIdx.x;
+  // the activations are requested before the maximum is known
+  uint4 xh = make_uint4(0u, 0u, 0u, 0u), xl = xh;
+  if (own < vec_per_row) {
+    xh = act_hi[(size_t)row * vec_per_row + own];
+    xl = act_lo[(size_t)row * vec_per_row + own];
   }
-  const size_t plane_stride = (size_t)rows_cap * (inter / 2);
-  const size_t scale_stride = (size_t)rows_cap * (inter / kNvfp4Block);
-  block_to_planes(res, t, planes, plane_stride, (size_t)row * (inter / 2) + (size_t)b * 8, scales,
-                  scale_stride, (size_t)row * (inter / kNvfp4Block) + b);
+  const int tiles = (inter + 127) / 128;
+  float amax = 0.0f;
+  for (int i = threadIdx.x; i < tiles; i += kNvfp4RowThreads)
+    amax = fmaxf(amax, tile_amax[(size_t)row * tiles + i]);
+  amax = nv_block_max(amax, s_tmp);
+  const float t = row_scale_pow2(amax);
+  if (threadIdx.x == 0 && blockIdx.y == 0) row_scale[row] = t;
+  if (own >= vec_per_row) return;
+  float hi[8], lo[8], res[8];
+  bf16x8_to_float(xh, hi);
+  bf16x8_to_float(xl, lo);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) res[j] = __fadd_rn(hi[j], lo[j]);
+  octet_to_planes(res, t, planes, (size_t)rows_cap * (inter / 2),
+                  (size_t)row * (inter / 2) + (size_t)own * 4);
 }
 
 // Standalone row -> planes conversion of FP32 rows (tests of the plane rule).
 __global__ void __launch_bounds__(kNvfp4RowThreads)
 rows_to_planes_nvfp4_kernel(const float* __restrict__ rows, uint8_t* __restrict__ planes,
-                            uint8_t* __restrict__ scales, float* __restrict__ row_scale,
-                            int cols, int rows_cap) {
+                            float* __restrict__ row_scale, int cols, int rows_cap) {
   __shared__ float s_tmp[kNvfp4RowThreads / 32];
   const int row = blockIdx.x;
   const float* src = rows + (size_t)row * cols;
@@ -297,16 +286,14 @@ rows_to_planes_nvfp4_kernel(const float* __restrict__ rows, uint8_t* __restrict_
   for (int c = threadIdx.x; c < cols; c += kNvfp4RowThreads) amax = fmaxf(amax, fabsf(src[c]));
   amax = nv_block_max(amax, s_tmp);
   const float t = row_scale_pow2(amax);
-  if (threadIdx.x == 0) row_scale[row] = t;
-  const size_t plane_stride = (size_t)rows_cap * (cols / 2);
-  const size_t scale_stride = (size_t)rows_cap * (cols / kNvfp4Block);
-  for (int b = threadIdx.x; b < cols / kNvfp4Block; b += kNvfp4RowThreads) {
-    float res[16];
+  if (threadIdx.x == 0 && blockIdx.y == 0) row_scale[row] = t;
+  const int own = blockIdx.y * kNvfp4RowThreads + threadIdx.x;
+  if (own >= cols / 8) return;
+  float res[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) res[j] = src[b * 16 + j];
-    block_to_planes(res, t, planes, plane_stride, (size_t)row * (cols / 2) + (size_t)b * 8, scales,
-                    scale_stride, (size_t)row * (cols / kNvfp4Block) + b);
-  }
+  for (int j = 0; j < 8; ++j) res[j] = src[own * 8 + j];
+  octet_to_planes(res, t, planes, (size_t)rows_cap * (cols / 2),
+                  (size_t)row * (cols / 2) + (size_t)own * 4);
 }
 
 // ---- launchers -------------------------------------------------------------------------
@@ -338,35 +325,36 @@ static cudaError_t launch_rows_pdl(const void* func, int rows, int chunks, void*
 }
 
 cudaError_t launch_gather_nvfp4(const void* hidden, const int64_t* permutation, void* out,
-                                uint8_t* planes, uint8_t* scales, float* row_scale,
-                                uint32_t* act_amax, int num_assign, int num_tokens, int top_k,
-                                int hidden_size, int rows_cap, unsigned long long* trace,
-                                bool pdl, cudaStream_t stream) {
+                                uint8_t* planes, float* row_scale, int num_assign,
+                                int num_tokens, int top_k, int hidden_size, int rows_cap,
+                                unsigned long long* trace, bool pdl, cudaStream_t stream) {
   const uint4* h = static_cast<const uint4*>(hidden);
   uint4* o = static_cast<uint4*>(out);
-  void* args[] = {&h, &permutation, &o, &planes, &scales, &row_scale, &act_amax, &num_assign,
+  void* args[] = {&h, &permutation, &o, &planes, &row_scale, &num_assign,
                   &num_tokens, &top_k, &hidden_size, &rows_cap, &trace};
-  return launch_rows_pdl(reinterpret_cast<const void*>(&gather_rows_nvfp4_kernel), num_assign, 1,
-                         args, pdl, stream);
+  const int chunks = (hidden_size / 8 + kNvfp4RowThreads - 1) / kNvfp4RowThreads;
+  return launch_rows_pdl(reinterpret_cast<const void*>(&gather_rows_nvfp4_kernel), num_assign,
+                         chunks, args, pdl, stream);
 }
 
 cudaError_t launch_act_planes_nvfp4(const void* act_hi, const void* act_lo,
-                                    const uint32_t* act_amax, uint8_t* planes, uint8_t* scales,
-                                    float* row_scale, int num_assign, int inter, int rows_cap,
-                                    bool pdl, cudaStream_t stream) {
+                                    const float* tile_amax, uint8_t* planes, float* row_scale,
+                                    int num_assign, int inter, int rows_cap, bool pdl,
+                                    cudaStream_t stream) {
   const uint4* hi = static_cast<const uint4*>(act_hi);
   const uint4* lo = static_cast<const uint4*>(act_lo);
-  void* args[] = {&hi, &lo, &act_amax, &planes, &scales, &row_scale, &inter, &rows_cap};
-  const int chunks = (inter / kNvfp4Block + kNvfp4RowThreads - 1) / kNvfp4RowThreads;
+  void* args[] = {&hi, &lo, &tile_amax, &planes, &row_scale, &inter, &rows_cap};
+  const int chunks = (inter / 8 + kNvfp4RowThreads - 1) / kNvfp4RowThreads;
   return launch_rows_pdl(reinterpret_cast<const void*>(&act_planes_nvfp4_kernel), num_assign,
                          chunks, args, pdl, stream);
 }
 
 cudaError_t launch_rows_to_planes_nvfp4(const float* rows, int num_rows, int cols,
-                                        uint8_t* planes, uint8_t* scales, float* row_scale,
+                                        uint8_t* planes, float* row_scale,
                                         cudaStream_t stream) {
-  rows_to_planes_nvfp4_kernel<<<num_rows, kNvfp4RowThreads, 0, stream>>>(rows, planes, scales,
-                                                                        row_scale, cols, num_rows);
+  const int chunks = (cols / 8 + kNvfp4RowThreads - 1) / kNvfp4RowThreads;
+  rows_to_planes_nvfp4_kernel<<<dim3(num_rows, chunks), kNvfp4RowThreads, 0, stream>>>(
+      rows, planes, row_scale, cols, num_rows);
   return cudaGetLastError();
 }
 

@@ -4,7 +4,8 @@
 // softmax of the selected logits in FP32, cast back to the logits' dtype) and what its
 // benchmark counts inside routing_us / total_us (benchmark/benchmark_goal_1b.py:464).
 // Selected experts come out in descending logit order; among equal logits the lower
-// expert id wins.
+// expert id wins; a NaN logit ranks above every number, as torch.topk ranks it, and a row
+// of NaN or -inf still yields top_k distinct ids in [0, E).
 #include "common.cuh"
 
 namespace b200moe {
@@ -37,36 +38,43 @@ router_topk_kernel(const T* __restrict__ logits, int num_tokens, int num_experts
     const int e = lane + 32 * i;
     v[i] = e < num_experts ? logit_to_float(logits[(size_t)token * num_experts + e]) : -INFINITY;
   }
+  // Selection key: the logit's bits mapped to an unsigned order (NaN above every number,
+  // as torch.topk ranks it; -inf still above nothing), then the lower expert id; 0 marks
+  // an entry that is taken or does not exist.  Every slot therefore gets an id in [0, E)
+  // as long as top_k <= E, whatever the logits hold.
+  unsigned long long key[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int e = lane + 32 * i;
+    const uint32_t bits = __float_as_uint(v[i]);
+    uint32_t order = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    if (v[i] != v[i]) order = 0xFFFFFFFFu;
+    key[i] = e < num_experts ? ((unsigned long long)order << 32) | (uint32_t)(0x7fffffff - e) : 0ull;
+  }
   float sel[8];
   float denom = 0.0f;
   for (int k = 0; k < top_k; ++k) {
-    // lane-local best (lowest index on ties), then warp argmax on (value, -index)
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
+    unsigned long long best = 0ull;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = lane + 32 * i;
-      if (v[i] > best || (v[i] == best && e < best_e && v[i] != -INFINITY)) {
-        best = v[i];
-        best_e = e;
-      }
-    }
+    for (int i = 0; i < 8; ++i) best = key[i] > best ? key[i] : best;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, d);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
-      if (ov > best || (ov == best && oe < best_e)) {
-        best = ov;
-        best_e = oe;
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, d);
+      best = other > best ? other : best;
+    }
+    const int best_e = 0x7fffffff - (int)(uint32_t)(best & 0xFFFFFFFFull);
+    float value = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (lane + 32 * i == best_e) {
+        value = v[i];
+        key[i] = 0ull;  // taken
       }
     }
-    if ((best_e & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (lane + 32 * i == best_e) v[i] = -INFINITY;  // taken
-    }
+    // the owner lane holds the logit; everyone needs it for the softmax
+    value = __shfl_sync(0xffffffffu, value, best_e & 31);
     if (lane == 0) ids[(size_t)token * top_k + k] = best_e;
-    sel[k] = best;
+    sel[k] = value;
   }
   // softmax over the selected logits; sel[0] is the maximum
   const float top = sel[0];

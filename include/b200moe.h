@@ -443,13 +443,13 @@ int b200moe_nvfp4_quantize(const void* weights_bf16, int num_experts, int rows, 
                            float* tensor_scale_out, uint32_t* amax_scratch, void* stream);
 /*
  * The rule by which the NVFP4 kernels hold a token row, exposed for tests: FP32 rows
- * [num_rows][cols] -> four E2M1 planes [4][num_rows][cols / 2] bytes, their unsigned-E4M3
- * block scales [4][num_rows][cols / 16] bytes and one power-of-two FP32 scale per row, with
- * row ~= row_scale * sum over planes of block_scale * element; every plane quantises what
- * the planes before it left over.
+ * [num_rows][cols] -> four E2M1 planes [4][num_rows][cols / 2] bytes and one power-of-two
+ * FP32 scale t per row (max |row| / t in [2, 4)), with
+ * row ~= t * (plane0 + plane1 / 8 + plane2 / 64 + plane3 / 512); every plane rounds what the
+ * planes before it left over, so |row - that| <= t / 1024.
  */
 int b200moe_nvfp4_rows_to_planes(const float* rows_f32, int num_rows, int cols, uint8_t* planes,
-                                 uint8_t* block_scales, float* row_scale, void* stream);
+                                 float* row_scale, void* stream);
 
 /*
  * FP8 (E4M3) weight preparation, run once when the model is loaded.  No counterpart in the
@@ -502,6 +502,10 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              the weight stream and re-read weights of longer experts)
  *   B200MOE_TUNE_DOWN_TARGET   number of blocks the split-K of the down projection aims
  *                              at when few (segment, tile) units exist (0 = default)
+ *   B200MOE_TUNE_NVFP4_PREFETCH  NVFP4 GEMMs: weight slots a block requests before it waits
+ *                              for the previous kernel (0..8, default 8 = the whole ring)
+ *   B200MOE_TUNE_NVFP4_ISSUERS  NVFP4 gate+up: 1 = one thread issues the MMAs of the gate and
+ *                              the up tile, 2 = one thread each (default)
  */
 #define B200MOE_TUNE_STAGE_KB     1
 #define B200MOE_TUNE_L2_PROMOTION 2
@@ -510,6 +514,8 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
 #define B200MOE_TUNE_DOWN_TARGET  5
 #define B200MOE_TUNE_DOWN_SPLITS  6
 #define B200MOE_TUNE_FP8_SEG_ROWS 7
+#define B200MOE_TUNE_NVFP4_PREFETCH 8
+#define B200MOE_TUNE_NVFP4_ISSUERS 9
 int b200moe_tune(int knob, int value);
 
 #ifdef __cplusplus

@@ -25,8 +25,8 @@ Layer semantics with NVFP4 weights = the FP32 oracle (``moe_oracle.routed_moe``)
 dequantised weights; the same 2e-2 x RMS bar applies.
 
 The token operand of the block-scaled tensor-core instruction must be E2M1 as well, so the
-kernels hold each token row as several E2M1 *planes* with their own block scales
-(``split_planes``): plane p quantises what planes 0..p-1 left over.
+kernels hold each token row as several E2M1 *planes* in fixed point (``split_planes``):
+plane p rounds what planes 0..p-1 left over, in a unit eight times finer than the one before.
 """
 
 from __future__ import annotations
@@ -100,14 +100,6 @@ def unpack_nibbles(packed) -> np.ndarray:
     return out
 
 
-def _e4m3_round_up(x) -> np.ndarray:
-    """Smallest positive-E4M3 code whose value is >= x (x >= 0, saturating at 448)."""
-
-    grid = fp8_oracle.e4m3_table()[:0x7F].astype(np.float64)
-    code = np.searchsorted(grid, np.asarray(x, dtype=np.float64), side="left")
-    return np.clip(code, 0, 0x7E).astype(np.uint8)
-
-
 def quantize_weights(weights: torch.Tensor) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
     """``[E, rows, cols]`` weights -> ``(packed uint8 [E, rows, cols/2], block_scale uint8
     [E, rows, cols/16], tensor_scale float32 [E])``.
@@ -170,54 +162,49 @@ def swizzle_block_scales(block_scale) -> np.ndarray:
         sf.shape[:-2] + (row_tiles, k_tiles, 512))
 
 
+PLANE_STEP = 0.125   # every plane's unit is an eighth of the one before
+
+
 def row_scale_pow2(rows) -> np.ndarray:
     """Per-row float32 scale of the token planes: the power of two ``t`` with
-    ``max|row| / t`` in ``[256, 512)`` (1 for an all-zero row), so that ``max|block| / 6 / t``
-    sits in the middle of the E4M3 range and every product ``t * scale * element`` is exact."""
+    ``max|row| / t`` in ``[2, 4)`` (1 for an all-zero row, never below 2**-100)."""
 
     x = np.asarray(rows, dtype=np.float32)
     amax = np.max(np.abs(x), axis=-1)
     _, exponent = np.frexp(amax)
-    return np.where(amax > 0, np.ldexp(np.float32(1.0), exponent - 9), np.float32(1.0)).astype(np.float32)
+    exponent = np.maximum(exponent - 2, -100)
+    return np.where(amax > 0, np.ldexp(np.float32(1.0), exponent), np.float32(1.0)).astype(np.float32)
 
 
-def split_planes(rows, planes: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
-    """Token rows ``[R, C]`` as ``planes`` E2M1 planes with block scales.
+def split_planes(rows, planes: int) -> tuple[np.ndarray, np.ndarray]:
+    """Token rows ``[R, C]`` as ``planes`` E2M1 planes in fixed point.
 
-    ``t = row_scale_pow2(rows)``; the residual starts as ``x``; for every plane and block:
-    ``s = e4m3_round_up(max|residual block| / 6 / t)`` (rounded up, so the largest element
-    never saturates), ``q = e2m1(residual / (t * s))`` with the exact quotient rounded to
-    nearest even, ``residual -= t * s * q`` (exact in float32).  Returns ``(codes uint8 [planes, R, C], scales uint8 [planes, R, C/16],
-    t float32 [R])`` with ``x ~= t * sum_p s_p * q_p``.
+    ``t = row_scale_pow2(rows)``; the residual starts as ``x``; plane ``p`` is
+    ``q_p = e2m1(residual / (t * 8**-p))`` (nearest, ties to the even mantissa bit) and
+    ``residual -= t * 8**-p * q_p``.  Every step is exact in float32: the units are powers of
+    two and the residual is a multiple of a much smaller one.  ``|x| / t < 4`` lies where the
+    E2M1 grid is at most 1 apart, so the first residual is at most ``t / 2 = 4 * t / 8`` and,
+    in turn, every plane removes three bits: ``|x - t * sum_p 8**-p q_p| <= t * 8**-(planes-1) / 2``.
+    Returns ``(codes uint8 [planes, R, C], t float32 [R])``.
     """
 
     x = np.asarray(rows, dtype=np.float32)
-    count, cols = x.shape
-    if cols % BLOCK:
-        raise ValueError("the row length must be a multiple of 16")
     t = row_scale_pow2(x)
-    residual = x.reshape(count, cols // BLOCK, BLOCK).copy()
-    all_codes, all_scales = [], []
+    residual = x.copy()
+    all_codes = []
+    step = t[:, None].astype(np.float32)
     for _ in range(planes):
-        amax = np.max(np.abs(residual), axis=-1)
-        sf = _e4m3_round_up((amax / np.float32(E2M1_MAX)).astype(np.float32) / t[:, None])
-        step = (fp8_oracle.dequantize_e4m3(sf).astype(np.float32) * t[:, None]).astype(np.float32)
-        safe = np.where(step > 0, step, np.float32(1.0))
-        # the exact quotient decides (float64 holds the quotient of two float32 values far
-        # more precisely than the gap to any E2M1 midpoint that is not hit exactly)
-        codes = _quantize_e2m1_f64(residual.astype(np.float64) / safe[..., None].astype(np.float64))
-        codes = np.where(step[..., None] > 0, codes, 0).astype(np.uint8)
-        residual = (residual - dequantize_e2m1(codes) * step[..., None]).astype(np.float32)
-        all_codes.append(codes.reshape(count, cols))
-        all_scales.append(sf)
-    return np.stack(all_codes), np.stack(all_scales), t
+        # a power-of-two divisor: the float64 quotient is exact
+        codes = _quantize_e2m1_f64(residual.astype(np.float64) / step.astype(np.float64)).astype(np.uint8)
+        residual = (residual - dequantize_e2m1(codes) * step).astype(np.float32)
+        all_codes.append(codes)
+        step = (step * np.float32(PLANE_STEP)).astype(np.float32)
+    return np.stack(all_codes), t
 
 
-def join_planes(codes, scales, t) -> np.ndarray:
+def join_planes(codes, t) -> np.ndarray:
     """Inverse of :func:`split_planes` in float64."""
 
     values = dequantize_e2m1(codes).astype(np.float64)
-    planes, count, cols = values.shape
-    sf = fp8_oracle.dequantize_e4m3(scales).astype(np.float64)
-    blocks = values.reshape(planes, count, cols // BLOCK, BLOCK) * sf[..., None]
-    return blocks.reshape(planes, count, cols).sum(axis=0) * np.asarray(t, np.float64)[:, None]
+    weights = PLANE_STEP ** np.arange(values.shape[0], dtype=np.float64)
+    return (values * weights[:, None, None]).sum(axis=0) * np.asarray(t, np.float64)[:, None]

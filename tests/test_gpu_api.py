@@ -548,6 +548,30 @@ def test_router_topk_matches_reference_golden(case, cuda_device) -> None:
                                rtol=ulp)
 
 
+def test_router_keeps_ids_in_range_on_nan_and_infinite_logits(cuda_device) -> None:
+    """A NaN logit ranks first, as in ``torch.topk``; rows of -inf or NaN still give top_k
+    distinct experts in [0, E), so a poisoned router output cannot index past the weights."""
+
+    from b200moe import topk_routing
+
+    E, K = 40, 4
+    logits = torch.randn(5, E, generator=torch.Generator().manual_seed(9))
+    logits[1, 17] = float("nan")
+    logits[2] = float("-inf")
+    logits[3] = float("nan")
+    logits[4, :38] = float("-inf")          # fewer finite logits than top_k
+    ids, weights = topk_routing(logits.to(cuda_device), K)
+    ids = ids.cpu()
+    assert int(ids.min()) >= 0 and int(ids.max()) < E
+    assert all(len(set(row.tolist())) == K for row in ids)
+    want_ids, _ = moe_oracle.topk_routing(logits, K)
+    assert torch.equal(ids[0], want_ids[0])
+    assert int(ids[1, 0]) == 17 and torch.equal(ids[1, 1:], want_ids[0 + 1, 1:])
+    assert ids[2].tolist() == [0, 1, 2, 3] and ids[3].tolist() == [0, 1, 2, 3]
+    assert ids[4].tolist() == [38, 39, 0, 1] or ids[4].tolist() == [39, 38, 0, 1]
+    assert torch.isfinite(weights[0]).all()
+
+
 def test_router_then_layer_end_to_end(cuda_device) -> None:
     from b200moe import b300_moe_forward, topk_routing, workloads
 
