@@ -224,13 +224,18 @@ class _CallPlan:
     __slots__ = ("h_shape", "r_shape", "device", "device_index", "gate_up_ptr", "down_ptr",
                  "gate_up_shape", "num_experts", "top_k", "backend", "quant_mode_in",
                  "gemm_policy", "use_pdl", "allocations", "stream", "stream_ptr", "args",
-                 "args_ref", "flags", "fn", "last_shape")
+                 "args_ref", "flags", "fn", "last_shape", "weights_obj")
 
 
 def _remember_plan(workspace, hidden_states, expert_indices, gate_up_weight, down_weight,
                    num_experts, top_k, backend, quant_mode_in, gemm_policy, use_pdl, shape,
-                   flags) -> None:
+                   flags, weights_obj=None) -> None:
+    """``weights_obj``: the quantised-weights object of the FP8 / NVFP4 entry points (its
+    payload tensors stand in for the BF16 weight tensors; the scale pointers stay in the
+    bound argument struct, so the object itself is part of the signature)."""
+
     plan = _CallPlan()
+    plan.weights_obj = weights_obj
     plan.h_shape = hidden_states.shape
     plan.r_shape = expert_indices.shape
     plan.device = hidden_states.device
@@ -254,12 +259,14 @@ def _remember_plan(workspace, hidden_states, expert_indices, gate_up_weight, dow
 
 
 def _repeat_call(workspace, hidden_states, expert_indices, expert_weights, gate_up_weight,
-                 down_weight, num_experts, top_k, quant_mode, backend, gemm_policy, use_pdl):
+                 down_weight, num_experts, top_k, quant_mode, backend, gemm_policy, use_pdl,
+                 weights_obj=None):
     """The output of a call that matches the workspace's remembered plan, or ``None``."""
 
     plan = workspace._plan
     if (
         plan is None
+        or plan.weights_obj is not weights_obj
         or hidden_states.shape != plan.h_shape
         or expert_indices.shape != plan.r_shape
         or expert_weights.shape != plan.r_shape

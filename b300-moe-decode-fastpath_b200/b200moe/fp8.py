@@ -23,7 +23,8 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from .forward import _enqueue, _native_args, _resolve_native_backend
+from .forward import (_enqueue, _native_args, _remember_plan, _repeat_call,
+                      _resolve_native_backend)
 from .validation import RoutedMoEShape, validate_routing
 from .workspace import B300MoEWorkspace
 
@@ -193,6 +194,14 @@ def b300_moe_forward_fp8(
 
     if not isinstance(return_metadata, bool):
         raise TypeError("return_metadata must be a bool")
+    if workspace is not None and not return_metadata and not check_status and \
+            type(workspace) is B300MoEWorkspace and hasattr(weights, "gate_up_q"):
+        # a call that repeats the last fully checked one on this workspace (forward._CallPlan)
+        repeated = _repeat_call(workspace, hidden_states, expert_indices, expert_weights,
+                                weights.gate_up_q, weights.down_q, num_experts, top_k, "fp8",
+                                "fp8", None, use_pdl, weights)
+        if repeated is not None:
+            return repeated
     shape = _validate(hidden_states, expert_indices, expert_weights, weights, num_experts, top_k)
     if workspace is not None and not isinstance(workspace, B300MoEWorkspace):
         raise TypeError("workspace must be a B300MoEWorkspace or None")
@@ -241,6 +250,10 @@ def b300_moe_forward_fp8(
                 "weight_bytes": weights.nbytes,
             }
         active._record_use()
+        if workspace is not None:
+            _remember_plan(active, hidden_states, expert_indices, weights.gate_up_q,
+                           weights.down_q, num_experts, top_k, "fp8", "fp8", None, use_pdl,
+                           shape, flags, weights)
         if check_status:
             active.raise_for_status()
     if return_metadata:

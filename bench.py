@@ -659,6 +659,68 @@ def packed_step_inputs(hidden, ids, weights, device):
     return host_pack, dev_pack, host_views, carve(dev_pack)
 
 
+def run_timeline(args: argparse.Namespace) -> dict[str, object]:
+    """Device timeline of one forward per T from the kernels' own ``%globaltimer`` stamps.
+
+    Every kernel of the library stamps when its first block started and when its last block
+    finished, and the GEMMs when block 0 had its first complete operand stage
+    (``B300MoEWorkspace.timeline()``); values are microseconds after the start of the routing
+    kernel (negative for a kernel that started before it), medians of 11 forwards with L2
+    flushed before each.  ``event_us`` is the CUDA-event time around the same forward.  A
+    diagnosis aid: nothing here enters the benchmark line.
+    """
+
+    from b200moe import (B300MoEWorkspace, StagedLayer, quantize_expert_weights_fp8,
+                         quantize_expert_weights_nvfp4, workloads)
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    sweep = tuple(args.only_tokens) if args.only_tokens else SWEEP
+    gate_up, down = workloads.make_expert_weights(EXPERTS, HIDDEN, INTER, seed=1236, std=0.02,
+                                                  device=device)
+    extra: dict[str, object] = {}
+    if args.weights == "fp8":
+        extra["fp8_weights"] = quantize_expert_weights_fp8(gate_up, down)
+    elif args.weights == "nvfp4":
+        extra["nvfp4_weights"] = quantize_expert_weights_nvfp4(gate_up, down)
+    if extra:
+        gate_up = down = None
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    drain = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=device)
+    rows = {}
+    for T in sweep:
+        dev = (workloads.make_hidden(T, HIDDEN, seed=1234).to(device),
+               workloads.make_routing(T, EXPERTS, TOP_K, ROUTING, 1235).to(device),
+               workloads.make_routing_weights(T, TOP_K, WEIGHT_KIND, 1235).to(device))
+        layer = StagedLayer(*dev, gate_up, down, num_experts=EXPERTS, top_k=TOP_K,
+                            workspace=B300MoEWorkspace(capacity_tokens=max(sweep), device=device),
+                            **extra)
+        for _ in range(3):
+            layer.forward()
+        torch.cuda.synchronize(device)
+        timelines, events = [], []
+        for _ in range(11):
+            flush.fill_(1)
+            drain.sum()
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+            layer.forward()
+            b.record()
+            torch.cuda.synchronize(device)
+            events.append(a.elapsed_time(b) * 1e3)
+            timelines.append(layer.workspace.timeline())
+        median = lambda xs: sorted(xs)[len(xs) // 2]  # noqa: E731
+        rows[str(T)] = {
+            "event_us": round(median(events), 1),
+            **{key: [round(median([t[key][0] for t in timelines]), 1),
+                     round(median([t[key][1] for t in timelines]), 1)]
+               for key in timelines[0]},
+        }
+    return {"timeline_us_after_routing_start": rows, "weights": args.weights,
+            "config": {"workload": WORKLOAD}}
+
+
 def run_ours(args: argparse.Namespace) -> dict[str, object]:
     from b200moe import (B300MoEWorkspace, StagedLayer, b300_moe_forward,
                          b300_moe_forward_pinned, workloads)
@@ -1503,6 +1565,9 @@ def main() -> int:
     parser.add_argument("--parity-only", action="store_true",
                         help="N > 1: run the parity check of every token layout and transport "
                              "against the oracle, print it and exit without timing anything")
+    parser.add_argument("--timeline", action="store_true",
+                        help="N=1: print the device timeline of one forward per T (in-kernel "
+                             "timer stamps) instead of the benchmark line")
     parser.add_argument("--prepare-reference", nargs="?", const="/root/reference", default=None,
                         metavar="CHECKOUT",
                         help="copy the reference's fastpath/ and baseline/ packages from CHECKOUT "
@@ -1516,6 +1581,9 @@ def main() -> int:
         args.no_cpu_baseline = True  # the CPU legs run the reference's BF16 layer
     if args.config in ("wide", "wide_e16", "deepseek", "deepseek_hotspot"):
         args.no_cpu_baseline = True  # ~21 GiB of weights: the CPU port is not timed on these
+    if args.timeline:
+        print(json.dumps(run_timeline(args)), flush=True)
+        return 0
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup

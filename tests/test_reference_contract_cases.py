@@ -1,8 +1,8 @@
 """The reference's own contract tests, run against this library.
 
 ``tests/test_contract.py`` restates the input contract.  This file does not restate
-anything: where a checkout of the reference is available (``B200MOE_REFERENCE_ROOT``,
-default ``/root/reference``) it loads the reference's test module
+anything: where a checkout of the reference is available (the directory named by
+``B200MOE_REFERENCE_ROOT``, else the build container's default) it loads the reference's test module
 ``tests/test_goal_1b_edge_cases.py`` with the name ``fastpath`` bound to this package, and
 runs the reference's assertions on the error table -- the cases that must fail before any
 backend is chosen, so they hold for a library that has no PyTorch execution path:
