@@ -153,7 +153,7 @@ int g_nvfp4_prefetch = 8;   // NVFP4 GEMMs: weight slots requested before the wa
 int g_nvfp4_issuers = 2;    // NVFP4 gate+up: threads issuing MMAs (1 or 2)
 int g_fp8_seg_rows = kSegRowsFp8;  // segment length of the FP8-weight path (16, 32, 48 or 64)
 int g_down_splits = 0;   // forced split-K factor of the down projection (0: chosen on the device)
-int g_small_call_max = kSmallCallMaxAssign;  // most assignments that run in small-call order (0: never)
+int g_small_call_max = -1;  // most assignments that run in small-call order (0: never; -1: default rule)
 
 int down_target(int sm_count) { return g_down_target > 0 ? g_down_target : 2 * sm_count; }
 // what the routing kernel receives: the target, or minus the forced split factor
@@ -571,8 +571,15 @@ int stage_routing(const B200MoeArgs* a, const Ctx& c, bool after_gate_up = false
 
 // Small-call order applies to BF16 weights, device-resident per-step tensors and ids that
 // are in place when the forward is enqueued (not pushed by peers during it).
+// Default rule: T * top_k <= 32 and top_k <= 4.  With top_k = 8 the same number of
+// assignments means four times as many one-row segments, each of whose blocks repeats the
+// routing vote and whose first tile copies a row: measured 0-3 us slower than the five-launch
+// order (H = I = 2880 and H = 7168 / I = 2048 layers, T = 1...4), against 1-4 us faster for
+// top_k = 2.
 bool small_call(const B200MoeArgs* a, int assignments) {
-  int most = g_small_call_max < kSmallCallMaxAssign ? g_small_call_max : kSmallCallMaxAssign;
+  int most = kSmallCallMaxAssign;
+  if (g_small_call_max >= 0) most = g_small_call_max < most ? g_small_call_max : most;
+  else if (a->top_k > 4) return false;
   return assignments <= most && !fp8_weights(a) && !nvfp4_weights(a) &&
          a->ep_wait_flags == nullptr &&
          (a->flags & B200MOE_FLAG_HOST_IO) == 0;
@@ -832,7 +839,7 @@ int b200moe_tune(int knob, int value) {
       g_fp8_seg_rows = value;
       return 0;
     case B200MOE_TUNE_SMALL_CALL_MAX:
-      if (value < 0 || value > kSmallCallMaxAssign) return B200MOE_E_SHAPE;
+      if (value < -1 || value > kSmallCallMaxAssign) return B200MOE_E_SHAPE;
       g_small_call_max = value;
       return 0;
     case B200MOE_TUNE_NVFP4_PREFETCH:

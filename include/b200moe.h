@@ -494,7 +494,8 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *   B200MOE_TUNE_EVICT_FIRST   1: weight tiles are loaded with an L2
  *                              evict-first hint (default 0)
  *   B200MOE_TUNE_SMALL_CALL_MAX  most assignments (T * top_k) for which b200moe_forward
- *                              uses small-call order (0..32, default 32; 0 = never)
+ *                              uses small-call order, for every top_k (0..32; 0 = never);
+ *                              -1 = the default rule: T * top_k <= 32 and top_k <= 4
  *   B200MOE_TUNE_DOWN_SPLITS   force the split-K factor of the down projection (1..8;
  *                              0 = chosen on the device from the routing result)
  *   B200MOE_TUNE_FP8_SEG_ROWS  longest segment of the FP8-weight path: 16, 32, 48 or 64 rows

@@ -638,7 +638,7 @@ def test_small_call_order_equals_regular_order_bitwise(spec, use_pdl, cuda_devic
             results[most] = _forward_with_buffers(tensors, E, K, cuda_device, use_pdl=use_pdl,
                                                   check_status=True)
     finally:
-        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, 32)
+        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, -1)   # back to the default rule
     (out0, meta0, buf0, valid0, _), (out1, meta1, buf1, valid1, ws1) = results[0], results[32]
     assert torch.equal(out0, out1)
     for key in ("expert_counts", "expert_offsets", "permutation", "reverse_mapping"):
@@ -695,7 +695,7 @@ def test_small_call_order_with_dropped_ids_and_local_experts(cuda_device) -> Non
             assert ws2.status() == 0
             outs[most] += (part.clone(),)
     finally:
-        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, 32)
+        lib.b200moe_tune(_lib.TUNE_SMALL_CALL_MAX, -1)   # back to the default rule
     for a, b in zip(outs[0], outs[32]):
         assert torch.equal(a, b)
 
