@@ -42,6 +42,7 @@ TUNE_DOWN_SPLITS = 6
 TUNE_FP8_SEG_ROWS = 7
 TUNE_NVFP4_PREFETCH = 8
 TUNE_NVFP4_ISSUERS = 9
+TUNE_GEMM_OVERLAP = 10
 
 EXPORTS = (
     "b200moe_abi_version",

@@ -45,12 +45,12 @@ cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const CUtensorMap* map_hidden, const int32_t* sched, int sched_cap,
                            uint32_t* status, void* act_hi, void* act_lo, int inter, int hidden,
-                           int rows_cap, int grid, const SmallCall* small, int sm_count,
-                           bool pdl, cudaStream_t stream);
+                           int rows_cap, int grid, const SmallCall* small, int overlap,
+                           int sm_count, bool pdl, cudaStream_t stream);
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, int sched_cap,
                         uint32_t* status, float* partials, int hidden, int inter, int rows_cap,
-                        int grid, const SmallCall* small, int sm_count, bool pdl,
+                        int grid, const SmallCall* small, int overlap, int sm_count, bool pdl,
                         cudaStream_t stream);
 
 cudaError_t launch_gate_up_fp8(const CUtensorMap& map_w, const CUtensorMap& map_x,
@@ -149,6 +149,7 @@ namespace {
 int g_l2_promotion = 2;  // 0 none, 1 128 B, 2 256 B
 int g_down_target = 0;   // blocks the down projection's split-K aims at (0: 2 per SM)
 
+int g_gemm_overlap = -1;    // BF16 forward: down takes over from gate+up segment by segment (-1: rule)
 int g_nvfp4_prefetch = 8;   // NVFP4 GEMMs: weight slots requested before the wait for the previous kernel
 int g_nvfp4_issuers = 2;    // NVFP4 gate+up: threads issuing MMAs (1 or 2)
 int g_fp8_seg_rows = kSegRowsFp8;  // segment length of the FP8-weight path (16, 32, 48 or 64)
@@ -367,7 +368,7 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
 
 int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int experts,
                int hidden, int inter, void* act_hi, const Scratch& s, const SmallCall* small,
-               const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
+               bool overlap, const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
   CUtensorMap map_w, map_x, map_hidden;
   {
     const uint64_t dims[4] = {(uint64_t)hidden, (uint64_t)inter, 2, (uint64_t)experts};
@@ -391,11 +392,12 @@ int do_gate_up(const void* x, const void* w, int rows_cap, int assignments, int 
   }
   return (int)launch_gate_up(map_w, map_x, small ? &map_hidden : nullptr, s.sched,
                              max_segments(rows_cap, experts), s.status, act_hi, s.act_lo, inter,
-                             hidden, rows_cap, grid, small, dev.sm_count, pdl, stream);
+                             hidden, rows_cap, grid, small, overlap ? 1 : 0, dev.sm_count, pdl,
+                             stream);
 }
 
 int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, int experts,
-            int hidden, int inter, const Scratch& s, const SmallCall* small,
+            int hidden, int inter, const Scratch& s, const SmallCall* small, bool overlap,
             const DeviceInfo& dev, bool pdl, cudaStream_t stream) {
   CUtensorMap map_w, map_hi, map_lo;
   {
@@ -414,7 +416,7 @@ int do_down(const void* act_hi, const void* w, int rows_cap, int assignments, in
                              (inter + 63) / 64, dev.sm_count);
   return (int)launch_down(map_w, map_hi, map_lo, s.sched, max_segments(rows_cap, experts),
                           s.status, s.partials, hidden, inter, rows_cap, grid, small,
-                          dev.sm_count, pdl, stream);
+                          overlap ? 1 : 0, dev.sm_count, pdl, stream);
 }
 
 // FP8 weights: one-byte tensor maps of the weights and of the token planes.
@@ -617,7 +619,8 @@ int stage_gather(const B200MoeArgs* a, const Ctx& c, bool pdl) {
                             a->num_tokens, a->top_k, a->hidden_size, trace_of(c.s), pdl, c.stream);
 }
 
-int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr) {
+int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr,
+                  bool overlap = false) {
   if (!a->permuted_hidden || !a->gate_up_weight || !a->swiglu_output) return B200MOE_E_NULL;
   if (!aligned16(a->permuted_hidden) || !aligned16(a->gate_up_weight) ||
       !aligned16(a->swiglu_output))
@@ -635,10 +638,11 @@ int stage_gate_up(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall*
   }
   return do_gate_up(a->permuted_hidden, a->gate_up_weight, a->rows_cap, c.assignments,
                     a->num_experts, a->hidden_size, a->intermediate_size, a->swiglu_output, c.s,
-                    small, c.dev, pdl, c.stream);
+                    small, overlap, c.dev, pdl, c.stream);
 }
 
-int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr) {
+int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* small = nullptr,
+               bool overlap = false) {
   if (!a->swiglu_output || !a->down_weight) return B200MOE_E_NULL;
   if (!aligned16(a->swiglu_output) || !aligned16(a->down_weight)) return B200MOE_E_ALIGN;
   if (nvfp4_weights(a)) {
@@ -653,7 +657,7 @@ int stage_down(const B200MoeArgs* a, const Ctx& c, bool pdl, const SmallCall* sm
                        c.dev, pdl, c.stream);
   }
   return do_down(a->swiglu_output, a->down_weight, a->rows_cap, c.assignments, a->num_experts,
-                 a->hidden_size, a->intermediate_size, c.s, small, c.dev, pdl, c.stream);
+                 a->hidden_size, a->intermediate_size, c.s, small, overlap, c.dev, pdl, c.stream);
 }
 
 int stage_combine(const B200MoeArgs* a, const Ctx& c, bool pdl) {
@@ -841,6 +845,10 @@ int b200moe_tune(int knob, int value) {
     case B200MOE_TUNE_SMALL_CALL_MAX:
       if (value < -1 || value > kSmallCallMaxAssign) return B200MOE_E_SHAPE;
       g_small_call_max = value;
+      return 0;
+    case B200MOE_TUNE_GEMM_OVERLAP:
+      if (value < -1 || value > 1) return B200MOE_E_SHAPE;
+      g_gemm_overlap = value;
       return 0;
     case B200MOE_TUNE_NVFP4_PREFETCH:
       if (value < 0 || value > 8) return B200MOE_E_SHAPE;
@@ -1114,10 +1122,20 @@ int b200moe_forward(const B200MoeArgs* a, void* stream) {
     if ((rc = stage_down(a, c, c.pdl, &sc))) return rc;
     return skip_combine ? 0 : stage_combine(a, c, c.pdl);
   }
+  // Inside one forward with dependent launches the down projection can take over segment by
+  // segment from gate+up (BF16 weights; the quantised paths have a plane pass in between).
+  // After such a hand-over the down blocks of the LAST segment run alone, each at what one
+  // block can pull from HBM, so it pays only where those blocks are short: I <= H (a down
+  // block then streams at most a quarter of a gate+up block's bytes).  Measured: H = 7168,
+  // I = 2048, 64 experts: 580 -> 557, 838 -> 817, 844 -> 825 us at T = 8 / 32 / 64;
+  // H = I = 2880: 1-2 us of 90-95; Mixtral shape (I = 3.5 H): 0 to +8 us, hence the rule.
+  const bool overlap_wanted = g_gemm_overlap < 0 ? a->intermediate_size <= a->hidden_size
+                                                 : g_gemm_overlap != 0;
+  const bool overlap = c.pdl && overlap_wanted && !fp8_weights(a) && !nvfp4_weights(a);
   if ((rc = stage_routing(a, c))) return rc;
   if ((rc = stage_gather(a, c, c.pdl))) return rc;
-  if ((rc = stage_gate_up(a, c, c.pdl))) return rc;
-  if ((rc = stage_down(a, c, c.pdl))) return rc;
+  if ((rc = stage_gate_up(a, c, c.pdl, nullptr, overlap))) return rc;
+  if ((rc = stage_down(a, c, c.pdl, nullptr, overlap))) return rc;
   return skip_combine ? 0 : stage_combine(a, c, c.pdl);
 }
 

@@ -46,6 +46,18 @@ constexpr uint32_t kMaxStageBudget = 220u * 1024u;        // one block per SM
 constexpr int kTileM = 128;   // weight rows per unit
 constexpr int kTileK = 64;    // elements per pipeline stage along K (128 bytes)
 constexpr uint64_t kAbortDrainNs = 1000000ull;
+constexpr uint64_t kHandoverWaitNs = 200000000ull;   // a down block's wait for its segment's rows
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// orders earlier generic-proxy accesses (here: other blocks' stores, acquired through a
+// flag) before this thread's later async-proxy accesses (TMA loads from global memory)
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 
 struct GemmParams {
   const int32_t* sched;
@@ -58,6 +70,10 @@ struct GemmParams {
   int m_tiles;             // ceil(m_total / 128)
   int rows_cap;
   int sched_cap;           // segment entries the schedule array holds
+  // Regular order inside one forward: gate+up blocks count their finished tiles per segment
+  // in the schedule entry's fourth word, and a down block waits for its own segment's count
+  // instead of the whole gate+up grid (see "segment hand-over" below).
+  int overlap;
   // small calls (<= kSmallCallMaxAssign assignments): every block derives its unit from
   // the call's expert ids and does not read the schedule before its dependency wait
   int small;
@@ -230,7 +246,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   // ---- the dependency wait ------------------------------------------------------
-  if (!(kGateUp && p.small)) {
+  // Segment hand-over (regular order, p.overlap): a down block does not wait for the whole
+  // gate+up grid.  This grid is launched once every gate+up block has started (each
+  // executes launch_dependents right after its own wait), i.e. into the slots that free up
+  // during gate+up's last, partial wave; the blocks of early segments, whose activations are
+  // complete by then, stream their weights under that tail instead of idling until the
+  // last gate+up block has finished.  Only the thread that loads activations waits, on its
+  // segment's tile count (bounded).  No deadlock is possible even without the bound: every
+  // gate+up block is resident or finished before the first down block exists.
+  const bool handover = !kGateUp && p.overlap != 0 && p.small == 0;
+  if (handover) {
+    pdl_launch_dependents();
+  } else if (!(kGateUp && p.small)) {
     pdl_wait();
     pdl_launch_dependents();
   }
@@ -261,7 +288,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   if (warp == 0) {
     // ===== TMA producer =====
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
+      bool rows_ready = true;
+      if (handover) {
+        // all gate+up tiles of this segment have stored their activations: acquire the
+        // count, then order those generic-proxy writes before this thread's TMA reads
+        const int* done = p.sched + kSchedHeaderWords + kSchedSegWords * (unit / tiles) + 3;
+        const int need = (p.k_total + kTileM - 1) / kTileM;   // gate+up tiles = ceil(I / 128)
+        const uint64_t t0 = global_timer_ns();
+        while (ld_acquire_gpu(done) < need) {
+          if (*abort_flag || global_timer_ns() - t0 > kHandoverWaitNs) {
+            rows_ready = false;
+            *abort_flag = 1;
+            break;
+          }
+        }
+        fence_proxy_async_global();
+      }
+      for (int i = 0; rows_ready && i < num_kb; ++i) {
         const int s = i % num_stages;
         const uint32_t round = (uint32_t)(i / num_stages);
         if (i >= num_stages &&
@@ -390,8 +433,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     while (global_timer_ns() - t0 < kAbortDrainNs) {
     }
   }
+  // segment hand-over: every thread's activation stores are ordered before the count
+  if (kGateUp && p.overlap != 0 && p.small == 0 && warp >= 2) __threadfence();
   tc_fence_before_sync();
   __syncthreads();
+  if (kGateUp && p.overlap != 0 && p.small == 0 && threadIdx.x == 0 && !*abort_flag)
+    atomicAdd(const_cast<int*>(p.sched) + kSchedHeaderWords + kSchedSegWords * (unit / tiles) + 3, 1);
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
   trace_end(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
   if (warp == 1) {
@@ -447,9 +494,10 @@ static cudaError_t launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_
 cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
                            const CUtensorMap* map_hidden, const int32_t* sched, int sched_cap,
                            uint32_t* status, void* act_hi, void* act_lo, int inter, int hidden,
-                           int rows_cap, int grid, const SmallCall* small, int sm_count,
-                           bool pdl, cudaStream_t stream) {
+                           int rows_cap, int grid, const SmallCall* small, int overlap,
+                           int sm_count, bool pdl, cudaStream_t stream) {
   GemmParams p = {};
+  p.overlap = overlap;
   if (small != nullptr && map_hidden != nullptr) {
     p.small = 1;
     p.ids = small->ids;
@@ -481,9 +529,10 @@ cudaError_t launch_gate_up(const CUtensorMap& map_w, const CUtensorMap& map_x,
 cudaError_t launch_down(const CUtensorMap& map_w, const CUtensorMap& map_hi,
                         const CUtensorMap& map_lo, const int32_t* sched, int sched_cap,
                         uint32_t* status, float* partials, int hidden, int inter, int rows_cap,
-                        int grid, const SmallCall* small, int sm_count, bool pdl,
+                        int grid, const SmallCall* small, int overlap, int sm_count, bool pdl,
                         cudaStream_t stream) {
   GemmParams p = {};
+  p.overlap = overlap;
   if (small != nullptr) {
     p.small = 1;
     p.ids = small->ids;

@@ -503,6 +503,10 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              the weight stream and re-read weights of longer experts)
  *   B200MOE_TUNE_DOWN_TARGET   number of blocks the split-K of the down projection aims
  *                              at when few (segment, tile) units exist (0 = default)
+ *   B200MOE_TUNE_GEMM_OVERLAP  1: inside b200moe_forward (regular order, BF16, dependent
+ *                              launches) a down block waits for the gate+up tiles of its own
+ *                              segment only; 0: for the whole gate+up grid; -1 (default):
+ *                              1 where intermediate_size <= hidden_size, else 0
  *   B200MOE_TUNE_NVFP4_PREFETCH  NVFP4 GEMMs: weight slots a block requests before it waits
  *                              for the previous kernel (0..8, default 8 = the whole ring)
  *   B200MOE_TUNE_NVFP4_ISSUERS  NVFP4 gate+up: 1 = one thread issues the MMAs of the gate and
@@ -517,6 +521,7 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
 #define B200MOE_TUNE_FP8_SEG_ROWS 7
 #define B200MOE_TUNE_NVFP4_PREFETCH 8
 #define B200MOE_TUNE_NVFP4_ISSUERS 9
+#define B200MOE_TUNE_GEMM_OVERLAP 10
 int b200moe_tune(int knob, int value);
 
 #ifdef __cplusplus
