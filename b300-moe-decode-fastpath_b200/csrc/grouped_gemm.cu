@@ -437,8 +437,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
   if (kGateUp && p.overlap != 0 && p.small == 0 && warp >= 2) __threadfence();
   tc_fence_before_sync();
   __syncthreads();
-  if (kGateUp && p.overlap != 0 && p.small == 0 && threadIdx.x == 0 && !*abort_flag)
+  if (kGateUp && p.overlap != 0 && p.small == 0 && threadIdx.x == 0 && !*abort_flag) {
+    // release: the other threads' stores happen before this fence through the barrier
+    __threadfence();
     atomicAdd(const_cast<int*>(p.sched) + kSchedHeaderWords + kSchedSegWords * (unit / tiles) + 3, 1);
+  }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, B200MOE_STATUS_PIPE_TIMEOUT);
   trace_end(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
   if (warp == 1) {

@@ -67,6 +67,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   __shared__ __align__(8) uint64_t s_acc;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_token_scale[kSegRowsFp8];
+  __shared__ float s_row_max[4][kSegRowsFp8];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -224,6 +226,25 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
     const int trow = quarter * 32 + lane;  // accumulator lane = weight row of the tile
     const int m = tile * kQTileM + trow;
     const bool m_ok = m < p.m_total;
+    // Everything the epilogue needs from global memory is fetched now, under the main loop:
+    // a load issued after the accumulators are complete would queue behind the weight
+    // prefetch of the next kernel's blocks, which become resident at about that time.
+    const int et = (int)threadIdx.x - 64;   // 0..127
+    float scale0 = 0.0f, scale1 = 0.0f;     // gate and up row scales, or the down row scale
+    if (m_ok) {
+      if (kGateUp) {
+        scale0 = p.row_scale[(size_t)expert * 2 * p.m_total + m];
+        scale1 = p.row_scale[(size_t)expert * 2 * p.m_total + p.m_total + m];
+      } else {
+        scale0 = p.row_scale[(size_t)expert * p.m_total + m];
+      }
+    }
+    if (et < kSegRowsFp8) {
+      s_token_scale[et] = et < n_rows ? p.token_scale[row_start + et] : 0.0f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) s_row_max[q][et] = 0.0f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
     bool have_acc = true;
     if (num_kb > 0) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
     have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld needs the whole warp
@@ -244,8 +265,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
           for (int j = 0; j < 16; ++j) {
             float v = __uint_as_float(a[0][j]) + __uint_as_float(a[1][j]) * 0.0625f;
             if (kPlanes > 2) v += __uint_as_float(a[kPlanes - 1][j]) * 0.00390625f;
-            const float ts = (c0 + j < n_rows) ? p.token_scale[row_start + c0 + j] : 0.0f;
-            out[j] = v * ts;
+            out[j] = v * s_token_scale[c0 + j];
           }
         } else {
 #pragma unroll
@@ -253,11 +273,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
         }
       };
       if (kGateUp) {
-        float gate_scale = 0.0f, up_scale = 0.0f;
-        if (m_ok) {
-          gate_scale = p.row_scale[(size_t)expert * 2 * p.m_total + m];
-          up_scale = p.row_scale[(size_t)expert * 2 * p.m_total + p.m_total + m];
-        }
+        const float gate_scale = scale0, up_scale = scale1;
         float g[16], u[16];
         for (int c0 = 0; c0 < n_mma; c0 += 16) {
           load_columns(0, c0, g);
@@ -279,12 +295,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
             }
             // non-negative floats order like their bit patterns
             const uint32_t warp_max = __reduce_max_sync(0xffffffffu, __float_as_uint(mag));
-            if (lane == 0 && c0 + j < n_rows && warp_max != 0u)
-              atomicMax(p.act_amax + row_start + c0 + j, warp_max);
+            if (lane == 0) s_row_max[quarter][c0 + j] = __uint_as_float(warp_max);
           }
         }
       } else {
-        const float scale = m_ok ? p.row_scale[(size_t)expert * p.m_total + m] : 0.0f;
+        const float scale = scale0;
         float* dst = p.partials + (size_t)split * p.rows_cap * p.m_total;
         float v[16];
         for (int c0 = 0; c0 < n_mma; c0 += 16) {
@@ -295,6 +310,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
               dst[(size_t)(row_start + c0 + j) * p.m_total + m] = v[j] * scale;
           }
         }
+      }
+    }
+    if (kGateUp) {
+      // one atomic per block and row (one per warp made 448 same-address atomics per row
+      // at T = 1, all at the end of the launch)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (have_acc && et < n_rows) {
+        const float mx = fmaxf(fmaxf(s_row_max[0][et], s_row_max[1][et]),
+                               fmaxf(s_row_max[2][et], s_row_max[3][et]));
+        if (mx > 0.0f) atomicMax(p.act_amax + row_start + et, __float_as_uint(mx));
       }
     }
   }
@@ -316,7 +341,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 }
 
-constexpr uint32_t kQStageBudget = 111u * 1024u;  // 16 rows: three 36 KB (gate+up) or five 22 KB (down) stages; two blocks per SM
+constexpr uint32_t kQStageBudget = 110u * 1024u;  // 16 rows: three 36 KB (gate+up) or five 22 KB (down) stages; with 1.4 KB of static shared memory two blocks fit an SM
 // a grid of at most one block per SM gets the whole SM's shared memory per block (deeper
 // ring: more bytes in flight when few blocks stream)
 constexpr uint32_t kQLoneBlockStageBudget = 216u * 1024u;
