@@ -245,6 +245,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     }
   }
 
+  // ---- tensor memory (allocated before the dependency wait: one step less between the
+  // wait's return and the first token load) ----------------------------------------
+  const uint32_t cols_needed = (uint32_t)n_mma * 2u;  // gate and up, or high and low halves
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < cols_needed) tmem_cols <<= 1;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+
   // ---- the dependency wait ------------------------------------------------------
   // Segment hand-over (regular order, p.overlap): a down block does not wait for the whole
   // gate+up grid.  This grid is launched once every gate+up block has started (each
@@ -271,14 +281,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
       s_abort = 1;
   }
 
-  // ---- tensor memory ------------------------------------------------------------
-  const uint32_t cols_needed = (uint32_t)n_mma * 2u;  // gate and up, or high and low halves
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < cols_needed) tmem_cols <<= 1;
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
-    tmem_relinquish();
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();

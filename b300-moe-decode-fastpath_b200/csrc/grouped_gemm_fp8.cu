@@ -151,10 +151,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
       load_weights(smem_base + (uint32_t)i * stage_bytes, bar, (kb0 + i) * kQStageK);
     }
   }
-  pdl_wait();
-  pdl_launch_dependents();
-
-  // ---- tensor memory: one accumulator of n_mma columns per plane (gate and up: each) -------
+  // ---- tensor memory: one accumulator of n_mma columns per plane (gate and up: each);
+  // allocated before the dependency wait ------------------------------------------------
   constexpr int kAccSets = kGateUp ? 2 : 1;
   uint32_t tmem_cols = 32;
   while (tmem_cols < (uint32_t)(kAccSets * kPlanes * n_mma)) tmem_cols <<= 1;
@@ -162,6 +160,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w,
     tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
     tmem_relinquish();
   }
+  pdl_wait();
+  pdl_launch_dependents();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();

@@ -251,14 +251,18 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
   pdl_wait();
   pdl_launch_dependents();
   if (threadIdx.x == 0) STAGE_STAMP(7, 1);
-  if (warp >= 2 && warp < 6) {
-    const int r = (int)threadIdx.x - 64;
-    if (r < kSegRowsNvfp4) s_token_scale[r] = r < n_rows ? p.token_scale[row_start + r] : 0.0f;
-    fence_proxy_async_smem();   // the tensor-memory copy reads the tiles through the async proxy
-  }
+  // the tensor-memory copy reads the token-scale tiles through the async proxy
+  if (warp >= 2 && warp < 6) fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if (warp >= 2 && warp < 6) {
+    // the rows' scales (written by the previous kernel) are only needed by the epilogue: they
+    // are fetched here, under the main loop, and not in front of the barrier above, which
+    // would keep the producer from requesting the token planes for the length of this load
+    const int r = (int)threadIdx.x - 64;
+    if (r < kSegRowsNvfp4) s_token_scale[r] = r < n_rows ? p.token_scale[row_start + r] : 0.0f;
+  }
   const uint32_t tmem = s_tmem_base;
   const uint32_t tmem_sfa = tmem + acc_cols;
   const uint32_t tmem_sfb = tmem_sfa + kSfaCols;
@@ -357,6 +361,7 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
     const int et = (int)threadIdx.x - 64;
     const int m = tile * kFTileM + quarter * 32 + lane;   // weight row of this thread
     const bool m_ok = m < p.m_total;
+    epilogue_warps_sync();   // s_token_scale is complete
     bool have_acc = true;
     if (num_kb > 0) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
     have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld needs the whole warp
