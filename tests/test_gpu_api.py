@@ -657,6 +657,53 @@ def test_small_call_order_equals_regular_order_bitwise(spec, use_pdl, cuda_devic
         assert moe_oracle.relative_max_error(out1.float().cpu(), ref) <= 2e-2
 
 
+HANDOVER_CASES = [
+    # T, H, I, E, K, routing  (I <= H is where the host applies the hand-over by default)
+    (40, 512, 256, 8, 2, "uniform"),
+    (150, 512, 384, 4, 2, "uniform"),        # experts longer than one 128-row segment
+    (64, 1024, 512, 64, 8, "zipf"),          # many small segments, empty experts
+    (33, 2880, 2880, 32, 8, "concentrated"),  # ragged tiles
+    (17, 256, 384, 8, 2, "uniform"),         # I > H: only reached through the knob
+]
+
+
+@pytest.mark.parametrize("spec", HANDOVER_CASES, ids=lambda s: "T{}_H{}_I{}_E{}_K{}_{}".format(*s))
+def test_segment_handover_equals_the_grid_wait_bitwise(spec, cuda_device) -> None:
+    """With the hand-over a down block waits for the gate+up tiles of its own segment (a
+    counter in the schedule entry) instead of the whole gate+up grid.  A scheduling choice
+    only: outputs and public buffers are bit-identical with it forced on and off, over
+    repeated calls on one workspace, and the output meets the oracle bar."""
+
+    from b200moe import B300MoEWorkspace, _lib, b300_moe_forward, workloads
+    from oracle import moe_oracle
+
+    T, H, I, E, K, routing = spec
+    tensors = workloads.make_case(T, H, I, E, K, routing=routing, std=0.02 if H >= 2048 else None,
+                                  device=cuda_device, seed=91 + T)
+    lib = _lib.load()
+    results = {}
+    try:
+        for mode in (0, 1):
+            assert lib.b200moe_tune(_lib.TUNE_GEMM_OVERLAP, mode) == 0
+            results[mode] = _forward_with_buffers(tensors, E, K, cuda_device, check_status=True)
+        # many calls in a row: the counters are zeroed by every forward's routing kernel
+        assert lib.b200moe_tune(_lib.TUNE_GEMM_OVERLAP, 1) == 0
+        ws = B300MoEWorkspace(device=cuda_device)
+        for _ in range(50):
+            again = b300_moe_forward(*tensors, num_experts=E, top_k=K, workspace=ws)
+        torch.cuda.synchronize(cuda_device)
+        assert ws.status() == 0
+    finally:
+        lib.b200moe_tune(_lib.TUNE_GEMM_OVERLAP, -1)   # back to the default rule
+    (out0, meta0, buf0, valid0, _), (out1, meta1, buf1, valid1, ws1) = results[0], results[1]
+    assert torch.equal(out0, out1) and torch.equal(out1, again)
+    for name in buf0:
+        assert torch.equal(buf0[name], buf1[name]), name
+    cpu = [t.float().cpu() if t.is_floating_point() else t.cpu() for t in tensors]
+    ref, _ = moe_oracle.routed_moe(*cpu, num_experts=E, top_k=K)
+    assert moe_oracle.relative_max_error(out1.float().cpu(), ref) <= 2e-2
+
+
 def test_small_call_order_with_dropped_ids_and_local_experts(cuda_device) -> None:
     """Small-call order under the two conditions that change which rows exist: an id outside
     [0, E) (row dropped, status bit, zero-filled gather row) and an expert-parallel rank's
