@@ -75,11 +75,16 @@ class ExpertParallelMoE:
         use_pdl: bool = True,
         transport: str = "nccl",
         fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
+        nvfp4_scales: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
         wait_limit_us: int = 0,
         combine: str = "auto",
     ) -> None:
         """``fp8_scales = (gate_up_scale [E_local, 2I], down_scale [E_local, H])`` marks the two
         weight tensors as E4M3 codes (uint8) of the FP8-weight path (``b200moe.fp8``).
+        ``nvfp4_scales = (gate_up_scale [E_local], down_scale [E_local], gate_up_block_scale,
+        down_block_scale)`` marks them as packed E2M1 (uint8 ``[E_local, 2I, H/2]`` and
+        ``[E_local, H, I/2]``) of the NVFP4 path (``b200moe.nvfp4``: the fields of an
+        ``Nvfp4ExpertWeights`` quantised from this rank's experts).
         ``wait_limit_us`` bounds every device-side wait for a peer (0: one second).
         ``combine`` (``transport="p2p"`` only) selects how rows cross the ranks: ``"push"``
         stores flagged rows into the receivers' inboxes (lowest latency; needs
@@ -90,7 +95,10 @@ class ExpertParallelMoE:
 
         self.wait_limit_us = int(wait_limit_us)
 
+        if fp8_scales is not None and nvfp4_scales is not None:
+            raise ValueError("give fp8_scales or nvfp4_scales, not both")
         self.fp8_scales = fp8_scales
+        self.nvfp4_scales = nvfp4_scales
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -104,7 +112,8 @@ class ExpertParallelMoE:
             )
         self.gate_up = gate_up_local
         self.down = down_local
-        self.hidden_size = gate_up_local.shape[2]
+        # packed E2M1 holds two elements of H per byte
+        self.hidden_size = gate_up_local.shape[2] * (2 if nvfp4_scales is not None else 1)
         self.use_pdl = use_pdl
         self._local_forward = local_forward or self._native_local_forward
         self._native = local_forward is None
@@ -313,7 +322,7 @@ class ExpertParallelMoE:
             hidden, ids, weights, self.gate_up, self.down, top_k=self.top_k,
             expert_id_base=self.base, num_experts_global=self.num_experts,
             workspace=self.workspace, use_pdl=self.use_pdl, ep_wait=ep_wait,
-            fp8_scales=self.fp8_scales, skip_combine=p2p,
+            fp8_scales=self.fp8_scales, nvfp4_scales=self.nvfp4_scales, skip_combine=p2p,
             ep_wait_limit_us=self.wait_limit_us,
         )
         self._last_call = call
@@ -337,12 +346,13 @@ class ExpertParallelMoE:
             raise RuntimeError("expert-parallel native compute requires compute capability (10, 0)")
         if ids.dtype != torch.int64:
             raise TypeError("expert_indices must have dtype torch.int64")
-        weight_dtype = torch.uint8 if self.fp8_scales is not None else torch.bfloat16
+        quantised = self.fp8_scales is not None or self.nvfp4_scales is not None
+        weight_dtype = torch.uint8 if quantised else torch.bfloat16
         for t, want in ((hidden, torch.bfloat16), (weights, torch.bfloat16),
                         (self.gate_up, weight_dtype), (self.down, weight_dtype)):
             if t.dtype != want:
                 raise TypeError("native expert-parallel compute requires bfloat16 inputs and "
-                                "bfloat16 (or, with fp8_scales, uint8 E4M3) weights")
+                                "bfloat16 (or, with fp8_scales / nvfp4_scales, uint8) weights")
         if self.fp8_scales is not None:
             gs, ds = self.fp8_scales
             inter_ = self.gate_up.shape[1] // 2
@@ -360,8 +370,19 @@ class ExpertParallelMoE:
         inter = self.gate_up.shape[1] // 2
         if self.hidden_size % 8 or inter % 8:
             raise ValueError("hidden_size and intermediate_size must be divisible by 8")
-        if tuple(self.down.shape) != (self.local_experts, self.hidden_size, inter):
-            raise ValueError("down_weight must have shape [E_local, H, I]")
+        packed = 2 if self.nvfp4_scales is not None else 1
+        if tuple(self.down.shape) != (self.local_experts, self.hidden_size, inter // packed):
+            raise ValueError("down_weight must have shape [E_local, H, I] ([E_local, H, I/2] "
+                             "bytes for NVFP4)")
+        if self.nvfp4_scales is not None:
+            gs, ds, gb, db = self.nvfp4_scales
+            if tuple(gs.shape) != (self.local_experts,) or tuple(ds.shape) != (self.local_experts,) \
+                    or gs.dtype != torch.float32 or ds.dtype != torch.float32 \
+                    or gb.dtype != torch.uint8 or db.dtype != torch.uint8:
+                raise ValueError("nvfp4_scales must be (float32 [E_local], float32 [E_local], "
+                                 "uint8 block scales, uint8 block scales)")
+            if self.hidden_size % 64 or inter % 64:
+                raise ValueError("the NVFP4 path requires H and I divisible by 64")
         _lib.load()
 
     # ------------------------------------------------------------------ forward
@@ -474,6 +495,7 @@ def local_partial_forward(
     fp8_scales: tuple[torch.Tensor, torch.Tensor] | None = None,
     skip_combine: bool = False,
     ep_wait_limit_us: int = 0,
+    nvfp4_scales: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -512,11 +534,18 @@ def local_partial_forward(
             flags |= _lib.FLAG_PDL
         if fp8_scales is not None:
             flags |= _lib.FLAG_FP8_WEIGHTS
+        if nvfp4_scales is not None:
+            flags |= _lib.FLAG_NVFP4_WEIGHTS
         args = _native_args(hidden, ids, weights, gate_up_local, down_local, shape, workspace,
                             partial, flags, expert_id_base=expert_id_base)
         if fp8_scales is not None:
             args.gate_up_scale = fp8_scales[0].data_ptr()
             args.down_scale = fp8_scales[1].data_ptr()
+        if nvfp4_scales is not None:
+            args.gate_up_scale = nvfp4_scales[0].data_ptr()
+            args.down_scale = nvfp4_scales[1].data_ptr()
+            args.gate_up_block_scale = nvfp4_scales[2].data_ptr()
+            args.down_block_scale = nvfp4_scales[3].data_ptr()
         if ep_wait is not None:
             # (device address of this rank's dispatch flags, world size, epoch): the routing
             # kernel waits for every rank's pushed shard before it reads ids or rows

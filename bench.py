@@ -1113,6 +1113,10 @@ def run_ours_expert_parallel(args, rank: int, world: int, local: int, dist):
     gate_up, down = workloads.make_expert_weights(count, HIDDEN, INTER, seed=1236 + rank,
                                                   std=0.02, device=device)
     fp8_scales = None
+    if args.weights == "nvfp4":
+        # ExpertParallelMoE takes NVFP4 weights (nvfp4_scales=...; tests/test_gpu_nvfp4.py), but
+        # this benchmark's N-GPU parity step has no NVFP4 leg: refuse rather than time BF16
+        raise SystemExit("bench.py --gpus N > 1 supports --weights bf16 and fp8 only")
     if args.weights == "fp8":
         # each rank quantises its own experts once, outside every timed region
         from b200moe import quantize_expert_weights_fp8

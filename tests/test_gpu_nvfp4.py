@@ -204,3 +204,36 @@ def test_mixtral_shaped_decode_step_with_nvfp4_weights(cuda_device) -> None:
     print(f"nvfp4 mixtral-shaped T=8: err/rms={err:.5f} floor={moe_oracle.bf16_floor(ref):.5f} "
           f"weight bytes {fw.nbytes / 1e6:.1f} MB")
     assert err <= TOLERANCE
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_shares_with_nvfp4_weights(world, cuda_device) -> None:
+    """Each rank's share of an expert-parallel forward with NVFP4 weights, run one after
+    another on one GPU: the FP32 partial outputs add up to the NVFP4 layer."""
+
+    from b200moe import B300MoEWorkspace, quantize_expert_weights_nvfp4
+    from b200moe.expert_parallel import expert_range, local_partial_forward
+
+    T, H, I, E, K = 16, 256, 384, 8, 2
+    hidden, ids, weights, gate_up, down = _case(cuda_device, T, H, I, E, K, routing="zipf", seed=7)
+    fw = quantize_expert_weights_nvfp4(gate_up, down)
+    total = torch.zeros(T, H, dtype=torch.float32, device=cuda_device)
+    for rank in range(world):
+        base, count = expert_range(rank, world, E)
+        ws = B300MoEWorkspace(device=cuda_device)
+        own = slice(base, base + count)
+        partial, _ = local_partial_forward(
+            hidden, ids, weights, fw.gate_up_q[own].contiguous(), fw.down_q[own].contiguous(),
+            top_k=K, expert_id_base=base, num_experts_global=E, workspace=ws,
+            nvfp4_scales=(fw.gate_up_scale[own].contiguous(), fw.down_scale[own].contiguous(),
+                          fw.gate_up_block_scale[own].contiguous(),
+                          fw.down_block_scale[own].contiguous()))
+        torch.cuda.synchronize(cuda_device)
+        assert ws.status() == 0
+        total += partial
+    gu_deq, dn_deq = _dequantised(fw)
+    ref, _ = moe_oracle.routed_moe(hidden.cpu(), ids.cpu(), weights.cpu(), gu_deq, dn_deq,
+                                   num_experts=E, top_k=K)
+    err = moe_oracle.relative_max_error(total.cpu(), ref)
+    print(f"nvfp4 expert-parallel shares, world {world}: err/rms={err:.5f}")
+    assert err <= TOLERANCE
