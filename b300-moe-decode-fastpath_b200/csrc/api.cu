@@ -104,7 +104,7 @@ cudaError_t launch_down_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_a
                               const int32_t* sched, int sched_cap, uint32_t* status,
                               float* partials, const uint8_t* sfa, const float* tensor_scale,
                               const float* token_scale, int hidden, int inter, int rows_cap,
-                              int grid, int sm_count, int prefetch_slots, bool pdl,
+                              int grid, int sm_count, int prefetch_slots, int issuers, bool pdl,
                               cudaStream_t stream);
 
 cudaError_t launch_combine_bf16(const void* expert_rows, const int64_t* assignment_to_permuted,
@@ -515,7 +515,7 @@ int do_down_nvfp4(const B200MoeArgs* a, const Scratch& s, int assignments, const
                                 s.status, s.partials,
                                 static_cast<const uint8_t*>(a->down_block_scale), a->down_scale,
                                 s.a_scale, hidden, inter, a->rows_cap, grid, dev.sm_count,
-                                g_nvfp4_prefetch, pdl, stream);
+                                g_nvfp4_prefetch, g_nvfp4_issuers, pdl, stream);
 }
 
 // geometry and pointers the NVFP4 path needs on top of the common checks

@@ -123,25 +123,6 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // With two issuers the gate tile's MMAs come from warp 1 and the up tile's from warp 6:
-  // issuing one block-scaled MMA holds a thread for longer than the tensor core works on it,
-  // and the two tiles have separate accumulators, so two threads issue in parallel.
-  const int issuers = kGateUp && p.issuers == 2 ? 2 : 1;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kFMaxSlots; ++s) {
-      mbar_init(smem_u32(&s_a_full[s]), 1);
-      mbar_init(smem_u32(&s_a_empty[s]), 1);
-      mbar_init(smem_u32(&s_b_full[s]), 1);
-      mbar_init(smem_u32(&s_b_empty[s]), (uint32_t)issuers);
-    }
-    mbar_init(smem_u32(&s_acc), (uint32_t)issuers);
-    mbar_init(smem_u32(&s_sfb_ready), 1);
-    s_abort = 0;
-    fence_mbar_init();
-    prefetch_tensormap(&map_w);
-    prefetch_tensormap(&map_b);
-  }
-  __syncthreads();
 
   // ---- this block's unit (the schedule is final before this grid can start) ----------
   int unit = blockIdx.x;
@@ -165,6 +146,30 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
   trace_start(p.trace, kGateUp ? kTraceGateUp : kTraceDown);
   if (threadIdx.x == 0) STAGE_STAMP(7, 0);
 
+  // Two issuing threads (warps 1 and 6): issuing one block-scaled MMA holds a thread for
+  // longer than the tensor core works on it, so two threads with separate accumulators issue
+  // in parallel.  gate+up: one thread per weight tile (gate, up) of every step.  down: the
+  // threads take alternate steps into two accumulator sets that the epilogue adds -- for
+  // segments of at most 32 rows, with two sets of 64 columns (32 rows: two planes per MMA
+  // and two passes instead of four planes in one).
+  const int issuers = p.issuers == 2 && (kGateUp || n_mma <= 32) ? 2 : 1;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFMaxSlots; ++s) {
+      mbar_init(smem_u32(&s_a_full[s]), 1);
+      mbar_init(smem_u32(&s_a_empty[s]), 1);
+      mbar_init(smem_u32(&s_b_full[s]), 1);
+      // gate+up: both issuers read a step's token planes; down: the step's own issuer does
+      mbar_init(smem_u32(&s_b_empty[s]), kGateUp ? (uint32_t)issuers : 1u);
+    }
+    mbar_init(smem_u32(&s_acc), (uint32_t)issuers);
+    mbar_init(smem_u32(&s_sfb_ready), 1);
+    s_abort = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_b);
+  }
+  __syncthreads();
+
   const int kblocks = (p.k_total + kFStageK - 1) / kFStageK;
   const int k_tiles = (p.k_total + 63) / 64;   // scale tiles along K
   int kb0 = 0, num_kb = kblocks;
@@ -178,7 +183,9 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
   constexpr int kSets = kGateUp ? 2 : 1;   // gate and up tiles, or the one down tile
   const uint32_t plane_bytes = (uint32_t)n_mma * 128u;
   const uint32_t b_bytes = kNvfp4Planes * plane_bytes;
-  const int q_planes = nvfp4_planes_per_mma(n_mma, kGateUp);   // planes per MMA
+  const int q_planes = (!kGateUp && issuers == 2 && n_mma == 32)
+                           ? 2
+                           : nvfp4_planes_per_mma(n_mma, kGateUp);   // planes per MMA
   const int passes = kNvfp4Planes / q_planes;                  // MMAs per weight tile and 64 elements of K
   // gate+up: two token slots serve any number of weight slots; down: one token slot per step
   const int n_b = kGateUp ? 2 : min((int)(p.stage_budget / (kFSlotBytes + b_bytes)), kFMaxSlots);
@@ -221,8 +228,9 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 
   // ---- tensor memory: accumulators, two sets of weight-scale columns, token scales -------
-  const uint32_t set_cols = (uint32_t)(q_planes * n_mma);   // accumulator columns per weight tile
-  const uint32_t acc_cols = kSets * set_cols;
+  const uint32_t set_cols = (uint32_t)(q_planes * n_mma);   // accumulator columns of one set
+  const int acc_sets = kGateUp ? kSets : issuers;            // gate and up tiles, or one set per issuer
+  const uint32_t acc_cols = (uint32_t)acc_sets * set_cols;
   constexpr uint32_t kSfaCols = 2u * 16u;                  // 4 tiles x 4 columns, twice
   const uint32_t sfb_cols = (uint32_t)passes * 4u;
   uint32_t tmem_cols = 32;
@@ -338,7 +346,8 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
         for (int g = 0; g < groups; ++g)
           tmem_copy_scales(sfa_t + (uint32_t)(g * 4), a_addr + kFTileBytes + (uint32_t)g * kFSfTile);
         const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
-        const uint32_t d_tmem = tmem + (uint32_t)set * set_cols;
+        const uint32_t d_tmem = tmem + (uint32_t)(kGateUp ? set : me) * set_cols;
+        const bool first_step = kGateUp ? i == 0 : h < issuers;   // of this accumulator set
         for (int g = 0; g < groups; ++g) {
           for (int pass = 0; pass < passes; ++pass) {
             // the pass's q_planes planes are one operand of q_planes * n_mma rows;
@@ -346,14 +355,19 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
             const uint64_t b_desc =
                 umma_smem_desc_sw128(b_addr + (uint32_t)(pass * q_planes) * plane_bytes) + 2u * g;
             umma_nvfp4(d_tmem, a_desc + 2u * g, b_desc, idesc, sfa_t + (uint32_t)(g * 4),
-                       tmem_sfb + (uint32_t)(pass * 4), (i > 0 || g > 0 || pass > 0) ? 1u : 0u);
+                       tmem_sfb + (uint32_t)(pass * 4), (!first_step || g > 0 || pass > 0) ? 1u : 0u);
           }
         }
         umma_commit(smem_u32(&s_a_empty[sa]));
         if (set == kSets - 1 || issuers == 2) umma_commit(smem_u32(&s_b_empty[sb]));
         STAGE_STAMP(3, h);
       }
-      if (ok && num_kb > 0) umma_commit(smem_u32(&s_acc));
+      if (ok && num_kb > 0) {
+        // an issuer that had no step of its own (a block with a single step) has nothing
+        // in flight: it arrives directly
+        if (me < num_h) umma_commit(smem_u32(&s_acc));
+        else mbar_arrive(smem_u32(&s_acc));
+      }
     }
   } else {
     // ===== epilogue (warps 2..5) =====
@@ -376,15 +390,19 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.0f;
         if (num_kb > 0) {
-          for (int q = 0; q < q_planes; ++q) {
-            uint32_t a[16], b[16];
-            tmem_ld_16(lane_base + (uint32_t)(q * n_mma + c0), a);
-            if (kGateUp) tmem_ld_16(lane_base + set_cols + (uint32_t)(q * n_mma + c0), b);
-            tmem_ld_wait();
+          // down with two issuers: the second set exists only if that issuer had a step
+          const int sets_to_add = kGateUp ? 1 : min(issuers, num_h);
+          for (int a_set = 0; a_set < sets_to_add; ++a_set) {
+            for (int q = 0; q < q_planes; ++q) {
+              uint32_t a[16], b[16];
+              tmem_ld_16(lane_base + (uint32_t)a_set * set_cols + (uint32_t)(q * n_mma + c0), a);
+              if (kGateUp) tmem_ld_16(lane_base + set_cols + (uint32_t)(q * n_mma + c0), b);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              g[j] += __uint_as_float(a[j]);
-              if (kGateUp) u[j] += __uint_as_float(b[j]);
+              for (int j = 0; j < 16; ++j) {
+                g[j] += __uint_as_float(a[j]);
+                if (kGateUp) u[j] += __uint_as_float(b[j]);
+              }
             }
           }
         }
@@ -521,10 +539,10 @@ cudaError_t launch_down_nvfp4(const CUtensorMap& map_w, const CUtensorMap& map_a
                               const int32_t* sched, int sched_cap, uint32_t* status,
                               float* partials, const uint8_t* sfa, const float* tensor_scale,
                               const float* token_scale, int hidden, int inter, int rows_cap,
-                              int grid, int sm_count, int prefetch_slots, bool pdl,
+                              int grid, int sm_count, int prefetch_slots, int issuers, bool pdl,
                               cudaStream_t stream) {
   FGemmParams p = nvfp4_params(sched, sched_cap, status, sfa, tensor_scale, token_scale, hidden,
-                               inter, rows_cap, grid, sm_count, prefetch_slots, 1);
+                               inter, rows_cap, grid, sm_count, prefetch_slots, issuers);
   p.partials = partials;
   return launch_nvfp4<false>(map_w, map_act, p, grid, pdl, stream);
 }
