@@ -36,7 +36,8 @@
 // per SM.  A token slot holds the planes of a step (4 x rows x 128 bytes) and serves both
 // tiles of the step.  Same structure as the other GEMM kernels otherwise: one block =
 // (segment of <= 64 rows, 128-row weight tile[, K split]); warp 0 = TMA producer, warp 1 =
-// TMEM allocation + MMA issue, warps 2..5 = epilogue; every wait bounded.
+// TMEM allocation + MMA issue, warps 2..5 = epilogue, warp 6 = second MMA issuer; every wait
+// bounded.
 #include "common.cuh"
 
 namespace b200moe {

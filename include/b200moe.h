@@ -509,8 +509,9 @@ int b200moe_router_topk(const void* logits, int logits_are_f32, int num_tokens, 
  *                              1 where intermediate_size <= hidden_size, else 0
  *   B200MOE_TUNE_NVFP4_PREFETCH  NVFP4 GEMMs: weight slots a block requests before it waits
  *                              for the previous kernel (0..8, default 8 = the whole ring)
- *   B200MOE_TUNE_NVFP4_ISSUERS  NVFP4 gate+up: 1 = one thread issues the MMAs of the gate and
- *                              the up tile, 2 = one thread each (default)
+ *   B200MOE_TUNE_NVFP4_ISSUERS  NVFP4 GEMMs: 1 = one thread issues every MMA of a block;
+ *                              2 (default) = two threads: gate+up one per weight tile, down
+ *                              alternate K steps (segments of at most 32 rows)
  */
 #define B200MOE_TUNE_STAGE_KB     1
 #define B200MOE_TUNE_L2_PROMOTION 2
