@@ -312,6 +312,11 @@ def dist_setup(n_gpus: int):
     if n_gpus > 1 and world > 1:
         import torch.distributed as dist
 
+        # The product path crosses ranks with plain peer loads and stores of its own kernels;
+        # NCCL serves the unfused baseline and the set-up only.  Its in-switch reduction is
+        # left off unless the caller asks for it, so that no buffer of this process is bound
+        # to an NVLink multicast object (every number in profiles/ was measured this way).
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         return rank, world, local, dist
