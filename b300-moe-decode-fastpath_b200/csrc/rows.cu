@@ -117,6 +117,97 @@ combine_rows_kernel(const int64_t* __restrict__ reverse_mapping,
   trace_end(trace, kTraceCombine);
 }
 
+// The same combine for calls of few assignments, where its latency and not its bytes count:
+// kGroup (a power of two >= top_k) consecutive lanes share eight consecutive hidden columns
+// of one token.  Lane k of the group fetches slot k (its routing weight, its row's split-K
+// slices, all in flight at once), sums the slices and stores the BF16 expert row; the
+// group's first lane then collects the sums with shuffles and adds them in slot order.  The
+// arithmetic is exactly the one of combine_rows_kernel, but the slots' trips to L2 overlap
+// instead of following one another (top_k = 8, one token: 5.4 -> 2.1 us).  With many tokens
+// the extra lanes and shuffles cost more than the latency they hide (top_k = 2, 64 tokens:
+// 2.9 -> 6.2 us), so the host uses it for T * top_k <= kSlotCombineMaxAssign only.
+constexpr int kSlotCombineMaxAssign = 64;
+
+template <int kGroup>
+__global__ void __launch_bounds__(128)
+combine_rows_slots_kernel(const int64_t* __restrict__ reverse_mapping,
+                    const __nv_bfloat16* __restrict__ weights, const float* __restrict__ partials,
+                    const int32_t* __restrict__ sched, uint4* __restrict__ out,
+                    uint4* __restrict__ expert_out, int num_assign, int top_k, int hidden,
+                    size_t slice_elems, int f32_out, unsigned long long* __restrict__ trace) {
+  pdl_wait();
+  pdl_launch_dependents();
+  trace_start(trace, kTraceCombine);
+  const int token = blockIdx.x;
+  const int k = threadIdx.x & (kGroup - 1);                              // this lane's slot
+  const int col = (int)((blockIdx.y * blockDim.x + threadIdx.x) / kGroup) * 8;   // the group's columns
+  const bool in_range = col < hidden;
+  const int splits = sched[kSchedDownSplits];
+
+  int64_t row = -1;
+  float w = 0.0f;
+  if (in_range && k < top_k) {
+    row = reverse_mapping[token * top_k + k];
+    w = __bfloat162float(weights[token * top_k + k]);
+  }
+  const bool ok = row >= 0 && row < (int64_t)num_assign;
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+  if (ok) {
+    const float* src = partials + (size_t)row * hidden + col;
+    float4 lo[kDownSplitMax], hi[kDownSplitMax];
+#pragma unroll
+    for (int s = 0; s < kDownSplitMax; ++s) {
+      if (s < splits) {
+        lo[s] = *reinterpret_cast<const float4*>(src + (size_t)s * slice_elems);
+        hi[s] = *reinterpret_cast<const float4*>(src + (size_t)s * slice_elems + 4);
+      }
+    }
+    v[0] = lo[0].x; v[1] = lo[0].y; v[2] = lo[0].z; v[3] = lo[0].w;
+    v[4] = hi[0].x; v[5] = hi[0].y; v[6] = hi[0].z; v[7] = hi[0].w;
+#pragma unroll
+    for (int s = 1; s < kDownSplitMax; ++s) {
+      if (s < splits) {
+        v[0] += lo[s].x; v[1] += lo[s].y; v[2] += lo[s].z; v[3] += lo[s].w;
+        v[4] += hi[s].x; v[5] += hi[s].y; v[6] += hi[s].z; v[7] += hi[s].w;
+      }
+    }
+    if (expert_out) expert_out[((size_t)row * hidden + col) >> 3] = pack_bf16x8(v);
+  }
+
+  // the group's first lane adds the slots in order
+  const unsigned full = 0xffffffffu;
+  const int leader = (int)(threadIdx.x & 31) & ~(kGroup - 1);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+  for (int kk = 0; kk < kGroup; ++kk) {
+    const float wk = __shfl_sync(full, w, leader + kk);
+    const int okk = __shfl_sync(full, (int)ok, leader + kk);
+    float vk[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vk[i] = __shfl_sync(full, v[i], leader + kk);
+    if (okk) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(vk[i], wk, acc[i]);
+    }
+  }
+  if (k == 0 && in_range) {
+    if (f32_out) {
+      // unrounded sums, for callers that add partial outputs of several ranks
+      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) +
+                                            (size_t)token * hidden + col);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      out[((size_t)token * hidden + col) >> 3] = pack_bf16x8(acc);
+    }
+  }
+  trace_end(trace, kTraceCombine);
+}
+
 // Legacy combine: out[t, :] = bf16( sum_k float(w[t,k]) * float(rows[map[t*K+k], :]) ) on BF16
 // expert rows, FP32 accumulation in slot order, rows with an invalid mapping skipped
 // (csrc/combine_cuda.cu:23-52).
@@ -351,6 +442,15 @@ cudaError_t launch_combine(const int64_t* reverse_mapping, const void* weights,
   void* args[] = {&reverse_mapping, &w, &partials, &sched, &o, &eo, &num_assign, &top_k,
                   &hidden_size, &slice_elems, &f32, &trace};
   const int vecs = hidden_size / 8;
+  if (num_assign <= kSlotCombineMaxAssign && top_k > 1) {
+    // few assignments: one lane per slot, so that the slots' loads overlap
+    const int group = top_k <= 2 ? 2 : (top_k <= 4 ? 4 : 8);
+    const void* kernel = group == 2 ? reinterpret_cast<const void*>(&combine_rows_slots_kernel<2>)
+                         : group == 4 ? reinterpret_cast<const void*>(&combine_rows_slots_kernel<4>)
+                                      : reinterpret_cast<const void*>(&combine_rows_slots_kernel<8>);
+    dim3 grid(num_tokens, (vecs * group + 127) / 128);
+    return launch_with_pdl(kernel, grid, dim3(128), args, pdl, stream);
+  }
   dim3 grid(num_tokens, (vecs + 127) / 128);
   return launch_with_pdl(reinterpret_cast<const void*>(&combine_rows_kernel), grid, dim3(128),
                          args, pdl, stream);
