@@ -271,15 +271,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
     pdl_wait();
     pdl_launch_dependents();
   }
-  if (!kGateUp && p.small) {
-    // The routing kernel's schedule is authoritative; a block whose own derivation
-    // disagreed with it would have streamed the wrong tiles.  Never observed; reported.
-    const int4 header = *reinterpret_cast<const int4*>(p.sched);
-    const int4 entry = *reinterpret_cast<const int4*>(
-        p.sched + kSchedHeaderWords + kSchedSegWords * min(unit / tiles, p.sched_cap - 1));
-    if (header.w != n_split || entry.x != expert || entry.y != row_start || entry.z != n_rows)
-      s_abort = 1;
-  }
 
   tc_fence_before_sync();
   __syncthreads();
@@ -379,11 +370,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
         for (int v = t; v < p.hidden_vecs; v += 128) dst[v] = __ldg(src + v);
       }
     }
+    // Small-call down: the routing kernel's schedule is authoritative; a block whose own
+    // derivation disagreed with it would have streamed the wrong tiles (never observed;
+    // reported, and the block then writes nothing).  Checked here, by the warps that idle
+    // during the main loop, so that the two loads do not stand between the dependency wait
+    // and the producer's first token loads.
+    bool unit_agrees = true;
+    if (!kGateUp && p.small) {
+      const int4 header = *reinterpret_cast<const int4*>(p.sched);
+      const int4 entry = *reinterpret_cast<const int4*>(
+          p.sched + kSchedHeaderWords + kSchedSegWords * min(unit / tiles, p.sched_cap - 1));
+      unit_agrees = header.w == n_split && entry.x == expert && entry.y == row_start &&
+                    entry.z == n_rows;
+      if (!unit_agrees) *abort_flag = 1;
+    }
     // ----- TMEM -> registers -> global -----
     bool have_acc = num_kb > 0;
     if (have_acc) have_acc = mbar_wait_bounded(smem_u32(&s_acc), 0u, abort_flag);
+    have_acc = have_acc && unit_agrees;
     have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld needs the whole warp
-    if (have_acc || num_kb == 0) {
+    if ((have_acc || num_kb == 0) && unit_agrees) {
       // A block that gave up writes nothing; the status word reports it.
       const int m = tile * kTileM + quarter * 32 + lane;  // weight row of this thread
       const bool m_ok = m < p.m_total;
