@@ -453,8 +453,19 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
   pdl_launch_dependents();
   trace_start(p.trace, kTraceCombine);
   const int token = blockIdx.x;
-  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-  const bool active = col < p.hidden;
+  // A block covers 1024 columns, a warp 256 of them, and a lane the four column PAIRS
+  // base + 64 j + 2 lane (j = 0..3): every 16-byte {value, epoch, value, epoch} store of a
+  // warp then lands in one contiguous 512-byte run, so the stores cross NVLink as full
+  // 128-byte writes instead of 32 separate 16-byte ones (a lane that owned 8 adjacent
+  // columns wrote at a 64-byte stride: ~8 us more at T = 64).
+  const int warp_base = blockIdx.y * 1024 + (threadIdx.x >> 5) * 256 + 2 * (threadIdx.x & 31);
+  int cols[4];
+  bool on[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    cols[j] = warp_base + 64 * j;
+    on[j] = cols[j] < p.hidden;
+  }
   const int splits = p.sched[kSchedDownSplits];
   // this rank has begun epoch `epoch`: its previous forward, and every read that forward
   // made of this rank's inbox, is complete
@@ -490,30 +501,41 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
   for (int k = 0; k < 8; ++k) {
     if (k >= p.top_k) break;
     const int64_t row = rows[k];
-    if (row < 0 || row >= (int64_t)p.num_assign || !active) continue;
-    const float* src = p.slices + (size_t)row * p.hidden + col;
-    float4 lo[kDownSplitMax], hi[kDownSplitMax];
+    if (row < 0 || row >= (int64_t)p.num_assign) continue;
+    const float* src = p.slices + (size_t)row * p.hidden;
+    float2 part[kDownSplitMax][4];
 #pragma unroll
     for (int s = 0; s < kDownSplitMax; ++s) {
       if (s < splits) {
-        lo[s] = *reinterpret_cast<const float4*>(src + (size_t)s * p.slice_elems);
-        hi[s] = *reinterpret_cast<const float4*>(src + (size_t)s * p.slice_elems + 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          part[s][j] = on[j] ? *reinterpret_cast<const float2*>(src + (size_t)s * p.slice_elems +
+                                                                 cols[j])
+                             : make_float2(0.0f, 0.0f);
       }
     }
-    float v[8] = {lo[0].x, lo[0].y, lo[0].z, lo[0].w, hi[0].x, hi[0].y, hi[0].z, hi[0].w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = part[0][j].x;
+      v[2 * j + 1] = part[0][j].y;
+    }
 #pragma unroll
     for (int s = 1; s < kDownSplitMax; ++s) {
       if (s < splits) {
-        v[0] += lo[s].x; v[1] += lo[s].y; v[2] += lo[s].z; v[3] += lo[s].w;
-        v[4] += hi[s].x; v[5] += hi[s].y; v[6] += hi[s].z; v[7] += hi[s].w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[2 * j] += part[s][j].x;
+          v[2 * j + 1] += part[s][j].y;
+        }
       }
     }
     if (p.expert_out) {
-      uint4 packed;
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+      __nv_bfloat162* out_row =
+          reinterpret_cast<__nv_bfloat162*>(p.expert_out) + (((size_t)row * p.hidden) >> 1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-      p.expert_out[((size_t)row * p.hidden + col) >> 3] = packed;
+      for (int j = 0; j < 4; ++j)
+        if (on[j]) out_row[cols[j] >> 1] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
     }
     const float w = wts[k];
 #pragma unroll
@@ -543,57 +565,59 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
     }
   }
   __syncthreads();
-  // words of 8 bytes: word index of (slot rank r, token, col) inside one parity half
+  // words of 8 bytes: word index of (slot rank r, token, column) inside one parity half;
+  // a column pair is one 16-byte vector (every term of the index is even)
   const size_t parity_base = (size_t)(p.epoch & 1u) * p.world * p.rank_stride;
-  const size_t at = (size_t)token * p.hidden + col;
-  if (contributes && active && s_ok) {
-    const size_t word = parity_base + (size_t)p.rank * p.rank_stride + at;  // 8 words follow
+  const size_t at = (size_t)token * p.hidden;
+  if (contributes && s_ok) {
+    const size_t word = parity_base + (size_t)p.rank * p.rank_stride + at;
 #pragma unroll
     for (int r = 0; r < kMaxEpWorld; ++r) {
       if (r < p.world && ((targets >> r) & 1u)) {
-        uint4* dst = p.inbox[r] + (word >> 1);  // two words per 16 bytes
+        uint4* dst = p.inbox[r] + (word >> 1);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          dst[j] = make_uint4(__float_as_uint(acc[2 * j]), p.epoch,
-                              __float_as_uint(acc[2 * j + 1]), p.epoch);
+          if (on[j])
+            dst[cols[j] >> 1] = make_uint4(__float_as_uint(acc[2 * j]), p.epoch,
+                                           __float_as_uint(acc[2 * j + 1]), p.epoch);
       }
     }
   }
 
   // ---- 3. tokens this rank outputs ---------------------------------------------------
   if (token < p.first_token || token >= p.first_token + p.out_tokens) return;
-  const size_t out_at = ((size_t)(token - p.first_token) * p.hidden + col) >> 3;
+  __nv_bfloat162* out_row = reinterpret_cast<__nv_bfloat162*>(p.output) +
+                            (((size_t)(token - p.first_token) * p.hidden) >> 1);
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
   bool ok = s_ok != 0;
-  if (active) {
 #pragma unroll
-    for (int r = 0; r < kMaxEpWorld; ++r) {
-      if (r >= p.world || !((owners >> r) & 1u)) continue;
-      if (r == p.rank) {
+  for (int r = 0; r < kMaxEpWorld; ++r) {
+    if (r >= p.world || !((owners >> r) & 1u)) continue;
+    if (r == p.rank) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum[i] += acc[i];
-        continue;
-      }
-      const uint4* src = p.inbox[p.rank] + ((parity_base + (size_t)r * p.rank_stride + at) >> 1);
-      uint4 w[4];
-      uint32_t spins = 0;
-      while (ok) {
+      for (int i = 0; i < 8; ++i) sum[i] += acc[i];
+      continue;
+    }
+    const uint4* src = p.inbox[p.rank] + ((parity_base + (size_t)r * p.rank_stride + at) >> 1);
+    uint4 w[4];
+    uint32_t spins = 0;
+    while (ok) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = ld_volatile_v4(src + j);
-        bool all = true;
+      for (int j = 0; j < 4; ++j)
+        w[j] = on[j] ? ld_volatile_v4(src + (cols[j] >> 1)) : make_uint4(0u, p.epoch, 0u, p.epoch);
+      bool all = true;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) all = all && w[j].y == p.epoch && w[j].w == p.epoch;
-        if (all) break;
-        if ((++spins & 15u) == 0u && global_timer_ns() - t0 > p.wait_limit_ns) ok = false;
-      }
-      if (ok) {
+      for (int j = 0; j < 4; ++j) all = all && w[j].y == p.epoch && w[j].w == p.epoch;
+      if (all) break;
+      if ((++spins & 15u) == 0u && global_timer_ns() - t0 > p.wait_limit_ns) ok = false;
+    }
+    if (ok) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          sum[2 * j] += __uint_as_float(w[j].x);
-          sum[2 * j + 1] += __uint_as_float(w[j].z);
-        }
+      for (int j = 0; j < 4; ++j) {
+        sum[2 * j] += __uint_as_float(w[j].x);
+        sum[2 * j + 1] += __uint_as_float(w[j].z);
       }
     }
   }
@@ -602,15 +626,14 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
   __syncthreads();
   if (!s_ok) {
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200MOE_STATUS_PEER_TIMEOUT);
-    if (active) p.output[out_at] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (on[j]) out_row[cols[j] >> 1] = __floats2bfloat162_rn(0.0f, 0.0f);
     return;
   }
-  if (!active) return;
-  uint4 packed;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(sum[2 * i], sum[2 * i + 1]);
-  p.output[out_at] = packed;
+  for (int j = 0; j < 4; ++j)
+    if (on[j]) out_row[cols[j] >> 1] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
   trace_end(p.trace, kTraceCombine);
 }
 
