@@ -471,6 +471,16 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
   // made of this rank's inbox, is complete
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < p.world)
     st_relaxed_sys(p.progress[threadIdx.x] + p.rank, p.epoch);
+  // ranks that output this token, as a mask
+  unsigned targets = p.tokens_per_rank > 0 ? 1u << (token / p.tokens_per_rank)
+                                           : (p.world >= 32 ? 0xffffffffu : (1u << p.world) - 1u);
+  targets &= ~(1u << p.rank);
+  // how far each target has got (checked in step 2): the load goes out together with the
+  // loads of step 1 instead of after them; the word only ever grows, so an early value
+  // that already passes is as good as a late one
+  const bool watches = threadIdx.x < p.world && ((targets >> threadIdx.x) & 1u);
+  uint32_t progress_seen = p.epoch;
+  if (watches) progress_seen = ld_relaxed_sys(p.progress[p.rank] + threadIdx.x);
 
   // ---- 1. this rank's share of the token (as in ep_combine_reduce_kernel) ------------
   float acc[8];
@@ -543,25 +553,20 @@ ep_combine_push_kernel(const EpPushCombineParams p) {
   }
 
   // ---- 2. push this rank's row to the ranks that output the token --------------------
-  // ranks that output this token, as a mask
-  unsigned targets = p.tokens_per_rank > 0 ? 1u << (token / p.tokens_per_rank)
-                                           : (p.world >= 32 ? 0xffffffffu : (1u << p.world) - 1u);
-  targets &= ~(1u << p.rank);
   const uint64_t t0 = global_timer_ns();
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  if (contributes) {
+  if (contributes && watches) {
     // the slot was last used two epochs ago: wait (normally not at all) until the target
     // has begun the previous epoch
-    if (threadIdx.x < p.world && ((targets >> threadIdx.x) & 1u)) {
-      const uint32_t* word = p.progress[p.rank] + threadIdx.x;
-      while ((int32_t)(ld_relaxed_sys(word) - (p.epoch - 1u)) < 0) {
-        if (global_timer_ns() - t0 > p.wait_limit_ns) {
-          s_ok = 0;
-          break;
-        }
-        __nanosleep(32);
+    const uint32_t* word = p.progress[p.rank] + threadIdx.x;
+    while ((int32_t)(progress_seen - (p.epoch - 1u)) < 0) {
+      if (global_timer_ns() - t0 > p.wait_limit_ns) {
+        s_ok = 0;
+        break;
       }
+      __nanosleep(32);
+      progress_seen = ld_relaxed_sys(word);
     }
   }
   __syncthreads();
