@@ -59,6 +59,18 @@ def expert_range(rank: int, world: int, num_experts: int) -> tuple[int, int]:
     return rank * per_rank, per_rank
 
 
+class _StepPlan:
+    """What a repeated step of one rank needs, remembered after one fully checked forward with
+    replicated tokens over peer memory (the counterpart of ``forward._CallPlan``): a later
+    forward whose three tensors have the same dtypes, device, layout and width, on the same
+    stream and workspace allocation, rewrites the per-call fields of the bound argument
+    struct and goes straight to the two library calls of the step.  Anything else takes the
+    checked path, which also covers every error case."""
+
+    __slots__ = ("device", "device_index", "allocations", "stream", "stream_ptr", "args",
+                 "args_ref", "fn", "flags", "shape_tail")
+
+
 class ExpertParallelMoE:
     """The MoE decode layer with its experts spread over the ranks of a process group."""
 
@@ -125,6 +137,8 @@ class ExpertParallelMoE:
         self._checked = False
         self._last_call = None
         self.last_tokens = 0
+        self._plan: _StepPlan | None = None
+        self.repeated_steps = 0  # forwards that took the remembered plan
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' or 'p2p'")
         if transport == "p2p" and not self._native:
@@ -255,7 +269,7 @@ class ExpertParallelMoE:
         return gathered, (self._g_flags.data_ptr(), self.world, self._epoch & 0xFFFFFFFF)
 
     def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype,
-                     first_token: int = 0) -> torch.Tensor:
+                     first_token: int = 0, stream_ptr: int | None = None) -> torch.Tensor:
         """One launch after the down projection: this rank's combine, publish, wait for the
         peers (bounded), add the owning ranks' partial rows in rank order over NVLink, round
         to BF16.  ``tokens`` rows starting at ``first_token`` are returned."""
@@ -288,6 +302,12 @@ class ExpertParallelMoE:
         args.status = self.workspace.scratch.data_ptr()
         layer_args = self._last_call[0]
         lib = _lib.load()
+        if stream_ptr is not None:  # a repeated step: device and stream are already checked
+            code = lib.b200moe_ep_combine_reduce(ctypes.byref(layer_args), ctypes.byref(args),
+                                                 stream_ptr)
+            if code:
+                _lib.check(code, "b200moe_ep_combine_reduce")
+            return output
         stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         if torch.cuda.current_device() == device.index:
             code = lib.b200moe_ep_combine_reduce(ctypes.byref(layer_args), ctypes.byref(args),
@@ -385,6 +405,91 @@ class ExpertParallelMoE:
                 raise ValueError("the NVFP4 path requires H and I divisible by 64")
         _lib.load()
 
+    # ------------------------------------------------------------------ repeated steps
+    def _remember_step(self) -> None:
+        """Keep what the checked forward that just ran established (peer transport,
+        replicated tokens)."""
+
+        ws = self.workspace
+        if ws is None or self._last_call is None or torch.cuda.is_current_stream_capturing():
+            self._plan = None
+            return
+        device = self.gate_up.device
+        plan = _StepPlan()
+        plan.device, plan.device_index = device, device.index
+        plan.allocations = ws.allocation_count
+        plan.stream = torch.cuda.current_stream(device)
+        plan.stream_ptr = int(plan.stream.cuda_stream)
+        plan.args = self._last_call[0]
+        plan.args_ref = ctypes.byref(plan.args)
+        plan.fn = _lib.load().b200moe_forward
+        plan.flags = int(plan.args.flags)
+        plan.shape_tail = tuple(ws._last_shape[1:]) if ws._last_shape else None
+        self._plan = plan if plan.shape_tail is not None else None
+
+    def _repeat_step(self, hidden: torch.Tensor, ids: torch.Tensor,
+                     weights: torch.Tensor) -> torch.Tensor | None:
+        """The output of a replicated-token forward that matches the remembered plan, or
+        ``None`` (the caller then takes the checked path)."""
+
+        plan, ws = self._plan, self.workspace
+        if plan is None or ws is None or hidden.dim() != 2:
+            return None
+        tokens = hidden.shape[0]
+        if (
+            hidden.shape[1] != self.hidden_size
+            or tuple(ids.shape) != (tokens, self.top_k)
+            or weights.shape != ids.shape
+            or hidden.dtype is not torch.bfloat16
+            or weights.dtype is not torch.bfloat16
+            or ids.dtype is not torch.int64
+            or hidden.device != plan.device
+            or ids.device != plan.device
+            or weights.device != plan.device
+            or not hidden.is_contiguous()
+            or not ids.is_contiguous()
+            or not weights.is_contiguous()
+            or hidden.requires_grad
+            or weights.requires_grad
+            or tokens < 1
+            or tokens > self.capacity_tokens
+            or torch.cuda.current_device() != plan.device_index
+        ):
+            return None
+        with ws._lock:
+            if (
+                ws._allocations != plan.allocations
+                or tokens > ws._tokens
+                or ws._last_stream != plan.stream_ptr
+                or torch._C._cuda_getCurrentRawStream(plan.device_index) != plan.stream_ptr
+                or torch._C._cuda_isCurrentStreamCapturing()
+            ):
+                return None
+            self._epoch += 1
+            args = plan.args
+            args.hidden_states = hidden.data_ptr()
+            args.expert_indices = ids.data_ptr()
+            args.expert_weights = weights.data_ptr()
+            args.num_tokens = tokens
+            args.output = None
+            args.flags = plan.flags
+            args.expert_id_base = self.base
+            args.ep_wait_flags = None
+            args.ep_world = 0
+            args.ep_epoch = 0
+            args.ep_wait_limit_us = 0
+            code = plan.fn(plan.args_ref, plan.stream_ptr)
+            if code:
+                _lib.check(code, "b200moe_forward (expert-parallel rank)")
+            ws._reuses += 1
+            ws._last_reused = True
+            ws._last_shape = (tokens,) + plan.shape_tail
+            ws._event.record(plan.stream)
+        self._last_call = (args, (hidden, ids, weights, self.gate_up, self.down, None))
+        self.last_tokens = tokens
+        self.repeated_steps += 1
+        return self._peer_reduce(tokens, self._epoch & 1, hidden.dtype, 0, plan.stream_ptr)
+
     # ------------------------------------------------------------------ forward
     def forward(
         self,
@@ -408,9 +513,16 @@ class ExpertParallelMoE:
             raise ValueError("tokens must be 'replicated' or 'sharded'")
         if expert_indices.shape[1] != self.top_k:
             raise ValueError("top_k must match expert_indices.shape[1]")
+        if tokens == "replicated" and self._plan is not None:
+            output = self._repeat_step(hidden_states, expert_indices, expert_weights)
+            if output is not None:
+                if check_status:
+                    self.workspace.raise_for_status()
+                return output
         local_tokens = hidden_states.shape[0]
         self._epoch += 1
         sharded = tokens == "sharded" and self.world > 1
+        self._plan = None
         ep_wait = None
         if sharded and self.transport == "p2p":
             (hidden_all, ids_all, weights_all), ep_wait = self._peer_dispatch(
@@ -433,6 +545,8 @@ class ExpertParallelMoE:
             first = self.rank * local_tokens if sharded else 0
             rows = local_tokens if sharded else hidden_all.shape[0]
             output = self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first)
+            if tokens == "replicated":
+                self._remember_step()
             if check_status:
                 self.workspace.raise_for_status()
             return output

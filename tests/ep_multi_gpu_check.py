@@ -64,6 +64,19 @@ def main() -> int:
                 worst = max(worst, err, err_s)
                 assert err <= 2e-2 and err_s <= 2e-2, (transport, repeat, err, err_s)
                 assert layer.workspace.status() == 0
+            if transport == "p2p":
+                # back-to-back replicated steps with fresh tensors and changing token counts
+                # take the plan remembered after one checked step, and give the same rows
+                layer.forward(*dev, tokens="replicated")
+                before = layer.repeated_steps
+                for n in (T, T // 2, 2, T):
+                    fresh = tuple(t[:n].clone() for t in dev)
+                    out = layer.forward(*fresh, tokens="replicated")
+                    err = moe_oracle.relative_max_error(out.float().cpu(), ref[:n])
+                    worst = max(worst, err)
+                    assert err <= 2e-2, ("repeated step", n, err)
+                assert layer.repeated_steps == before + 4, layer.repeated_steps
+                assert layer.workspace.status() == 0
         torch.cuda.synchronize(device)
         print(f"EP_CHECK_OK rank={rank} world={world} worst_err_over_rms={worst:.5f} "
               f"floor={moe_oracle.bf16_floor(ref):.5f}", flush=True)
