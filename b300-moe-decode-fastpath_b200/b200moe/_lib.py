@@ -30,6 +30,7 @@ FLAG_HOST_IO = 0x10
 FLAG_SKIP_COMBINE = 0x20
 FLAG_EP_PUSH = 0x40
 FLAG_NVFP4_WEIGHTS = 0x80
+FLAG_EP_AFTER_PUSH = 0x100
 
 STATIC_ROUTING_MAX_ASSIGNMENTS = 4096
 

@@ -343,7 +343,7 @@ class ExpertParallelMoE:
             expert_id_base=self.base, num_experts_global=self.num_experts,
             workspace=self.workspace, use_pdl=self.use_pdl, ep_wait=ep_wait,
             fp8_scales=self.fp8_scales, nvfp4_scales=self.nvfp4_scales, skip_combine=p2p,
-            ep_wait_limit_us=self.wait_limit_us,
+            ep_wait_limit_us=self.wait_limit_us, after_push=ep_wait is not None,
         )
         self._last_call = call
         return partial
@@ -610,6 +610,7 @@ def local_partial_forward(
     skip_combine: bool = False,
     ep_wait_limit_us: int = 0,
     nvfp4_scales: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+    after_push: bool = False,
 ):
     """One rank's share of the layer: FP32 ``[T,H]`` sum over the assignments whose expert
     id lies in ``[expert_id_base, expert_id_base + E_local)``.
@@ -665,6 +666,10 @@ def local_partial_forward(
             # kernel waits for every rank's pushed shard before it reads ids or rows
             args.ep_wait_flags, args.ep_world, args.ep_epoch = ep_wait
             args.ep_wait_limit_us = ep_wait_limit_us
+            if after_push:
+                # the dispatch kernel was enqueued just before this call on the same stream:
+                # the routing kernel may start beside it and wait for the flags alone
+                args.flags |= _lib.FLAG_EP_AFTER_PUSH
         code = _enqueue(_lib.load().b200moe_forward, args, hidden.device)
         if code:
             _lib.check(code, "b200moe_forward (expert-parallel rank)")

@@ -22,7 +22,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
                            unsigned long long wait_limit_ns, bool after_gate_up, bool pdl,
-                           void* zero_rows, int zero_row_vecs, cudaStream_t stream);
+                           bool after_dispatch, void* zero_rows, int zero_row_vecs,
+                           cudaStream_t stream);
 cudaError_t launch_ep_push(const void* hidden, const int64_t* ids, const void* weights,
                            void* const* hidden_dst, void* const* ids_dst,
                            void* const* weights_dst, void* const* flag_ptrs,
@@ -362,6 +363,8 @@ int do_routing(const B200MoeArgs* a, const Scratch& s, const DeviceInfo& dev,
                              (a->ep_wait_limit_us ? (unsigned long long)a->ep_wait_limit_us
                                                   : 1000000ull) * 1000ull,
                              after_gate_up, pdl,
+                             (a->flags & B200MOE_FLAG_EP_AFTER_PUSH) != 0 &&
+                                 (a->flags & B200MOE_FLAG_PDL) != 0,
                              after_gate_up ? a->permuted_hidden : nullptr, a->hidden_size / 8,
                              stream);
 }

@@ -248,7 +248,8 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
                            int target_ctas, int seg_rows, int id_base, bool foreign_ids_allowed,
                            const uint32_t* wait_flags, int wait_world, uint32_t wait_epoch,
                            unsigned long long wait_limit_ns, bool after_gate_up, bool pdl,
-                           void* zero_rows, int zero_row_vecs, cudaStream_t stream) {
+                           bool after_dispatch, void* zero_rows, int zero_row_vecs,
+                           cudaStream_t stream) {
   // One thread per expert and per assignment of a round, in whole warps; fewer warps make
   // the block-wide barriers of a decode-sized call cheaper.
   int threads = num_assign > num_experts ? num_assign : num_experts;
@@ -265,7 +266,10 @@ cudaError_t launch_routing(const int64_t* ids, const void* weights, int num_assi
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (after_gate_up && pdl) ? 1 : 0;
+  // `after_dispatch`: the kernel in front is this step's dispatch of sharded tokens, whose
+  // flags this kernel waits for anyway (its own rank's included), so it need not wait for
+  // that kernel's completion, only for the flags.
+  cfg.numAttrs = ((after_gate_up && pdl) || (after_dispatch && wait_flags != nullptr)) ? 1 : 0;
   return cudaLaunchKernelEx(
       &cfg, routing_kernel, ids, static_cast<const __nv_bfloat16*>(weights), num_assign, top_k,
       num_experts, counts, offsets, reverse_mapping, permutation, offsets_i32, perm_tokens,
@@ -340,8 +344,8 @@ cudaError_t launch_routing_static(const int64_t* ids, const void* weights, int n
                         reverse_mapping, permutation, offsets_i32, perm_tokens, perm_experts,
                         perm_weights, reinterpret_cast<int32_t*>(b + kStatusBytes),
                         reinterpret_cast<uint32_t*>(b), down_tiles, down_kblocks, target_ctas,
-                        kSegRows, 0, false, nullptr, 0, 0u, 0ull, false, false, nullptr, 0,
-                        stream);
+                        kSegRows, 0, false, nullptr, 0, 0u, 0ull, false, false, false, nullptr,
+                        0, stream);
 }
 
 }  // namespace b200moe

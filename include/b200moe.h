@@ -86,6 +86,14 @@ extern "C" {
  * what the reference's "cutlass_nvfp4" backend names and never had
  * (csrc/quantization_kernels.cu:3-13).  Not combined with B200MOE_FLAG_FP8_WEIGHTS. */
 #define B200MOE_FLAG_NVFP4_WEIGHTS 0x80u
+/* With ep_wait_flags and B200MOE_FLAG_PDL: the kernel in front of this call in its stream is
+ * the b200moe_ep_push of the same step, launched without any launch attribute.  The routing
+ * kernel, which waits for every rank's dispatch flag (this rank's own included) before it
+ * reads anything the dispatch writes, may then start while that kernel is still running
+ * (programmatic dependent launch) instead of after its completion.  Only for that
+ * situation: with any other kernel in front, the routing kernel could overwrite what an
+ * earlier forward's last kernel still reads. */
+#define B200MOE_FLAG_EP_AFTER_PUSH 0x100u
 /* With B200MOE_FLAG_FP8_WEIGHTS the staged entry points keep their meaning, with two
  * details: b200moe_gather also writes the gathered rows as E4M3 planes into scratch, which
  * b200moe_gate_up_swiglu consumes; b200moe_down first turns the activation rows into planes
