@@ -83,6 +83,34 @@ def test_args_struct_matches_the_header_field_order() -> None:
     assert ctypes.sizeof(B200MoeArgs) % 8 == 0
 
 
+def test_python_constants_match_the_header() -> None:
+    """Flags, status bits, tuning knobs and limits of the bindings are the header's."""
+
+    from b200moe import _lib
+
+    text = HEADER.read_text()
+    defines = {
+        name: int(value.rstrip("uU"), 0)
+        for name, value in re.findall(
+            r"^#define\s+B200MOE_(\w+)\s+\(?(-?(?:0[xX][0-9a-fA-F]+|\d+)[uU]?)\)?", text, re.M)
+    }
+    checked = 0
+    for name, value in vars(_lib).items():
+        if name.startswith(("FLAG_", "STATUS_", "TUNE_")) and isinstance(value, int):
+            assert defines.get(name) == value, (name, value, defines.get(name))
+            checked += 1
+    assert checked >= 20
+    # every flag, status bit and knob of the header has its Python name, and no two flags
+    # or two knobs share a value
+    for prefix in ("FLAG_", "STATUS_", "TUNE_"):
+        names = [n for n in defines if n.startswith(prefix)]
+        assert all(hasattr(_lib, n) for n in names), [n for n in names if not hasattr(_lib, n)]
+        values = [defines[n] for n in names]
+        assert len(set(values)) == len(values), prefix
+    assert _lib.EP_MAX_WORLD == defines["EP_MAX_WORLD"]
+    assert _lib.STATIC_ROUTING_MAX_ASSIGNMENTS == defines["STATIC_ROUTING_MAX_ASSIGNMENTS"]
+
+
 def test_scratch_bytes_and_host_side_errors(lib) -> None:
     from b200moe import _lib
 
