@@ -408,8 +408,9 @@ def _combine_push_call(device, ranks, rank, inboxes, flags, epoch, first, rows, 
     return output
 
 
-@pytest.mark.parametrize("spec", [(4, 16, 256, 384, 8, 2), (8, 64, 512, 256, 16, 4)],
-                         ids=["world4", "world8"])
+@pytest.mark.parametrize("spec", [(4, 16, 256, 384, 8, 2), (8, 64, 512, 256, 16, 4),
+                                  (2, 8, 1160, 256, 8, 2)],
+                         ids=["world4", "world8", "world2_ragged_width"])
 def test_push_combine_reduce_with_all_ranks_inboxes_on_one_gpu(spec, cuda_device) -> None:
     """The flagged-row push variant with every rank's inbox on this GPU.  Ranks run one after
     another, never together: in the first round a rank that runs before the owners of its
