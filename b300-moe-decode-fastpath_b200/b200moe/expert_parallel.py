@@ -269,14 +269,16 @@ class ExpertParallelMoE:
         return gathered, (self._g_flags.data_ptr(), self.world, self._epoch & 0xFFFFFFFF)
 
     def _peer_reduce(self, tokens: int, parity: int, dtype: torch.dtype,
-                     first_token: int = 0, stream_ptr: int | None = None) -> torch.Tensor:
+                     first_token: int = 0, stream_ptr: int | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
         """One launch after the down projection: this rank's combine, publish, wait for the
         peers (bounded), add the owning ranks' partial rows in rank order over NVLink, round
         to BF16.  ``tokens`` rows starting at ``first_token`` are returned."""
 
         assert self.workspace is not None and self.workspace.scratch is not None
         device = self.gate_up.device
-        output = torch.empty(tokens, self.hidden_size, dtype=dtype, device=device)
+        output = out if out is not None else \
+            torch.empty(tokens, self.hidden_size, dtype=dtype, device=device)
         args = self._reduce_args
         if args is None:
             # everything that does not change between forwards is filled in once
@@ -427,8 +429,8 @@ class ExpertParallelMoE:
         plan.shape_tail = tuple(ws._last_shape[1:]) if ws._last_shape else None
         self._plan = plan if plan.shape_tail is not None else None
 
-    def _repeat_step(self, hidden: torch.Tensor, ids: torch.Tensor,
-                     weights: torch.Tensor) -> torch.Tensor | None:
+    def _repeat_step(self, hidden: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                     out: torch.Tensor | None = None) -> torch.Tensor | None:
         """The output of a replicated-token forward that matches the remembered plan, or
         ``None`` (the caller then takes the checked path)."""
 
@@ -488,7 +490,7 @@ class ExpertParallelMoE:
         self._last_call = (args, (hidden, ids, weights, self.gate_up, self.down, None))
         self.last_tokens = tokens
         self.repeated_steps += 1
-        return self._peer_reduce(tokens, self._epoch & 1, hidden.dtype, 0, plan.stream_ptr)
+        return self._peer_reduce(tokens, self._epoch & 1, hidden.dtype, 0, plan.stream_ptr, out)
 
     # ------------------------------------------------------------------ forward
     def forward(
@@ -499,8 +501,14 @@ class ExpertParallelMoE:
         *,
         tokens: str = "replicated",
         check_status: bool = False,
+        out: torch.Tensor | None = None,
     ) -> torch.Tensor:
         """Run the layer; returns BF16 ``[T,H]`` for the tokens this rank was given.
+
+        ``out`` (peer transport only): where the cross-rank combine stores this rank's rows
+        instead of a fresh tensor -- contiguous, of the inputs' shape and dtype, on this
+        rank's GPU or in pinned host memory (the rows then cross PCIe from the kernel and no
+        device-to-host copy is needed).
 
         A peer that does not arrive within the wait limit does not hang the call: the rows
         that needed it come back as zeros and ``B200MOE_STATUS_PEER_TIMEOUT`` is set in the
@@ -513,8 +521,17 @@ class ExpertParallelMoE:
             raise ValueError("tokens must be 'replicated' or 'sharded'")
         if expert_indices.shape[1] != self.top_k:
             raise ValueError("top_k must match expert_indices.shape[1]")
+        if out is not None:
+            if self.transport != "p2p":
+                raise ValueError("out needs transport='p2p'")
+            if not isinstance(out, torch.Tensor) or out.shape != hidden_states.shape or \
+                    out.dtype != hidden_states.dtype or not out.is_contiguous() or \
+                    not (out.device == hidden_states.device or
+                         (out.device.type == "cpu" and out.is_pinned())):
+                raise ValueError("out must be a contiguous tensor of the inputs' shape and "
+                                 "dtype on this rank's GPU or in pinned host memory")
         if tokens == "replicated" and self._plan is not None:
-            output = self._repeat_step(hidden_states, expert_indices, expert_weights)
+            output = self._repeat_step(hidden_states, expert_indices, expert_weights, out)
             if output is not None:
                 if check_status:
                     self.workspace.raise_for_status()
@@ -544,7 +561,8 @@ class ExpertParallelMoE:
             # a sharded caller only needs its own rows: reduce that slice of every partial
             first = self.rank * local_tokens if sharded else 0
             rows = local_tokens if sharded else hidden_all.shape[0]
-            output = self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first)
+            output = self._peer_reduce(rows, self._epoch & 1, hidden_states.dtype, first,
+                                       out=out)
             if tokens == "replicated":
                 self._remember_step()
             if check_status:

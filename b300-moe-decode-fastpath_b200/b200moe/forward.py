@@ -169,6 +169,19 @@ def _enqueue(fn, args, device: torch.device) -> int:
         return fn(ctypes.byref(args), stream)
 
 
+def _check_out(out: torch.Tensor, hidden_states: torch.Tensor) -> None:
+    """``out`` of :func:`b300_moe_forward`: where the combine kernel stores the result."""
+
+    if not isinstance(out, torch.Tensor):
+        raise TypeError("out must be a torch.Tensor or None")
+    if out.shape != hidden_states.shape or out.dtype != hidden_states.dtype or \
+            not out.is_contiguous() or out.requires_grad:
+        raise ValueError("out must be a contiguous [T, H] tensor of the input dtype that does "
+                         "not require grad")
+    if out.device != hidden_states.device and not (out.device.type == "cpu" and out.is_pinned()):
+        raise ValueError("out must be on the inputs' device or in pinned host memory")
+
+
 def _run_native(
     hidden_states: torch.Tensor,
     expert_indices: torch.Tensor,
@@ -178,11 +191,13 @@ def _run_native(
     shape: RoutedMoEShape,
     workspace: B300MoEWorkspace,
     flags: int,
+    out: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, dict[str, torch.Tensor]]:
     """One C call enqueues routing, gather, gate+up+SwiGLU, down and combine."""
 
-    # The result is a fresh tensor, never a view of scratch (b300_moe.py:659).
-    output = torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
+    # The result is a fresh tensor (or the caller's), never a view of scratch (b300_moe.py:659).
+    output = out if out is not None else \
+        torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
     args = _native_args(
         hidden_states,
         expert_indices,
@@ -260,7 +275,7 @@ def _remember_plan(workspace, hidden_states, expert_indices, gate_up_weight, dow
 
 def _repeat_call(workspace, hidden_states, expert_indices, expert_weights, gate_up_weight,
                  down_weight, num_experts, top_k, quant_mode, backend, gemm_policy, use_pdl,
-                 weights_obj=None):
+                 weights_obj=None, out=None):
     """The output of a call that matches the workspace's remembered plan, or ``None``."""
 
     plan = workspace._plan
@@ -305,7 +320,7 @@ def _repeat_call(workspace, hidden_states, expert_indices, expert_weights, gate_
             or torch._C._cuda_isCurrentStreamCapturing()
         ):
             return None
-        output = torch.empty_like(hidden_states)
+        output = out if out is not None else torch.empty_like(hidden_states)
         args = plan.args
         args.hidden_states = hidden_states.data_ptr()
         args.expert_indices = expert_indices.data_ptr()
@@ -342,6 +357,7 @@ def b300_moe_forward(
     return_metadata: bool = False,
     check_status: bool = False,
     use_pdl: bool = True,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor | tuple[torch.Tensor, dict[str, object]]:
     """Explicitly routed two-GEMM SwiGLU MoE layer for decode-sized batches.
 
@@ -357,16 +373,22 @@ def b300_moe_forward(
     validated and reported but selects nothing.  ``check_status=True`` reads the
     device status word after the call (one synchronisation) and raises for
     out-of-range expert ids.  ``use_pdl`` chains the five kernels with
-    programmatic dependent launch.
+    programmatic dependent launch.  ``out`` (not in the reference's signature; BF16 backends
+    only) is where the combine kernel stores the result instead of a fresh tensor: a
+    contiguous ``[T,H]`` tensor on the same device, or in pinned host memory -- the rows then
+    cross PCIe from the kernel itself and no device-to-host copy is needed; the result is
+    valid once the stream has been synchronised.
     """
 
     if not isinstance(return_metadata, bool):
         raise TypeError("return_metadata must be a bool")
+    if out is not None and isinstance(hidden_states, torch.Tensor):
+        _check_out(out, hidden_states)
     if workspace is not None and not return_metadata and not check_status and \
             type(workspace) is B300MoEWorkspace:
         repeated = _repeat_call(workspace, hidden_states, expert_indices, expert_weights,
                                 gate_up_weight, down_weight, num_experts, top_k, quant_mode,
-                                backend, gemm_policy, use_pdl)
+                                backend, gemm_policy, use_pdl, out=out)
         if repeated is not None:
             return repeated
     quant_mode_in = quant_mode
@@ -407,6 +429,8 @@ def b300_moe_forward(
         if shape.hidden_size % 64 or shape.intermediate_size % 64:
             raise ValueError("cutlass_nvfp4 requires hidden_size and intermediate_size "
                              "divisible by 64")
+        if out is not None:
+            raise ValueError("out is supported by the BF16 backends only")
         return b300_moe_forward_nvfp4(
             hidden_states, expert_indices, expert_weights,
             prepared_nvfp4_weights(gate_up_weight, down_weight), num_experts=num_experts,
@@ -435,6 +459,7 @@ def b300_moe_forward(
             shape,
             active,
             _lib.FLAG_PDL if use_pdl else 0,
+            out,
         )
         metadata: dict[str, object] | None = None
         if return_metadata:

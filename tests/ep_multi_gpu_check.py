@@ -117,6 +117,19 @@ def main() -> int:
                     assert err <= 2e-2, ("repeated step", n, err)
                 assert layer.repeated_steps == before + 4, layer.repeated_steps
                 assert layer.workspace.status() == 0
+                # out=: the combine kernel stores into the caller's tensor, on the device or
+                # in pinned host memory, with the same bits
+                want_rows = layer.forward(*dev, tokens="replicated").clone()
+                for target in (torch.empty_like(want_rows),
+                               torch.empty(T, H, dtype=want_rows.dtype).pin_memory()):
+                    got = layer.forward(*dev, tokens="replicated", out=target)
+                    torch.cuda.synchronize(device)
+                    assert got is target and torch.equal(target.to(device), want_rows)
+                mine_rows = layer.forward(*shard, tokens="sharded").clone()
+                host_rows = torch.empty(per, H, dtype=mine_rows.dtype).pin_memory()
+                layer.forward(*shard, tokens="sharded", out=host_rows)
+                torch.cuda.synchronize(device)
+                assert torch.equal(host_rows.to(device), mine_rows)
         torch.cuda.synchronize(device)
         soak_steps = mixed_steps(layer, gate_up, down, E, K, H, rank, world, device)
         print(f"EP_CHECK_OK rank={rank} world={world} worst_err_over_rms={worst:.5f} "

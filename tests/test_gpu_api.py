@@ -886,6 +886,45 @@ def test_pinned_host_io_matches_device_io(cuda_device) -> None:
 
 
 @pytest.mark.gpu
+def test_out_tensor_on_the_device_or_in_pinned_host_memory(cuda_device) -> None:
+    """``out=``: the combine kernel stores into the caller's tensor -- on the device, or in
+    pinned host memory (no device-to-host copy) -- with the same bits as the returned
+    tensor of a plain call, on the checked path and on the repeated-call path, for the
+    small-call order (T * K <= 32) and the five-launch order."""
+
+    from b200moe import B300MoEWorkspace, b300_moe_forward, workloads
+
+    for T in (3, 40):
+        H, I, E, K = 512, 768, 16, 2
+        hidden, ids, weights, gate_up, down = workloads.make_case(
+            T, H, I, E, K, routing="zipf", std=None, device=cuda_device)
+        want = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K)
+        workspace = B300MoEWorkspace(capacity_tokens=64, device=cuda_device)
+        on_device = torch.empty_like(hidden)
+        on_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+        for _ in range(3):  # first call checked, then the remembered plan
+            for out in (on_device, on_host):
+                out.fill_(7.0)
+                got = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E,
+                                       top_k=K, workspace=workspace, out=out)
+                torch.cuda.synchronize(cuda_device)
+                assert got is out
+                assert torch.equal(out.to(cuda_device), want)
+        assert workspace.reuse_count >= 4 and workspace.status() == 0
+        with pytest.raises(ValueError, match="out must be"):
+            b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
+                             workspace=workspace, out=torch.empty(T + 1, H, dtype=torch.bfloat16,
+                                                                  device=cuda_device))
+        with pytest.raises(ValueError, match="pinned"):
+            b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
+                             workspace=workspace, out=torch.empty(T, H, dtype=torch.bfloat16))
+        with pytest.raises(ValueError, match="BF16 backends"):
+            b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
+                             workspace=workspace, backend="cutlass_nvfp4", quant_mode="nvfp4",
+                             out=on_device)
+
+
+@pytest.mark.gpu
 def test_bench_writes_reference_csv_schema(tmp_path):
     """``bench.py --csv`` emits the column set and stage names of the reference's result
     files (benchmark/benchmark_goal_1b.py:55-64, 77-122), one row per (T, stage)."""
