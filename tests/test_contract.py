@@ -240,3 +240,24 @@ def test_graphed_layer_rejects_bad_construction_on_the_host() -> None:
         GraphedMoEDecodeLayer(None, None, num_experts=4, top_k=2)
     with pytest.raises(TypeError, match="Fp8ExpertWeights"):
         GraphedMoEDecodeLayer(None, None, num_experts=4, top_k=2, fp8_weights=(gate_up, down))
+
+
+def test_out_tensor_rules() -> None:
+    """``out=`` of ``b300_moe_forward`` (not in the reference's signature): same shape and
+    dtype as the activations, contiguous, on their device or in pinned host memory."""
+
+    import torch
+
+    from b200moe.forward import _check_out
+
+    hidden = torch.empty(3, 8, dtype=torch.bfloat16, device="meta")
+    _check_out(torch.empty(3, 8, dtype=torch.bfloat16, device="meta"), hidden)
+    with pytest.raises(TypeError, match="out must be a torch.Tensor"):
+        _check_out([0.0], hidden)
+    for bad in (torch.empty(4, 8, dtype=torch.bfloat16, device="meta"),
+                torch.empty(3, 8, dtype=torch.float32, device="meta"),
+                torch.empty(8, 3, dtype=torch.bfloat16, device="meta").t()):
+        with pytest.raises(ValueError, match="out must be a contiguous"):
+            _check_out(bad, hidden)
+    with pytest.raises(ValueError, match="pinned host memory"):
+        _check_out(torch.empty(3, 8, dtype=torch.bfloat16), hidden)  # pageable host memory
