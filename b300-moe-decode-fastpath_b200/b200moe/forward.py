@@ -373,8 +373,8 @@ def b300_moe_forward(
     validated and reported but selects nothing.  ``check_status=True`` reads the
     device status word after the call (one synchronisation) and raises for
     out-of-range expert ids.  ``use_pdl`` chains the five kernels with
-    programmatic dependent launch.  ``out`` (not in the reference's signature; BF16 backends
-    only) is where the combine kernel stores the result instead of a fresh tensor: a
+    programmatic dependent launch.  ``out`` (not in the reference's signature) is where the
+    combine kernel stores the result instead of a fresh tensor: a
     contiguous ``[T,H]`` tensor on the same device, or in pinned host memory -- the rows then
     cross PCIe from the kernel itself and no device-to-host copy is needed; the result is
     valid once the stream has been synchronised.
@@ -429,13 +429,11 @@ def b300_moe_forward(
         if shape.hidden_size % 64 or shape.intermediate_size % 64:
             raise ValueError("cutlass_nvfp4 requires hidden_size and intermediate_size "
                              "divisible by 64")
-        if out is not None:
-            raise ValueError("out is supported by the BF16 backends only")
         return b300_moe_forward_nvfp4(
             hidden_states, expert_indices, expert_weights,
             prepared_nvfp4_weights(gate_up_weight, down_weight), num_experts=num_experts,
             top_k=top_k, workspace=workspace, return_metadata=return_metadata,
-            check_status=check_status, use_pdl=use_pdl, backend_name=backend)
+            check_status=check_status, use_pdl=use_pdl, backend_name=backend, out=out)
     active = workspace if workspace is not None else B300MoEWorkspace(device=hidden_states.device)
 
     with active._lock:

@@ -23,7 +23,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from .forward import (_enqueue, _native_args, _remember_plan, _repeat_call,
+from .forward import (_check_out, _enqueue, _native_args, _remember_plan, _repeat_call,
                       _resolve_native_backend)
 from .validation import RoutedMoEShape, validate_routing
 from .workspace import B300MoEWorkspace
@@ -184,22 +184,26 @@ def b300_moe_forward_fp8(
     return_metadata: bool = False,
     check_status: bool = False,
     use_pdl: bool = True,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor | tuple[torch.Tensor, dict[str, object]]:
     """The layer of :func:`b300_moe_forward` with FP8 expert weights.
 
     Same routing contract, workspace protocol and metadata; ``metadata["backend"]`` is
     ``"b200_fp8"`` and ``quant_mode`` ``"fp8_e4m3_per_row"``.  Segments are 64 rows long
     (128 in the BF16 path), which only changes how the work is cut, not any result tensor.
+    ``out``: as in :func:`b300_moe_forward`.
     """
 
     if not isinstance(return_metadata, bool):
         raise TypeError("return_metadata must be a bool")
+    if out is not None and isinstance(hidden_states, torch.Tensor):
+        _check_out(out, hidden_states)
     if workspace is not None and not return_metadata and not check_status and \
             type(workspace) is B300MoEWorkspace and hasattr(weights, "gate_up_q"):
         # a call that repeats the last fully checked one on this workspace (forward._CallPlan)
         repeated = _repeat_call(workspace, hidden_states, expert_indices, expert_weights,
                                 weights.gate_up_q, weights.down_q, num_experts, top_k, "fp8",
-                                "fp8", None, use_pdl, weights)
+                                "fp8", None, use_pdl, weights, out)
         if repeated is not None:
             return repeated
     shape = _validate(hidden_states, expert_indices, expert_weights, weights, num_experts, top_k)
@@ -215,7 +219,8 @@ def b300_moe_forward_fp8(
             device=hidden_states.device, dtype=hidden_states.dtype, backend="b200_bf16",
             quant_mode="bf16",
         )
-        output = torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
+        output = out if out is not None else \
+            torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
         flags = _lib.FLAG_FP8_WEIGHTS | (_lib.FLAG_PDL if use_pdl else 0)
         args = _native_args(hidden_states, expert_indices, expert_weights, weights.gate_up_q,
                             weights.down_q, shape, active, output, flags)

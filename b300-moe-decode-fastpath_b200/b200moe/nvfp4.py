@@ -27,7 +27,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from .forward import (_enqueue, _native_args, _remember_plan, _repeat_call,
+from .forward import (_check_out, _enqueue, _native_args, _remember_plan, _repeat_call,
                       _resolve_native_backend)
 from .validation import RoutedMoEShape, validate_routing
 from .workspace import B300MoEWorkspace
@@ -223,22 +223,26 @@ def b300_moe_forward_nvfp4(
     check_status: bool = False,
     use_pdl: bool = True,
     backend_name: str = "cutlass_nvfp4",
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor | tuple[torch.Tensor, dict[str, object]]:
     """The layer of :func:`b300_moe_forward` with NVFP4 expert weights.
 
     Same routing contract, workspace protocol and metadata; ``metadata["backend"]`` echoes
     ``backend_name`` and ``quant_mode`` is ``"nvfp4"``.  Segments are 64 rows long (128 in
     the BF16 path), which only changes how the work is cut, not any result tensor.
+    ``out``: as in :func:`b300_moe_forward`.
     """
 
     if not isinstance(return_metadata, bool):
         raise TypeError("return_metadata must be a bool")
+    if out is not None and isinstance(hidden_states, torch.Tensor):
+        _check_out(out, hidden_states)
     if workspace is not None and not return_metadata and not check_status and \
             type(workspace) is B300MoEWorkspace and hasattr(weights, "gate_up_q"):
         # a call that repeats the last fully checked one on this workspace (forward._CallPlan)
         repeated = _repeat_call(workspace, hidden_states, expert_indices, expert_weights,
                                 weights.gate_up_q, weights.down_q, num_experts, top_k, "nvfp4",
-                                "nvfp4", None, use_pdl, weights)
+                                "nvfp4", None, use_pdl, weights, out)
         if repeated is not None:
             return repeated
     shape = _validate(hidden_states, expert_indices, expert_weights, weights, num_experts, top_k)
@@ -255,7 +259,8 @@ def b300_moe_forward_nvfp4(
             device=hidden_states.device, dtype=hidden_states.dtype, backend="b200_bf16",
             quant_mode="bf16",
         )
-        output = torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
+        output = out if out is not None else \
+            torch.empty_like(hidden_states, memory_format=torch.contiguous_format)
         flags = _lib.FLAG_NVFP4_WEIGHTS | (_lib.FLAG_PDL if use_pdl else 0)
         args = _native_args(hidden_states, expert_indices, expert_weights, weights.gate_up_q,
                             weights.down_q, shape, active, output, flags)

@@ -918,10 +918,25 @@ def test_out_tensor_on_the_device_or_in_pinned_host_memory(cuda_device) -> None:
         with pytest.raises(ValueError, match="pinned"):
             b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
                              workspace=workspace, out=torch.empty(T, H, dtype=torch.bfloat16))
-        with pytest.raises(ValueError, match="BF16 backends"):
+        # the quantised paths take it too
+        from b200moe import b300_moe_forward_fp8, quantize_expert_weights_fp8
+
+        fw = quantize_expert_weights_fp8(gate_up, down)
+        want_fp8 = b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K)
+        want_fp4 = b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
+                                    backend="cutlass_nvfp4", quant_mode="nvfp4")
+        for _ in range(2):
+            b300_moe_forward_fp8(hidden, ids, weights, fw, num_experts=E, top_k=K,
+                                 workspace=workspace, out=on_host)
+            torch.cuda.synchronize(cuda_device)
+            assert torch.equal(on_host.to(cuda_device), want_fp8)
+        fp4_workspace = B300MoEWorkspace(capacity_tokens=64, device=cuda_device)
+        for _ in range(2):
             b300_moe_forward(hidden, ids, weights, gate_up, down, num_experts=E, top_k=K,
-                             workspace=workspace, backend="cutlass_nvfp4", quant_mode="nvfp4",
-                             out=on_device)
+                             workspace=fp4_workspace, backend="cutlass_nvfp4",
+                             quant_mode="nvfp4", out=on_host)
+            torch.cuda.synchronize(cuda_device)
+            assert torch.equal(on_host.to(cuda_device), want_fp4)
 
 
 @pytest.mark.gpu
